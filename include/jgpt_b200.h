@@ -1,0 +1,185 @@
+/*
+ * jgpt_b200 — C ABI of the B200-native KV-cache decode path for JGPT.
+ *
+ * Plain C: extern "C", POD arguments, opaque 64-bit handles, int32 status codes.  No PyTorch,
+ * no JNI types.  A JNI shim or a Java FFM (java.lang.foreign) downcall binds these symbols
+ * one to one.  Every entry point names the reference interface it replaces; paths are relative
+ * to the reference project root, J = src/main/java/com/veles/llm/jgpt, C = src/main/cpp.
+ *
+ * Conventions
+ *   - Every function returns a status (0 = JGPT_OK).  jgpt_last_error() returns the message of
+ *     the last failing call on the calling thread.  The Java side maps JGPT_ERR_INVALID_ARGUMENT
+ *     to IllegalArgumentException, JGPT_ERR_ILLEGAL_STATE to IllegalStateException,
+ *     JGPT_ERR_OUT_OF_RANGE to IndexOutOfBoundsException, JGPT_ERR_OUT_OF_MEMORY to OutOfMemoryError,
+ *     i.e. the classes the reference throws for the same misuse.
+ *   - One CUDA stream per context.  Calls on one context are stream ordered and must come from
+ *     one thread at a time (the reference is single threaded per model/cache as well:
+ *     J/model/KvCache.java:11).  Functions that write HOST memory synchronise before returning;
+ *     all others are asynchronous until jgpt_sync().
+ *   - "dev" pointers are device addresses on the context's GPU; "host" pointers are ordinary
+ *     host memory.  fp32 activations are row major, token major: [n_tokens, heads*dhead], head h
+ *     owning columns [h*dhead, (h+1)*dhead) — the layout the projections x.W produce, so the
+ *     reference's split_heads / concat_heads transposes disappear.
+ *   - There is no CPU fallback: without a usable GPU jgpt_ctx_create fails.
+ */
+#ifndef JGPT_B200_H
+#define JGPT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JGPT_API __attribute__((visibility("default")))
+
+typedef uint64_t jgpt_ctx;    /* one GPU + one stream                    */
+typedef uint64_t jgpt_kvpool; /* paged fp16 K/V store of one model       */
+
+
+enum {
+    JGPT_OK = 0,
+    JGPT_ERR_INVALID_ARGUMENT = 1, /* IllegalArgumentException   */
+    JGPT_ERR_ILLEGAL_STATE = 2,    /* IllegalStateException      */
+    JGPT_ERR_OUT_OF_RANGE = 3,     /* IndexOutOfBoundsException  */
+    JGPT_ERR_OUT_OF_MEMORY = 4,    /* OutOfMemoryError (device)  */
+    JGPT_ERR_POOL_EXHAUSTED = 5,   /* no free KV block / sequence slot */
+    JGPT_ERR_BAD_HANDLE = 6,
+    JGPT_ERR_CUDA = 7,
+    JGPT_ERR_UNSUPPORTED = 8,      /* the reference returns null / throws ISE for unsupported shapes */
+    JGPT_ERR_DEVICE_CHECK = 9,     /* a kernel reported a failed self-check or a timed-out wait */
+    JGPT_ERR_IO = 10
+};
+
+/* ---------------------------------------------------------------------------------------------
+ * Runtime: context, stream, device buffers
+ * ------------------------------------------------------------------------------------------- */
+
+/* Replaces TensorOpsGPU.initGPU / isGpuAvailable / requireCuda (J/TensorOpsGPU.java:87-132,
+ * 1197-1203; native C/jgpt_cuda_jni_ops_graph.inl:97-107) and the process-global stream of
+ * C/jgpt_cuda_runtime.inl:234-250.  `device` selects the GPU (the reference hard-codes 0). */
+JGPT_API int32_t jgpt_ctx_create(int32_t device, jgpt_ctx *out);
+JGPT_API int32_t jgpt_ctx_destroy(jgpt_ctx ctx);
+/* TensorOpsGPU.synchronizeStream (C/jgpt_cuda_jni_ops_graph.inl:123-176).  Also reads the
+ * device status word and returns JGPT_ERR_DEVICE_CHECK if a kernel recorded a failure. */
+JGPT_API int32_t jgpt_sync(jgpt_ctx ctx);
+JGPT_API const char *jgpt_last_error(void);
+/* cudaStream_t of the context, for callers that enqueue their own work or time with events. */
+JGPT_API int32_t jgpt_ctx_stream(jgpt_ctx ctx, void **stream_out);
+JGPT_API int32_t jgpt_device_count(int32_t *out);
+
+/* GpuFloatBuffer.allocate / close / copyFrom / copyTo / clear (J/GpuFloatBuffer.java:46-130,
+ * natives C/jgpt_cuda_jni_buffers.inl:185-487).  jgpt_d2h synchronises before returning. */
+JGPT_API int32_t jgpt_dev_alloc(jgpt_ctx ctx, uint64_t bytes, void **dev_out);
+JGPT_API int32_t jgpt_dev_free(jgpt_ctx ctx, void *dev);
+JGPT_API int32_t jgpt_h2d(jgpt_ctx ctx, void *dev_dst, const void *host_src, uint64_t bytes);
+JGPT_API int32_t jgpt_d2h(jgpt_ctx ctx, void *host_dst, const void *dev_src, uint64_t bytes);
+JGPT_API int32_t jgpt_dev_memset(jgpt_ctx ctx, void *dev, int32_t byte_value, uint64_t bytes);
+/* cuda.CudaPinnedHost (C/jgpt_cuda_jni_ops_graph.inl:494-519). */
+JGPT_API int32_t jgpt_host_alloc_pinned(uint64_t bytes, void **host_out);
+JGPT_API int32_t jgpt_host_free_pinned(void *host);
+
+/* Device-side timing on the context's stream (the reference has no equivalent; benchmarks use it). */
+JGPT_API int32_t jgpt_event_create(uint64_t *event_out);
+JGPT_API int32_t jgpt_event_destroy(uint64_t event);
+JGPT_API int32_t jgpt_event_record(jgpt_ctx ctx, uint64_t event);
+JGPT_API int32_t jgpt_event_elapsed_ms(uint64_t start, uint64_t stop, float *ms_out); /* syncs on stop */
+
+/* ---------------------------------------------------------------------------------------------
+ * Paged KV store.  Replaces KvCache / KvCacheGpu (J/model/KvCache.java:13-105,
+ * J/model/KvCacheGpu.java:12-118): instead of one contiguous fp32 [heads, maxSeq, dhead] buffer
+ * per layer and sequence, fp16 K/V live in fixed blocks of `block_tokens` tokens per layer and
+ * head; a per-sequence block table maps logical block -> physical block.  A "sequence" is one
+ * KvCacheGpu instance of the reference.
+ *
+ * HBM layout: kv[layer][physical block][head][K: block_tokens x dhead | V: block_tokens x dhead]
+ * (fp16).  K is stored after RoPE, V raw (J/model/KvCache.java:8).
+ * ------------------------------------------------------------------------------------------- */
+
+/* KvCacheGpu(numLayers, numHeads, dHead, maxSeqLen) (J/model/KvCacheGpu.java:24-45): rejects
+ * non-positive dimensions with JGPT_ERR_INVALID_ARGUMENT.  dhead in {4,8,16,32}; block_tokens
+ * must be 16.  max_positions bounds the RoPE table (positions 0..max_positions-1). */
+JGPT_API int32_t jgpt_kvpool_create(jgpt_ctx ctx, int32_t layers, int32_t heads, int32_t dhead,
+                                    int32_t block_tokens, int32_t n_blocks, int32_t max_seqs,
+                                    int32_t max_blocks_per_seq, int32_t max_positions, float rope_base,
+                                    jgpt_kvpool *out);
+JGPT_API int32_t jgpt_kvpool_destroy(jgpt_kvpool pool); /* KvCacheGpu.close() */
+JGPT_API int32_t jgpt_kvpool_free_blocks(jgpt_kvpool pool, int32_t *n_free_out);
+/* Device address and byte size of the K/V storage (tests poison / inspect it). */
+JGPT_API int32_t jgpt_kvpool_storage(jgpt_kvpool pool, void **dev_out, uint64_t *bytes_out);
+
+/* Sequence lifecycle: `new KvCacheGpu(..)` / close(); length(), setLength(), clear()
+ * (J/model/KvCacheGpu.java:60-101).  seq ids are small ints (lowest free slot first). */
+JGPT_API int32_t jgpt_seq_alloc(jgpt_kvpool pool, int32_t *seq_out);
+JGPT_API int32_t jgpt_seq_free(jgpt_kvpool pool, int32_t seq);
+/* Make sure blocks exist for token positions [0, n_tokens): all or nothing,
+ * JGPT_ERR_POOL_EXHAUSTED when the free list is too short, JGPT_ERR_INVALID_ARGUMENT when
+ * n_tokens exceeds max_blocks_per_seq*block_tokens. */
+JGPT_API int32_t jgpt_seq_reserve(jgpt_kvpool pool, int32_t seq, int32_t n_tokens);
+JGPT_API int32_t jgpt_seq_length(jgpt_kvpool pool, int32_t seq, int32_t *len_out);
+/* setLength: JGPT_ERR_INVALID_ARGUMENT unless 0 <= len <= reserved capacity. */
+JGPT_API int32_t jgpt_seq_set_length(jgpt_kvpool pool, int32_t seq, int32_t len);
+/* clear(): length 0, blocks returned to the pool and (zero_fill != 0) scrubbed by the eviction kernel. */
+JGPT_API int32_t jgpt_seq_clear(jgpt_kvpool pool, int32_t seq, int32_t zero_fill);
+/* Install an explicit block table (benchmark: seeded permutation of the pool).  The blocks must be free. */
+JGPT_API int32_t jgpt_seq_set_block_table(jgpt_kvpool pool, int32_t seq, const int32_t *blocks_host, int32_t n);
+/* Copy the sequence's block table out (bit-exact checks against the allocator specification). */
+JGPT_API int32_t jgpt_block_table_copy_out(jgpt_kvpool pool, int32_t seq, int32_t *blocks_host, int32_t cap,
+                                           int32_t *n_out);
+/* Same, read back from the DEVICE mirror the kernels use. */
+JGPT_API int32_t jgpt_block_table_copy_out_device(jgpt_kvpool pool, int32_t seq, int32_t *blocks_host,
+                                                  int32_t cap, int32_t *n_out);
+/* LRU eviction: frees whole sequences marked evictable (finished), least recently used first
+ * (ties: lower seq id), until `need_free` blocks are free.  Victim ids are written to
+ * victims_host.  zero_fill != 0 scrubs the freed blocks on the device (eviction kernel). */
+JGPT_API int32_t jgpt_seq_mark_evictable(jgpt_kvpool pool, int32_t seq, int32_t evictable);
+JGPT_API int32_t jgpt_kv_evict_lru(jgpt_kvpool pool, int32_t need_free, int32_t zero_fill, int32_t *victims_host,
+                                   int32_t cap, int32_t *n_victims_out);
+
+/* Append kernel.  Replaces rope_4d_kernel + kv_heads4d_to_cache_kernel
+ * (C/jgpt_cuda_extra_kernels_launches.inl:1127-1159, 1085-1099; TensorOps.copyKvHeadsIntoCache /
+ * copyKvOneTokenIntoCache, J/ops/TensorOps.java:2446-2557).  For token t in [0,n):
+ *   K row = RoPE(k_dev[t], rope_pos[t]) -> fp16 -> block_table[seq_ids[t]][slot_pos[t]/16], slot slot_pos[t]%16
+ *   V row = v_dev[t] -> fp16, same place.
+ * k_dev, v_dev: fp32 [n, heads*dhead]; seq_ids, slot_pos, rope_pos: int32 [n], all device memory. */
+JGPT_API int32_t jgpt_kv_append(jgpt_kvpool pool, int32_t layer, const float *k_dev, const float *v_dev,
+                                const int32_t *seq_ids_dev, const int32_t *slot_pos_dev,
+                                const int32_t *rope_pos_dev, int32_t n);
+
+/* Gather kernel: paged fp16 -> the reference's contiguous fp32 plane [heads, max_seq_len, dhead]
+ * (index h*maxSeq*dhead + pos*dhead + j, J/model/KvCacheGpu.java:7-8), rows >= len zero.
+ * Backs KvCacheGpu.getK/getV (J/model/KvCacheGpu.java:47-58) and TensorOps.sliceKvHeadPrefixFromGpu
+ * (J/ops/TensorOps.java:2333-2339). */
+JGPT_API int32_t jgpt_kv_gather(jgpt_kvpool pool, int32_t layer, int32_t seq, int32_t len, int32_t max_seq_len,
+                                float *k_out_dev, float *v_out_dev);
+
+/* Decode attention.  Replaces the per-head chain of TensorOps.scaledDotProductAttentionQueryOne
+ * (J/ops/TensorOps.java:1088-1140) inside multiHeadAttentionWithRoPEDecode (:2239-2309).
+ * For i in [0,n): RoPE(q[i]) at rope_pos[i]; softmax(scale * q.K^T) over lens[i] cached keys of
+ * sequence seq_ids[i]; out[i] = P.V in the concat-heads layout [n, heads*dhead].
+ * q_dev/out_dev hold `n_layers` slabs of [n, heads*dhead] (slab l uses pool layer layer0+l);
+ * n_layers = 1 inside the model step, > 1 only when the per-layer queries are independent
+ * (the microbenchmark).  max_len is a host-known upper bound of lens[] (sizes the split grid). */
+JGPT_API int32_t jgpt_attn_decode(jgpt_kvpool pool, int32_t layer0, int32_t n_layers, const float *q_dev,
+                                  const int32_t *seq_ids_dev, const int32_t *rope_pos_dev,
+                                  const int32_t *lens_dev, int32_t n, int32_t max_len, float *out_dev);
+
+/* Fused append + decode attention: the whole attention core of one decode step
+ * (J/ops/TensorOps.java:2279-2301).  The new token of sequence i is written at slot lens[i]-1
+ * (lens = cacheLenBefore + 1) with RoPE at rope_pos[i], and attended together with the cached ones. */
+JGPT_API int32_t jgpt_attn_decode_append(jgpt_kvpool pool, int32_t layer0, int32_t n_layers, const float *q_dev,
+                                         const float *k_dev, const float *v_dev, const int32_t *seq_ids_dev,
+                                         const int32_t *rope_pos_dev, const int32_t *lens_dev, int32_t n,
+                                         int32_t max_len, float *out_dev);
+
+/* Host-buffer form of the fused step (what a JNI caller holding float[] uses): copies q,k,v and
+ * the three index arrays to the device, runs jgpt_attn_decode_append, copies out back, synchronises. */
+JGPT_API int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n_layers,
+                                              const float *q_host, const float *k_host, const float *v_host,
+                                              const int32_t *seq_ids_host, const int32_t *rope_pos_host,
+                                              const int32_t *lens_host, int32_t n, float *out_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JGPT_B200_H */

@@ -1,0 +1,579 @@
+// Single-query decode attention over the paged fp16 K/V store, optionally fused with the append
+// of the step's new token.
+//
+// Work item = (layer, sequence, head group, chunk of `chunk_blocks` KV blocks).  A CTA owns a
+// ring of shared-memory stages; one producer warp walks the block table and fetches, per KV
+// block, the contiguous [head group][K tile | V tile] slab with ONE bulk async copy (TMA engine,
+// cp.async.bulk + mbarrier complete_tx).  Consumer threads are (head, token-in-block) pairs: a
+// thread scores its token against q (fp32 FMA), keeps a private online-softmax state
+// (m, l, o[DH]) and, at the end of the chunk, the 16 lanes of a head merge their states with warp
+// shuffles.  Chunks of one sequence are merged by the last CTA to arrive (atomic ticket, no
+// waiting), through a small fp32 scratch buffer.
+//
+// The kernel is HBM-bound (about 1 FLOP per byte at dhead 16): what matters is bytes in flight
+// per SM (stages x slab bytes x resident CTAs) and few, large, 16-byte-aligned transactions.
+#include "common.cuh"
+
+#include <algorithm>
+
+namespace jgpt {
+
+// ------------------------------------------------------------------------------------------
+// PTX helpers: mbarrier + bulk async copy (non-multicast, local global memory only)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kWaitSpins polls (each poll may itself block for a while in
+// hardware), records the failure in the status word and tells the caller to bail out.
+constexpr uint32_t kWaitSpins = 1u << 22;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < kWaitSpins; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;  // somebody else already gave up
+    }
+    atomicOr(status, DEV_STATUS_WAIT_TIMEOUT);
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+struct DecodeParams {
+    __half *kv;
+    const int *table;
+    const float2 *rope;
+    const float *q, *k_new, *v_new;
+    float *out;
+    const int *seq_ids, *rope_pos, *lens;
+    float *partials;
+    int *tickets;
+    int *status;
+    int n, H, HG, n_hg, layer0, n_layers, mbs, n_blocks, max_seqs, max_positions;
+    int chunk_blocks, max_chunks, n_items, stages, max_len;
+    float scale_log2e;
+};
+
+constexpr int kMaxStages = 8;
+
+// Loads one token row of DH halfs from a shared-memory tile into fp32 registers.  For DH = 16
+// (two 16-byte halves per row) the order of the two loads alternates with bit 2 of the token
+// index so the 8 lanes of a quarter-warp hit 8 distinct 16-byte bank groups.
+template <int DH>
+__device__ __forceinline__ void load_row(const unsigned char *tile, int t, float (&r)[DH]) {
+    if constexpr (DH == 16) {
+        const int sw = (t >> 2) & 1;
+        const uint4 a = *reinterpret_cast<const uint4 *>(tile + t * 32 + sw * 16);
+        const uint4 b = *reinterpret_cast<const uint4 *>(tile + t * 32 + (sw ^ 1) * 16);
+        const uint4 lo = sw ? b : a, hi = sw ? a : b;
+        const __half2 *pl = reinterpret_cast<const __half2 *>(&lo), *ph = reinterpret_cast<const __half2 *>(&hi);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 f = __half22float2(pl[i]), g = __half22float2(ph[i]);
+            r[2 * i] = f.x, r[2 * i + 1] = f.y, r[8 + 2 * i] = g.x, r[8 + 2 * i + 1] = g.y;
+        }
+    } else if constexpr (DH >= 8) {
+#pragma unroll
+        for (int c = 0; c < DH / 8; c++) {
+            const uint4 a = *reinterpret_cast<const uint4 *>(tile + t * (DH * 2) + c * 16);
+            const __half2 *pa = reinterpret_cast<const __half2 *>(&a);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(pa[i]);
+                r[c * 8 + 2 * i] = f.x, r[c * 8 + 2 * i + 1] = f.y;
+            }
+        }
+    } else {
+        const uint2 a = *reinterpret_cast<const uint2 *>(tile + t * (DH * 2));
+        const __half2 *pa = reinterpret_cast<const __half2 *>(&a);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const float2 f = __half22float2(pa[i]);
+            r[2 * i] = f.x, r[2 * i + 1] = f.y;
+        }
+    }
+}
+
+// Sum v[0..DH) over the 16 lanes of a half-warp.  On return lane t holds, in v[i], the total of
+// dimension (i*16 + t) for DH >= 16, or in v[0] the total of dimension (t % DH) for DH < 16.
+template <int DH>
+__device__ __forceinline__ void halfwarp_reduce_scatter(float (&v)[DH], int t) {
+    if constexpr (DH >= 16) {
+#pragma unroll
+        for (int g = 0; g < DH / 16; g++) {
+            float a8[8], a4[4], a2[2];
+            const bool b8 = t & 8, b4 = t & 4, b2 = t & 2, b1 = t & 1;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float keep = b8 ? v[g * 16 + 8 + j] : v[g * 16 + j];
+                const float send = b8 ? v[g * 16 + j] : v[g * 16 + 8 + j];
+                a8[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float keep = b4 ? a8[4 + j] : a8[j];
+                const float send = b4 ? a8[j] : a8[4 + j];
+                a4[j] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const float keep = b2 ? a4[2 + j] : a4[j];
+                const float send = b2 ? a4[j] : a4[2 + j];
+                a2[j] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+            }
+            const float keep = b1 ? a2[1] : a2[0];
+            const float send = b1 ? a2[0] : a2[1];
+            v[g] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+        }
+    } else {
+        float mine = 0.f;
+#pragma unroll
+        for (int d = 0; d < DH; d++) {
+            float x = v[d];
+#pragma unroll
+            for (int off = 8; off >= 1; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+            if (d == (t % DH)) mine = x;
+        }
+        v[0] = mine;
+    }
+}
+
+// Head-group cap: slab <= 24 KiB and at most 30 heads (480 consumer threads + the producer warp).
+template <int DH>
+constexpr int max_head_group() { return (384 / DH) < 30 ? (384 / DH) : 30; }
+
+template <int DH, bool FUSED>
+__global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) attn_decode_kernel(const DecodeParams P) {
+    constexpr int BT = kBlockTokens;
+    constexpr int TILE = BT * DH * 2;    // bytes of one K (or V) tile
+    constexpr int HEAD_BYTES = 2 * TILE; // K tile | V tile
+    constexpr int OPL = DH >= 16 ? DH / 16 : 1;  // output dims held per lane after the merge
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
+    __shared__ int s_last;
+    __shared__ int s_abort_mem;
+    volatile int *s_abort = &s_abort_mem;
+
+    const int tid = threadIdx.x;
+    const int n_cons = ((BT * P.HG + 31) / 32) * 32;  // consumer threads (padded to whole warps)
+    const int n_cons_warps = n_cons / 32;
+    const int stage_bytes = P.HG * HEAD_BYTES;
+    const int NS = P.stages;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], (uint32_t)n_cons_warps);
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const bool is_producer = tid >= n_cons;
+    uint32_t it = 0;  // KV blocks processed so far by this CTA (producer and consumers count alike)
+
+    for (int item = blockIdx.x; item < P.n_items; item += gridDim.x) {
+        if (*s_abort) break;  // a bounded wait ran out: stop taking work (status word says why)
+        // item -> (z = layer slab, i = sequence row, hg = head group, c = chunk); chunk is fastest.
+        int r = item;
+        const int c = r % P.max_chunks;
+        r /= P.max_chunks;
+        const int hg = r % P.n_hg;
+        r /= P.n_hg;
+        const int i = r % P.n;
+        const int z = r / P.n;
+        int len = P.lens[i];
+        if (len > P.max_len) {
+            if (tid == 0) atomicOr(P.status, DEV_STATUS_LEN_OVER_BOUND);
+            len = P.max_len;
+        }
+        const int nblk = len > 0 ? (len + BT - 1) / BT : 0;
+        const int nsplit = (nblk + P.chunk_blocks - 1) / P.chunk_blocks;
+        const int b0 = c * P.chunk_blocks;
+        const int b1 = min(b0 + P.chunk_blocks, nblk);
+        const int seq = P.seq_ids[i];
+        const bool seq_ok = seq >= 0 && seq < P.max_seqs;
+        if (!seq_ok && tid == 0) atomicOr(P.status, DEV_STATUS_BAD_SEQ);
+        const size_t row = ((size_t)z * P.n + i) * (size_t)(P.H * DH);  // fp32 row of q / k / v / out
+        const int head0 = hg * P.HG;
+
+        if (b0 >= b1 || !seq_ok) {
+            // Empty chunk.  A sequence without any key (len <= 0) gets a zero output row.
+            if ((nblk == 0 || !seq_ok) && c == 0 && !is_producer)
+                for (int e = tid; e < P.HG * DH; e += n_cons) P.out[row + (size_t)head0 * DH + e] = 0.f;
+            continue;
+        }
+        const int nb = b1 - b0;
+        const size_t layer_base = (size_t)(P.layer0 + z) * P.n_blocks;
+
+        if (is_producer) {
+            // ---------------- producer warp ----------------
+            const int lane = tid & 31;
+            int entry = 0;
+            if (lane < nb) entry = P.table[(size_t)seq * P.mbs + b0 + lane];
+            for (int j = 0; j < nb; j++, it++) {
+                int phys = __shfl_sync(0xffffffffu, entry, j);
+                if (lane == 0) {
+                    if (phys < 0 || phys >= P.n_blocks) {
+                        atomicOr(P.status, DEV_STATUS_BAD_BLOCK);
+                        phys = 0;
+                    }
+                    const int s = it % NS;
+                    const uint32_t round = it / NS;
+                    if (round > 0 && !*s_abort) mbar_wait_bounded(&empty_bar[s], (round - 1) & 1, P.status, s_abort);
+                    if (!*s_abort) {
+                        mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+                        const unsigned char *src = reinterpret_cast<const unsigned char *>(P.kv) +
+                                                   ((layer_base + phys) * P.H + head0) * (size_t)HEAD_BYTES;
+                        bulk_g2s(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s]);
+                    }
+                }
+            }
+            continue;
+        }
+
+        // ---------------- consumers ----------------
+        const int hl = tid / BT, t = tid % BT;
+        const bool active = hl < P.HG;
+        const int h = head0 + (active ? hl : 0);
+        int rp = P.rope_pos[i];
+        if (rp < 0 || rp >= P.max_positions) {
+            if (tid == 0) atomicOr(P.status, DEV_STATUS_BAD_POSITION);
+            rp = 0;
+        }
+        // q row: RoPE at rope_pos, then scaled by (1/sqrt(DH)) * log2(e) so that exp2f can be used.
+        float q[DH];
+        {
+            const float *qp = P.q + row + (size_t)h * DH;
+            const float2 *cs = P.rope + (size_t)rp * (DH / 2);
+#pragma unroll
+            for (int j = 0; j < DH / 2; j++) {
+                const float2 x = *reinterpret_cast<const float2 *>(qp + 2 * j);
+                const float2 w = cs[j];
+                q[2 * j] = __fsub_rn(__fmul_rn(x.x, w.x), __fmul_rn(x.y, w.y)) * P.scale_log2e;
+                q[2 * j + 1] = __fadd_rn(__fmul_rn(x.x, w.y), __fmul_rn(x.y, w.x)) * P.scale_log2e;
+            }
+        }
+        // Fused append: the thread whose token is the new one computes the stored payload (RoPE'd K,
+        // raw V, both rounded to fp16), writes it to the cache and scores it from registers.
+        // Private online-softmax state of this (head, token lane).
+        float m = -INFINITY, l = 0.f, o[DH];
+#pragma unroll
+        for (int d = 0; d < DH; d++) o[d] = 0.f;
+        // Fused append: the new token sits at slot len-1.  The lane that owns that slot computes the
+        // stored payload (RoPE'd K, raw V, both rounded to fp16), writes it to the cache and starts its
+        // softmax state from it; the block loop below then covers the len-1 tokens already cached.
+        const int len_cached = FUSED ? len - 1 : len;
+        if constexpr (FUSED) {
+            const int new_tok = len - 1;
+            if (active && (new_tok / BT >= b0) && (new_tok / BT < b1) && (t == new_tok % BT)) {
+                const float *kp = P.k_new + row + (size_t)h * DH, *vp = P.v_new + row + (size_t)h * DH;
+                const float2 *cs = P.rope + (size_t)rp * (DH / 2);
+                __align__(16) __half kh[DH], vh[DH];
+                float sc = 0.f;
+#pragma unroll
+                for (int j = 0; j < DH / 2; j++) {
+                    const float2 x = *reinterpret_cast<const float2 *>(kp + 2 * j);
+                    const float2 y = *reinterpret_cast<const float2 *>(vp + 2 * j);
+                    const float2 w = cs[j];
+                    kh[2 * j] = __float2half_rn(__fsub_rn(__fmul_rn(x.x, w.x), __fmul_rn(x.y, w.y)));
+                    kh[2 * j + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x.x, w.y), __fmul_rn(x.y, w.x)));
+                    vh[2 * j] = __float2half_rn(y.x);
+                    vh[2 * j + 1] = __float2half_rn(y.y);
+                    sc = fmaf(q[2 * j], __half2float(kh[2 * j]), sc);
+                    sc = fmaf(q[2 * j + 1], __half2float(kh[2 * j + 1]), sc);
+                    o[2 * j] = __half2float(vh[2 * j]);
+                    o[2 * j + 1] = __half2float(vh[2 * j + 1]);
+                }
+                m = sc, l = 1.f;
+                const int phys = P.table[(size_t)seq * P.mbs + new_tok / BT];
+                if (phys < 0 || phys >= P.n_blocks) {
+                    atomicOr(P.status, DEV_STATUS_BAD_BLOCK);
+                } else {
+                    __half *dst = P.kv + ((layer_base + phys) * P.H + h) * (size_t)(2 * BT * DH) + (size_t)t * DH;
+                    if constexpr (DH >= 8) {
+#pragma unroll
+                        for (int cc = 0; cc < DH / 8; cc++) {
+                            reinterpret_cast<uint4 *>(dst)[cc] = reinterpret_cast<const uint4 *>(kh)[cc];
+                            reinterpret_cast<uint4 *>(dst + BT * DH)[cc] = reinterpret_cast<const uint4 *>(vh)[cc];
+                        }
+                    } else {
+                        *reinterpret_cast<uint2 *>(dst) = *reinterpret_cast<const uint2 *>(kh);
+                        *reinterpret_cast<uint2 *>(dst + BT * DH) = *reinterpret_cast<const uint2 *>(vh);
+                    }
+                }
+            }
+        }
+
+        bool aborted = false;
+        for (int j = 0; j < nb; j++, it++) {
+            const int s = it % NS;
+            const uint32_t round = it / NS;
+            if (!aborted && !mbar_wait_bounded(&full_bar[s], round & 1, P.status, s_abort)) aborted = true;
+            if (aborted) continue;  // keep counting blocks, touch nothing
+            const int tok = (b0 + j) * BT + t;
+            if (active && tok < len_cached) {
+                const unsigned char *ktile = smem + (size_t)s * stage_bytes + (size_t)hl * HEAD_BYTES;
+                float kr[DH], vr[DH];
+                load_row<DH>(ktile, t, kr);
+                float sc = 0.f;
+#pragma unroll
+                for (int d = 0; d < DH; d++) sc = fmaf(q[d], kr[d], sc);
+                if (sc > m) {  // new running maximum: rescale the private state
+                    const float corr = exp2f(m - sc);  // m = -inf on the first token -> 0
+                    l *= corr;
+#pragma unroll
+                    for (int d = 0; d < DH; d++) o[d] *= corr;
+                    m = sc;
+                }
+                load_row<DH>(ktile + TILE, t, vr);
+                const float pexp = exp2f(sc - m);
+                l += pexp;
+#pragma unroll
+                for (int d = 0; d < DH; d++) o[d] = fmaf(pexp, vr[d], o[d]);
+            }
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&empty_bar[s]);
+        }
+        // After a timed-out wait the thread keeps walking the barriers below (so nobody is left
+        // waiting for it) but stores nothing; the item loop ends at its next iteration.
+
+        // ---- merge the 16 token lanes of each head (warp shuffles) ----
+        float M = m;
+#pragma unroll
+        for (int off = 8; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        const float f = (m == -INFINITY) ? 0.f : exp2f(m - M);
+        l *= f;
+#pragma unroll
+        for (int d = 0; d < DH; d++) o[d] *= f;
+#pragma unroll
+        for (int off = 8; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+        halfwarp_reduce_scatter<DH>(o, t);
+        // lane t now holds dims {g*16 + t} (DH >= 16) or dim t % DH (DH < 16) in o[0..OPL)
+        const bool writer = active && !aborted && (DH >= 16 || t < DH);
+
+        if (nsplit == 1) {
+            if (writer) {
+                const float inv = 1.f / fmaxf(l, 1e-12f);
+#pragma unroll
+                for (int g = 0; g < OPL; g++) P.out[row + (size_t)h * DH + g * 16 + (DH >= 16 ? t : t % DH)] = o[g] * inv;
+            }
+            continue;
+        }
+
+        // ---- split-K: publish the partial, last CTA of the sequence row merges ----
+        constexpr int PSTRIDE = DH + 2;
+        const size_t prow = (((size_t)z * P.n + i) * P.max_chunks) * (size_t)P.H;  // + c*H + head
+        if (writer) {
+            float *pp = P.partials + (prow + (size_t)c * P.H + h) * PSTRIDE;
+#pragma unroll
+            for (int g = 0; g < OPL; g++) pp[2 + g * 16 + (DH >= 16 ? t : t % DH)] = o[g];
+            if (t == 0) pp[0] = M, pp[1] = l;
+        }
+        __threadfence();
+        named_bar_sync(1, n_cons);
+        int *ticket = P.tickets + ((size_t)z * P.n + i) * P.n_hg + hg;
+        if (tid == 0) {
+            const int prev = atomicAdd(ticket, 1);
+            s_last = (prev == nsplit - 1);
+            if (prev == nsplit - 1) *ticket = 0;  // self-reset for the next launch
+        }
+        named_bar_sync(1, n_cons);
+        if (s_last) {
+            __threadfence();
+            if (writer) {
+                float Mx = -INFINITY;
+                for (int cc = 0; cc < nsplit; cc++)
+                    Mx = fmaxf(Mx, __ldcg(P.partials + (prow + (size_t)cc * P.H + h) * PSTRIDE));
+                float L = 0.f, acc[OPL];
+#pragma unroll
+                for (int g = 0; g < OPL; g++) acc[g] = 0.f;
+                for (int cc = 0; cc < nsplit; cc++) {
+                    const float *pp = P.partials + (prow + (size_t)cc * P.H + h) * PSTRIDE;
+                    const float w = exp2f(__ldcg(pp) - Mx);
+                    L = fmaf(__ldcg(pp + 1), w, L);
+#pragma unroll
+                    for (int g = 0; g < OPL; g++) acc[g] = fmaf(__ldcg(pp + 2 + g * 16 + (DH >= 16 ? t : t % DH)), w, acc[g]);
+                }
+                const float inv = 1.f / fmaxf(L, 1e-12f);
+#pragma unroll
+                for (int g = 0; g < OPL; g++) P.out[row + (size_t)h * DH + g * 16 + (DH >= 16 ? t : t % DH)] = acc[g] * inv;
+            }
+        }
+    }
+    // Abort path only: before the CTA (and its shared memory) goes away, give the bulk copies that
+    // were already issued a bounded chance to land.
+    __syncthreads();
+    if (*s_abort && tid == n_cons) {
+        const uint32_t first = it > (uint32_t)NS ? it - NS : 0;
+        for (uint32_t idx = first; idx < it; idx++)
+            for (uint32_t spin = 0; spin < (1u << 16); spin++)
+                if (mbar_try_wait(&full_bar[idx % NS], (idx / NS) & 1)) break;
+    }
+}
+
+// Largest divisor of H whose slab (HG * 64 * DH bytes) stays within 24 KiB and 480 consumer threads.
+static int pick_head_group(int H, int DH, int forced) {
+    const int cap = std::min(30, std::max(1, 384 / DH));  // == max_head_group<DH>()
+    if (forced > 0 && forced <= cap && H % forced == 0) return forced;
+    int best = 1;
+    for (int g = 1; g <= std::min(H, cap); g++)
+        if (H % g == 0) best = g;
+    return best;
+}
+
+template <int DH>
+static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int threads, size_t smem, int grid) {
+    auto kern = fused ? attn_decode_kernel<DH, true> : attn_decode_kernel<DH, false>;
+    JGPT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, threads, smem, p->ctx->stream>>>(P);
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
+int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, const float *k_new, const float *v_new,
+                           const int *seq_ids, const int *rope_pos, const int *lens, int n, int max_len, float *out) {
+    DecodeParams P;
+    memset(&P, 0, sizeof(P));
+    const int DH = p->dhead;
+    P.kv = p->kv, P.table = p->d_table, P.rope = p->d_rope;
+    P.q = q, P.k_new = k_new, P.v_new = v_new, P.out = out;
+    P.seq_ids = seq_ids, P.rope_pos = rope_pos, P.lens = lens;
+    P.status = p->ctx->d_status;
+    P.n = n, P.H = p->heads, P.layer0 = layer0, P.n_layers = n_layers, P.mbs = p->max_blocks_per_seq;
+    P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
+    P.HG = pick_head_group(p->heads, DH, p->head_group);
+    P.n_hg = p->heads / P.HG;
+    P.chunk_blocks = p->chunk_blocks;
+    const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
+    P.max_len = max_blocks * kBlockTokens;
+    P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
+    P.stages = p->stages;
+    P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
+    const long long items = (long long)n_layers * n * P.n_hg * P.max_chunks;
+    JGPT_REQUIRE(items < (1ll << 31), JGPT_ERR_INVALID_ARGUMENT, "too many work items (%lld)", items);
+    P.n_items = (int)items;
+    if (P.max_chunks > 1) {
+        int32_t rc = pool_ensure_split_scratch(p, (uint64_t)n_layers * n * P.max_chunks * p->heads * (DH + 2),
+                                               (uint64_t)n_layers * n * P.n_hg);
+        if (rc) return rc;
+    }
+    P.partials = p->d_partials, P.tickets = p->d_tickets;
+    const int n_cons = ((kBlockTokens * P.HG + 31) / 32) * 32;
+    const int threads = n_cons + 32;
+    const size_t stage_bytes = (size_t)P.HG * 2 * kBlockTokens * DH * 2;
+    const size_t smem = stage_bytes * P.stages;
+    int grid = P.n_items;
+    if (p->persistent > 0) grid = std::min(P.n_items, p->ctx->sm_count * p->persistent);
+    const bool fused = k_new != nullptr;
+    switch (DH) {
+        case 4: return launch_decode_t<4>(p, P, fused, threads, smem, grid);
+        case 8: return launch_decode_t<8>(p, P, fused, threads, smem, grid);
+        case 16: return launch_decode_t<16>(p, P, fused, threads, smem, grid);
+        case 32: return launch_decode_t<32>(p, P, fused, threads, smem, grid);
+        default: return fail(JGPT_ERR_UNSUPPORTED, "dhead %d not supported", DH);
+    }
+}
+
+}  // namespace jgpt
+
+using namespace jgpt;
+
+static int32_t decode_common(jgpt_kvpool h, int32_t layer0, int32_t n_layers, const float *q, const float *k, const float *v,
+                             const int32_t *seq_ids, const int32_t *rope_pos, const int32_t *lens, int32_t n, int32_t max_len,
+                             float *out, bool fused) {
+    Pool *p = pool_registry().get(h);
+    JGPT_REQUIRE(p, JGPT_ERR_BAD_HANDLE, "bad kvpool handle");
+    JGPT_CUDA_TRY(make_current(p->ctx));
+    JGPT_REQUIRE(n_layers >= 1 && layer0 >= 0 && layer0 + n_layers <= p->layers, JGPT_ERR_OUT_OF_RANGE,
+                 "layers [%d, %d) outside [0,%d)", layer0, layer0 + n_layers, p->layers);
+    if (n == 0) return JGPT_OK;
+    JGPT_REQUIRE(n > 0 && q && seq_ids && rope_pos && lens && out && (!fused || (k && v)), JGPT_ERR_INVALID_ARGUMENT,
+                 "null pointer or negative count");
+    JGPT_REQUIRE(max_len >= 1, JGPT_ERR_INVALID_ARGUMENT, "max_len must be >= 1");
+    return launch_attn_decode(p, layer0, n_layers, q, fused ? k : nullptr, fused ? v : nullptr, seq_ids, rope_pos, lens, n,
+                              max_len, out);
+}
+
+extern "C" {
+
+int32_t jgpt_attn_decode(jgpt_kvpool pool, int32_t layer0, int32_t n_layers, const float *q_dev, const int32_t *seq_ids_dev,
+                         const int32_t *rope_pos_dev, const int32_t *lens_dev, int32_t n, int32_t max_len, float *out_dev) {
+    return decode_common(pool, layer0, n_layers, q_dev, nullptr, nullptr, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len,
+                         out_dev, false);
+}
+
+int32_t jgpt_attn_decode_append(jgpt_kvpool pool, int32_t layer0, int32_t n_layers, const float *q_dev, const float *k_dev,
+                                const float *v_dev, const int32_t *seq_ids_dev, const int32_t *rope_pos_dev,
+                                const int32_t *lens_dev, int32_t n, int32_t max_len, float *out_dev) {
+    return decode_common(pool, layer0, n_layers, q_dev, k_dev, v_dev, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len,
+                         out_dev, true);
+}
+
+int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n_layers, const float *q_host,
+                                     const float *k_host, const float *v_host, const int32_t *seq_ids_host,
+                                     const int32_t *rope_pos_host, const int32_t *lens_host, int32_t n, float *out_host) {
+    Pool *p = pool_registry().get(pool);
+    JGPT_REQUIRE(p, JGPT_ERR_BAD_HANDLE, "bad kvpool handle");
+    JGPT_CUDA_TRY(make_current(p->ctx));
+    if (n == 0) return JGPT_OK;
+    JGPT_REQUIRE(n > 0 && n_layers >= 1 && q_host && k_host && v_host && seq_ids_host && rope_pos_host && lens_host && out_host,
+                 JGPT_ERR_INVALID_ARGUMENT, "null pointer or bad count");
+    const size_t slab = (size_t)n_layers * n * p->heads * p->dhead;
+    int32_t rc = pool_ensure_staging(p, 4 * slab, 3 * (size_t)n);
+    if (rc) return rc;
+    int max_len = 1;
+    for (int i = 0; i < n; i++) {
+        JGPT_REQUIRE(seq_ids_host[i] >= 0 && seq_ids_host[i] < p->max_seqs && p->seqs[(size_t)seq_ids_host[i]].used,
+                     JGPT_ERR_OUT_OF_RANGE, "seq_ids[%d] = %d is not an allocated sequence", i, seq_ids_host[i]);
+        JGPT_REQUIRE(lens_host[i] >= 1 && lens_host[i] <= (int)p->seqs[(size_t)seq_ids_host[i]].blocks.size() * kBlockTokens,
+                     JGPT_ERR_ILLEGAL_STATE, "lens[%d] = %d is beyond the blocks reserved for sequence %d", i, lens_host[i],
+                     seq_ids_host[i]);
+        JGPT_REQUIRE(rope_pos_host[i] >= 0 && rope_pos_host[i] < p->max_positions, JGPT_ERR_INVALID_ARGUMENT,
+                     "rope_pos[%d] = %d outside [0,%d)", i, rope_pos_host[i], p->max_positions);
+        max_len = std::max(max_len, lens_host[i]);
+    }
+    cudaStream_t st = p->ctx->stream;
+    float *dq = p->d_stage_f, *dk = dq + slab, *dv = dk + slab, *dout = dv + slab;
+    int *dseq = p->d_stage_i, *drp = dseq + n, *dlen = drp + n;
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dq, q_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dk, k_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dv, v_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dlen, lens_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+    rc = launch_attn_decode(p, layer0, n_layers, dq, dk, dv, dseq, drp, dlen, n, max_len, dout);
+    if (rc) return rc;
+    JGPT_CUDA_TRY(cudaMemcpyAsync(out_host, dout, sizeof(float) * slab, cudaMemcpyDeviceToHost, st));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+    return JGPT_OK;
+}
+
+}  // extern "C"

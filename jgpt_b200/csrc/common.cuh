@@ -1,0 +1,151 @@
+// Shared internals of libjgpt_b200: handles, error reporting, context and pool objects.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/jgpt_b200.h"
+
+namespace jgpt {
+
+// ------------------------------------------------------------------------------------------
+// Errors.  Native reference code prints to stderr and returns with stale outputs
+// (src/main/cpp/jgpt_cuda_error_macros.cuh:9-36); here every call returns a status and keeps a
+// thread-local message.
+// ------------------------------------------------------------------------------------------
+std::string &last_error_ref();
+int32_t fail(int32_t code, const char *fmt, ...);
+
+#define JGPT_CUDA_TRY(expr)                                                                           \
+    do {                                                                                              \
+        cudaError_t _e = (expr);                                                                      \
+        if (_e != cudaSuccess)                                                                        \
+            return ::jgpt::fail(_e == cudaErrorMemoryAllocation ? JGPT_ERR_OUT_OF_MEMORY : JGPT_ERR_CUDA, \
+                                "%s: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+#define JGPT_REQUIRE(cond, code, ...)                     \
+    do {                                                  \
+        if (!(cond)) return ::jgpt::fail(code, __VA_ARGS__); \
+    } while (0)
+
+// Bits of the device status word (Ctx::d_status).  Kernels never trap; they record and carry on.
+enum : int {
+    DEV_STATUS_BAD_BLOCK = 1,     // block-table entry outside [0, n_blocks)
+    DEV_STATUS_BAD_POSITION = 2,  // slot / RoPE position outside the pool's range
+    DEV_STATUS_BAD_SEQ = 4,       // sequence id outside [0, max_seqs)
+    DEV_STATUS_WAIT_TIMEOUT = 8,  // a bounded mbarrier wait ran out
+    DEV_STATUS_LEN_OVER_BOUND = 16  // lens[i] above the host-declared max_len
+};
+
+struct Ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int *d_status = nullptr;  // device status word
+    int *h_status = nullptr;  // pinned mirror
+    int sm_count = 0;
+};
+
+struct SeqState {
+    bool used = false;
+    bool evictable = false;
+    int len = 0;
+    uint64_t tick = 0;
+    std::vector<int> blocks;
+};
+
+constexpr int kBlockTokens = 16;
+
+struct Pool {
+    Ctx *ctx = nullptr;
+    int layers = 0, heads = 0, dhead = 0, n_blocks = 0, max_seqs = 0, max_blocks_per_seq = 0, max_positions = 0;
+    float rope_base = 10000.f;
+    // device
+    __half *kv = nullptr;      // [layers][n_blocks][heads][2][16][dhead]
+    uint64_t kv_bytes = 0;
+    int *d_table = nullptr;    // [max_seqs][max_blocks_per_seq], -1 = unmapped
+    float2 *d_rope = nullptr;  // [max_positions][dhead/2] (cos, sin)
+    float *d_partials = nullptr;  // split-K scratch
+    uint64_t partials_floats = 0;
+    int *d_tickets = nullptr;     // split-K arrival counters (self-resetting)
+    uint64_t n_tickets = 0;
+    int *d_evict_list = nullptr;  // freed block ids for the scrub kernel
+    int evict_cap = 0;
+    // staging for the host-buffer entry points (grow-only)
+    float *d_stage_f = nullptr;
+    uint64_t stage_f_floats = 0;
+    int *d_stage_i = nullptr;
+    uint64_t stage_i_ints = 0;
+    float *h_stage_f = nullptr;  // pinned
+    uint64_t h_stage_f_floats = 0;
+    int *h_stage_i = nullptr;    // pinned
+    uint64_t h_stage_i_ints = 0;
+    // host allocator state (authoritative)
+    std::vector<int> free_list;  // LIFO: back() is handed out next
+    std::vector<SeqState> seqs;
+    uint64_t clock = 0;
+    // launch tuning (read once from the environment at creation)
+    int chunk_blocks = 8;
+    int stages = 4;
+    int persistent = 0;
+    int head_group = 0;  // 0 = automatic
+};
+
+struct Model;
+
+// Handle registry: a handle is the object's address, valid only while registered.
+template <class T>
+struct Registry {
+    std::mutex mu;
+    std::unordered_set<T *> live;
+    uint64_t add(T *p) {
+        std::lock_guard<std::mutex> g(mu);
+        live.insert(p);
+        return reinterpret_cast<uint64_t>(p);
+    }
+    T *get(uint64_t h) {
+        std::lock_guard<std::mutex> g(mu);
+        T *p = reinterpret_cast<T *>(h);
+        return live.count(p) ? p : nullptr;
+    }
+    bool remove(T *p) {
+        std::lock_guard<std::mutex> g(mu);
+        return live.erase(p) != 0;
+    }
+};
+Registry<Ctx> &ctx_registry();
+Registry<Pool> &pool_registry();
+
+// Makes the context's device current for the calling thread.
+inline cudaError_t make_current(const Ctx *c) { return cudaSetDevice(c->device); }
+
+int env_int(const char *name, int dflt);
+
+// Grow-only staging helpers (never called on the steady-state decode path once sized).
+int32_t pool_ensure_staging(Pool *p, uint64_t n_floats, uint64_t n_ints);
+int32_t pool_ensure_split_scratch(Pool *p, uint64_t partial_floats, uint64_t tickets);
+// Push rows of the host block table to the device mirror.
+int32_t pool_upload_table_row(Pool *p, int seq);
+
+// Kernel launchers (defined in the .cu files)
+int32_t launch_kv_append(Pool *p, int layer, const float *k, const float *v, const int *seq_ids,
+                         const int *slot_pos, const int *rope_pos, int n);
+int32_t launch_kv_gather(Pool *p, int layer, int seq, int len, int max_seq_len, float *k_out, float *v_out);
+int32_t launch_kv_scrub(Pool *p, const std::vector<int> &blocks);
+int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, const float *k_new,
+                           const float *v_new, const int *seq_ids, const int *rope_pos, const int *lens, int n,
+                           int max_len, float *out);
+int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v,
+                            const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
+                            int n_seqs, float *out);
+
+}  // namespace jgpt

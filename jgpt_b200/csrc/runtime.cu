@@ -1,0 +1,234 @@
+// Context, stream, device buffers, events, error reporting.
+#include "common.cuh"
+
+#include <cstdlib>
+
+namespace jgpt {
+
+std::string &last_error_ref() {
+    static thread_local std::string s;
+    return s;
+}
+
+int32_t fail(int32_t code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error_ref() = buf;
+    return code;
+}
+
+Registry<Ctx> &ctx_registry() {
+    static Registry<Ctx> r;
+    return r;
+}
+Registry<Pool> &pool_registry() {
+    static Registry<Pool> r;
+    return r;
+}
+
+int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    if (!v || !*v) return dflt;
+    char *end = nullptr;
+    long x = strtol(v, &end, 10);
+    return (end && *end == 0) ? (int)x : dflt;
+}
+
+}  // namespace jgpt
+
+using namespace jgpt;
+
+extern "C" {
+
+const char *jgpt_last_error(void) { return last_error_ref().c_str(); }
+
+int32_t jgpt_device_count(int32_t *out) {
+    JGPT_REQUIRE(out, JGPT_ERR_INVALID_ARGUMENT, "out is null");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    *out = n;
+    return JGPT_OK;
+}
+
+int32_t jgpt_ctx_create(int32_t device, jgpt_ctx *out) {
+    JGPT_REQUIRE(out, JGPT_ERR_INVALID_ARGUMENT, "out is null");
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        // The reference throws IllegalStateException from requireCuda when no GPU is usable.
+        return fail(JGPT_ERR_ILLEGAL_STATE, "no CUDA device available (%s); this library has no CPU fallback",
+                    e != cudaSuccess ? cudaGetErrorString(e) : "device count 0");
+    }
+    JGPT_REQUIRE(device >= 0 && device < n, JGPT_ERR_INVALID_ARGUMENT, "device %d outside [0,%d)", device, n);
+    JGPT_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    JGPT_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    JGPT_REQUIRE(prop.major >= 10, JGPT_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                 device, prop.major, prop.minor);
+    Ctx *c = new Ctx();
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    JGPT_CUDA_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    JGPT_CUDA_TRY(cudaMalloc(&c->d_status, sizeof(int)));
+    JGPT_CUDA_TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream));
+    JGPT_CUDA_TRY(cudaHostAlloc(&c->h_status, sizeof(int), cudaHostAllocDefault));
+    *c->h_status = 0;
+    JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    *out = ctx_registry().add(c);
+    return JGPT_OK;
+}
+
+int32_t jgpt_ctx_destroy(jgpt_ctx h) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    make_current(c);
+    cudaStreamSynchronize(c->stream);
+    ctx_registry().remove(c);
+    cudaFree(c->d_status);
+    cudaFreeHost(c->h_status);
+    cudaStreamDestroy(c->stream);
+    delete c;
+    return JGPT_OK;
+}
+
+int32_t jgpt_sync(jgpt_ctx h) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    if (*c->h_status != 0) {
+        const int st = *c->h_status;
+        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+        return fail(JGPT_ERR_DEVICE_CHECK,
+                    "device self-check failed: status=0x%x%s%s%s%s%s", st, (st & DEV_STATUS_BAD_BLOCK) ? " bad-block-id" : "",
+                    (st & DEV_STATUS_BAD_POSITION) ? " bad-position" : "", (st & DEV_STATUS_BAD_SEQ) ? " bad-seq-id" : "",
+                    (st & DEV_STATUS_WAIT_TIMEOUT) ? " wait-timeout" : "",
+                    (st & DEV_STATUS_LEN_OVER_BOUND) ? " len-over-bound" : "");
+    }
+    return JGPT_OK;
+}
+
+int32_t jgpt_ctx_stream(jgpt_ctx h, void **stream_out) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(stream_out, JGPT_ERR_INVALID_ARGUMENT, "stream_out is null");
+    *stream_out = (void *)c->stream;
+    return JGPT_OK;
+}
+
+int32_t jgpt_dev_alloc(jgpt_ctx h, uint64_t bytes, void **dev_out) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(dev_out && bytes > 0, JGPT_ERR_INVALID_ARGUMENT, "bytes must be > 0");
+    JGPT_CUDA_TRY(make_current(c));
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(JGPT_ERR_OUT_OF_MEMORY, "cudaMalloc(%llu) failed: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+    }
+    *dev_out = p;
+    return JGPT_OK;
+}
+
+int32_t jgpt_dev_free(jgpt_ctx h, void *dev) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    if (!dev) return JGPT_OK;
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    JGPT_CUDA_TRY(cudaFree(dev));
+    return JGPT_OK;
+}
+
+int32_t jgpt_h2d(jgpt_ctx h, void *dev_dst, const void *host_src, uint64_t bytes) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    if (bytes == 0) return JGPT_OK;
+    JGPT_REQUIRE(dev_dst && host_src, JGPT_ERR_INVALID_ARGUMENT, "null pointer");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, c->stream));
+    // Pageable sources are staged by the runtime before the call returns; pinned ones are not,
+    // so the caller's buffer must stay untouched until the stream passes this point.
+    return JGPT_OK;
+}
+
+int32_t jgpt_d2h(jgpt_ctx h, void *host_dst, const void *dev_src, uint64_t bytes) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    if (bytes == 0) return JGPT_OK;
+    JGPT_REQUIRE(host_dst && dev_src, JGPT_ERR_INVALID_ARGUMENT, "null pointer");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, c->stream));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return JGPT_OK;
+}
+
+int32_t jgpt_dev_memset(jgpt_ctx h, void *dev, int32_t byte_value, uint64_t bytes) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    if (bytes == 0) return JGPT_OK;
+    JGPT_REQUIRE(dev, JGPT_ERR_INVALID_ARGUMENT, "null pointer");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaMemsetAsync(dev, byte_value, bytes, c->stream));
+    return JGPT_OK;
+}
+
+int32_t jgpt_host_alloc_pinned(uint64_t bytes, void **host_out) {
+    JGPT_REQUIRE(host_out && bytes > 0, JGPT_ERR_INVALID_ARGUMENT, "bytes must be > 0");
+    void *p = nullptr;
+    cudaError_t e = cudaHostAlloc(&p, bytes, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(JGPT_ERR_OUT_OF_MEMORY, "cudaHostAlloc(%llu) failed: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+    }
+    *host_out = p;
+    return JGPT_OK;
+}
+
+int32_t jgpt_host_free_pinned(void *host) {
+    if (!host) return JGPT_OK;
+    JGPT_CUDA_TRY(cudaFreeHost(host));
+    return JGPT_OK;
+}
+
+int32_t jgpt_event_create(uint64_t *event_out) {
+    JGPT_REQUIRE(event_out, JGPT_ERR_INVALID_ARGUMENT, "event_out is null");
+    cudaEvent_t e;
+    JGPT_CUDA_TRY(cudaEventCreate(&e));
+    *event_out = reinterpret_cast<uint64_t>(e);
+    return JGPT_OK;
+}
+
+int32_t jgpt_event_destroy(uint64_t event) {
+    if (!event) return JGPT_OK;
+    JGPT_CUDA_TRY(cudaEventDestroy(reinterpret_cast<cudaEvent_t>(event)));
+    return JGPT_OK;
+}
+
+int32_t jgpt_event_record(jgpt_ctx h, uint64_t event) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(event, JGPT_ERR_INVALID_ARGUMENT, "null event");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaEventRecord(reinterpret_cast<cudaEvent_t>(event), c->stream));
+    return JGPT_OK;
+}
+
+int32_t jgpt_event_elapsed_ms(uint64_t start, uint64_t stop, float *ms_out) {
+    JGPT_REQUIRE(start && stop && ms_out, JGPT_ERR_INVALID_ARGUMENT, "null argument");
+    JGPT_CUDA_TRY(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(stop)));
+    JGPT_CUDA_TRY(cudaEventElapsedTime(ms_out, reinterpret_cast<cudaEvent_t>(start), reinterpret_cast<cudaEvent_t>(stop)));
+    return JGPT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+"""Context (one GPU + one stream) and device buffers.
+
+Mirrors, on the reference side, ``TensorOpsGPU`` initialisation / ``synchronizeStream`` and
+``GpuFloatBuffer`` / ``GpuIntBuffer`` (src/main/java/com/veles/llm/jgpt/GpuFloatBuffer.java).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import binding as B
+
+
+class Context:
+    """One GPU and its stream.  The reference has one process-global stream on device 0."""
+
+    def __init__(self, device: int = 0):
+        self._lib = B.load()
+        h = C.c_uint64()
+        B.check(self._lib.jgpt_ctx_create(device, C.byref(h)))
+        self.handle = h.value
+        self.device = device
+
+    def synchronize(self):
+        """``TensorOpsGPU.synchronizeStream``; raises if a kernel recorded a failed self-check."""
+        B.check(self._lib.jgpt_sync(self.handle))
+
+    @property
+    def stream(self) -> int:
+        p = C.c_void_p()
+        B.check(self._lib.jgpt_ctx_stream(self.handle, C.byref(p)))
+        return p.value or 0
+
+    def alloc(self, shape, dtype=np.float32) -> "DeviceBuffer":
+        return DeviceBuffer(self, shape, dtype)
+
+    def from_host(self, arr) -> "DeviceBuffer":
+        arr = np.ascontiguousarray(arr)
+        buf = DeviceBuffer(self, arr.shape, arr.dtype)
+        buf.copy_from(arr)
+        return buf
+
+    def close(self):
+        if self.handle:
+            self._lib.jgpt_ctx_destroy(self.handle)
+            self.handle = 0
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+
+class Event:
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+        h = C.c_uint64()
+        B.check(ctx._lib.jgpt_event_create(C.byref(h)))
+        self.handle = h.value
+
+    def record(self):
+        B.check(self.ctx._lib.jgpt_event_record(self.ctx.handle, self.handle))
+
+    def elapsed_ms(self, later: "Event") -> float:
+        ms = C.c_float()
+        B.check(self.ctx._lib.jgpt_event_elapsed_ms(self.handle, later.handle, C.byref(ms)))
+        return ms.value
+
+    def __del__(self):
+        try:
+            if self.handle:
+                self.ctx._lib.jgpt_event_destroy(self.handle)
+        except Exception:
+            pass
+
+
+class DeviceBuffer:
+    """Typed device allocation (``GpuFloatBuffer.allocate`` / ``copyFrom`` / ``copyTo`` / ``clear``)."""
+
+    def __init__(self, ctx: Context, shape, dtype=np.float32):
+        self.ctx = ctx
+        self.shape = tuple(int(s) for s in (shape if hasattr(shape, "__len__") else (shape,)))
+        self.dtype = np.dtype(dtype)
+        self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
+        p = C.c_void_p()
+        B.check(ctx._lib.jgpt_dev_alloc(ctx.handle, max(self.nbytes, 1), C.byref(p)))
+        self.ptr = p.value
+
+    def copy_from(self, arr):
+        arr = np.ascontiguousarray(arr, dtype=self.dtype)
+        if arr.nbytes != self.nbytes:
+            raise ValueError(f"size mismatch: {arr.nbytes} != {self.nbytes}")
+        B.check(self.ctx._lib.jgpt_h2d(self.ctx.handle, self.ptr, arr.ctypes.data, arr.nbytes))
+        return self
+
+    def to_host(self) -> np.ndarray:
+        out = np.empty(self.shape, self.dtype)
+        B.check(self.ctx._lib.jgpt_d2h(self.ctx.handle, out.ctypes.data, self.ptr, self.nbytes))
+        return out
+
+    def fill_bytes(self, value: int):
+        B.check(self.ctx._lib.jgpt_dev_memset(self.ctx.handle, self.ptr, value, self.nbytes))
+        return self
+
+    def close(self):
+        if self.ptr:
+            self.ctx._lib.jgpt_dev_free(self.ctx.handle, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            if self.ptr and self.ctx.handle:
+                self.close()
+        except Exception:
+            pass

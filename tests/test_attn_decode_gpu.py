@@ -1,0 +1,166 @@
+"""GPU parity of single-query decode attention (plain and fused with the append) against the CPU
+oracle, through the C ABI.  The oracle attends over the same fp16-rounded payload the paged store
+holds, so the comparison isolates the kernel: tolerance 2e-5 max-abs on outputs of magnitude ~1
+(fp32 accumulation order and exp2f vs expf).  The end-to-end logits budget is 2e-3."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle as O
+from helpers import PagedCase
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-5
+
+
+def _oracle_decode(case, layer, q, lens, rope_pos):
+    """Attention only (no append): run the oracle's append+attend on a copy with the cached last token as 'new'."""
+    n, H, Dh = case.n, case.H, case.Dh
+    out = np.zeros((n, H * Dh), np.float32)
+    scale = 1.0 / np.sqrt(Dh)
+    qh = O.split_heads(q.reshape(n, 1, H * Dh), H)  # [n,H,1,Dh]
+    for i in range(n):
+        L = int(lens[i])
+        if L == 0:
+            continue
+        qr = O.rope_4d(qh[i:i + 1], positions=np.array([rope_pos[i]], np.int32))[0, :, 0]
+        for h in range(H):
+            out[i, h * Dh:(h + 1) * Dh] = O.attn_query_one(qr[h], case.kc[layer, i, h, :L], case.vc[layer, i, h, :L], scale)
+    return out
+
+
+@pytest.mark.parametrize("Dh,H", [(16, 24), (16, 5), (8, 4), (4, 2), (32, 6)])
+def test_decode_attention_matches_oracle_ragged(ctx, Dh, H):
+    lens = [1, 15, 16, 17, 33, 130, 257, 0]
+    case = PagedCase(ctx, lens, H=H, Dh=Dh, layers=2, seed=11)
+    try:
+        rng = np.random.default_rng(5)
+        n = case.n
+        rope_pos = np.array([max(l - 1, 0) for l in lens], np.int32)
+        for layer in range(2):
+            q = rng.standard_normal((n, H * Dh)).astype(np.float32)
+            out = ctx.alloc((n, H * Dh))
+            out.fill_bytes(0x7F)
+            case.pool.attn_decode(layer, 1, ctx.from_host(q), case.seq_ids_dev(), ctx.from_host(rope_pos),
+                                  ctx.from_host(case.lens), n, int(max(lens)), out)
+            ctx.synchronize()
+            got = out.to_host()
+            want = _oracle_decode(case, layer, q, lens, rope_pos)
+            assert np.abs(got - want).max() < TOL, (Dh, H, layer, np.abs(got - want).max())
+            assert not got[-1].any()  # empty sequence -> zero row
+    finally:
+        case.close()
+
+
+@pytest.mark.parametrize("chunk_blocks,stages,persistent", [(1, 2, 0), (4, 3, 0), (8, 4, 1), (32, 8, 2)])
+def test_split_and_pipeline_settings_agree(ctx, chunk_blocks, stages, persistent):
+    """Every split / pipeline configuration gives the oracle's answer (split-K merge, ring wrap-around,
+    persistent CTAs walking several work items)."""
+    os.environ["JGPT_B200_CHUNK_BLOCKS"] = str(chunk_blocks)
+    os.environ["JGPT_B200_STAGES"] = str(stages)
+    os.environ["JGPT_B200_PERSISTENT"] = str(persistent)
+    try:
+        lens = [700, 3, 512, 129, 1024, 16]
+        case = PagedCase(ctx, lens, H=24, Dh=16, layers=1, seed=21)
+    finally:
+        for k in ("JGPT_B200_CHUNK_BLOCKS", "JGPT_B200_STAGES", "JGPT_B200_PERSISTENT"):
+            os.environ.pop(k)
+    try:
+        rng = np.random.default_rng(6)
+        n, H, Dh = case.n, 24, 16
+        q = rng.standard_normal((n, H * Dh)).astype(np.float32)
+        rope_pos = np.array([l - 1 for l in lens], np.int32)
+        out = ctx.alloc((n, H * Dh))
+        for rep in range(2):  # twice: the arrival counters must have reset themselves
+            out.fill_bytes(0x7F)
+            case.pool.attn_decode(0, 1, ctx.from_host(q), case.seq_ids_dev(), ctx.from_host(rope_pos),
+                                  ctx.from_host(case.lens), n, 1024, out)
+            ctx.synchronize()
+            got = out.to_host()
+            want = _oracle_decode(case, 0, q, lens, rope_pos)
+            assert np.abs(got - want).max() < TOL, (rep, np.abs(got - want).max())
+    finally:
+        case.close()
+
+
+@pytest.mark.parametrize("Dh,H", [(16, 24), (8, 4)])
+def test_fused_append_decode_matches_oracle_step_by_step(ctx, Dh, H):
+    """Three decode steps of the fused kernel == oracle append + attend (payload bit-exact, outputs within TOL),
+    and == the unfused pair (append kernel, then attention kernel) bit for bit on the payload."""
+    lens0 = [0, 14, 15, 16, 47, 200]
+    case = PagedCase(ctx, lens0, H=H, Dh=Dh, layers=2, seed=31, spare_tokens=4)
+    try:
+        rng = np.random.default_rng(8)
+        n = case.n
+        lens = np.array(lens0, np.int32)
+        for step in range(3):
+            rope_pos = (lens + 3).astype(np.int32)  # RoPE position differs from the slot on purpose
+            q = rng.standard_normal((2, n, H * Dh)).astype(np.float32)
+            k = rng.standard_normal((2, n, H * Dh)).astype(np.float32)
+            v = rng.standard_normal((2, n, H * Dh)).astype(np.float32)
+            out = ctx.alloc((2, n, H * Dh))
+            # both layers in one launch (independent queries per layer)
+            case.pool.attn_decode_append(0, 2, ctx.from_host(q), ctx.from_host(k), ctx.from_host(v), case.seq_ids_dev(),
+                                         ctx.from_host(rope_pos), ctx.from_host(lens + 1), n, int(lens.max()) + 1, out)
+            ctx.synchronize()
+            got = out.to_host()
+            for layer in range(2):
+                want = O.decode_attn_batch(q[layer], k[layer], v[layer], case.kc[layer], case.vc[layer], lens, rope_pos,
+                                           H, Dh, case.max_seq, kv_fp16=True)
+                assert np.abs(got[layer] - want).max() < TOL, (step, layer, np.abs(got[layer] - want).max())
+                for i in range(n):
+                    kd, vd = ctx.alloc((H, case.max_seq, Dh)), ctx.alloc((H, case.max_seq, Dh))
+                    case.pool.gather(layer, case.seqs[i], int(lens[i]) + 1, case.max_seq, kd, vd)
+                    assert np.array_equal(kd.to_host().view(np.uint32), case.kc[layer, i].view(np.uint32))
+                    assert np.array_equal(vd.to_host().view(np.uint32), case.vc[layer, i].view(np.uint32))
+            lens = lens + 1
+    finally:
+        case.close()
+
+
+def test_host_buffer_entry_point_equals_device_entry_point(ctx):
+    lens0 = [31, 32, 100]
+    a = PagedCase(ctx, lens0, H=24, Dh=16, layers=1, seed=41, spare_tokens=2)
+    b = PagedCase(ctx, lens0, H=24, Dh=16, layers=1, seed=41, spare_tokens=2)
+    try:
+        rng = np.random.default_rng(9)
+        n, D = 3, 24 * 16
+        q, k, v = (rng.standard_normal((n, D)).astype(np.float32) for _ in range(3))
+        lens1 = np.array(lens0, np.int32) + 1
+        rope = np.array(lens0, np.int32)
+        out_h = a.pool.attn_decode_append_host(0, 1, q, k, v, a.seqs, rope, lens1)
+        out_d = ctx.alloc((n, D))
+        b.pool.attn_decode_append(0, 1, ctx.from_host(q), ctx.from_host(k), ctx.from_host(v), b.seq_ids_dev(),
+                                  ctx.from_host(rope), ctx.from_host(lens1), n, int(lens1.max()), out_d)
+        assert np.array_equal(out_h, out_d.to_host())
+        with pytest.raises(RuntimeError):  # length beyond the reserved blocks -> IllegalState
+            a.pool.attn_decode_append_host(0, 1, q, k, v, a.seqs, rope, lens1 + 64)
+        with pytest.raises(IndexError):
+            a.pool.attn_decode_append_host(0, 1, q, k, v, [0, 1, 7], rope, lens1)
+    finally:
+        a.close(), b.close()
+
+
+def test_device_self_checks_report_instead_of_faulting(ctx):
+    """A block table entry outside the pool is recorded in the status word (read by synchronize), the access
+    is redirected inside the pool, nothing faults."""
+    case = PagedCase(ctx, [40], H=2, Dh=16, layers=1, seed=1)
+    try:
+        q = np.zeros((1, 32), np.float32)
+        out = ctx.alloc((1, 32))
+        # lens says 40 tokens but claim a bound of 16: flagged, clamped
+        case.pool.attn_decode(0, 1, ctx.from_host(q), case.seq_ids_dev(), ctx.from_host(np.array([0], np.int32)),
+                              ctx.from_host(case.lens), 1, 16, out)
+        from jgpt_b200 import JgptError
+        with pytest.raises(JgptError, match="len-over-bound"):
+            ctx.synchronize()
+        ctx.synchronize()  # status word was cleared; the context stays usable
+        # sequence id outside the pool
+        case.pool.attn_decode(0, 1, ctx.from_host(q), ctx.from_host(np.array([99], np.int32)),
+                              ctx.from_host(np.array([0], np.int32)), ctx.from_host(case.lens), 1, 64, out)
+        with pytest.raises(JgptError, match="bad-seq-id"):
+            ctx.synchronize()
+        ctx.synchronize()
+    finally:
+        case.close()
