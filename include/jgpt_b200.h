@@ -85,6 +85,16 @@ JGPT_API int32_t jgpt_event_destroy(uint64_t event);
 JGPT_API int32_t jgpt_event_record(jgpt_ctx ctx, uint64_t event);
 JGPT_API int32_t jgpt_event_elapsed_ms(uint64_t start, uint64_t stop, float *ms_out); /* syncs on stop */
 
+/* CUDA graphs on the context's stream.  Replaces TensorOpsGPU.cudaStreamBeginCapture0 /
+ * cudaStreamEndCaptureAndInstantiate0 / cudaGraphExecLaunch0 / cudaGraphExecDestroy0
+ * (J/TensorOpsGPU.java:1023-1054, C/jgpt_cuda_jni_ops_graph.inl:185-460).  Everything enqueued on the
+ * context between begin and end is recorded instead of run; calls that synchronise or allocate
+ * (host-buffer entry points, first-use scratch growth) must not be made while capturing. */
+JGPT_API int32_t jgpt_graph_begin_capture(jgpt_ctx ctx);
+JGPT_API int32_t jgpt_graph_end_capture(jgpt_ctx ctx, uint64_t *graph_exec_out);
+JGPT_API int32_t jgpt_graph_launch(jgpt_ctx ctx, uint64_t graph_exec);
+JGPT_API int32_t jgpt_graph_destroy(uint64_t graph_exec);
+
 /* ---------------------------------------------------------------------------------------------
  * Paged KV store.  Replaces KvCache / KvCacheGpu (J/model/KvCache.java:13-105,
  * J/model/KvCacheGpu.java:12-118): instead of one contiguous fp32 [heads, maxSeq, dhead] buffer

@@ -84,14 +84,15 @@ constexpr int kMaxStages = 8;
 
 // Loads one token row of DH halfs from a shared-memory tile into fp32 registers.  For DH = 16
 // (two 16-byte halves per row) the order of the two loads alternates with bit 2 of the token
-// index so the 8 lanes of a quarter-warp hit 8 distinct 16-byte bank groups.
+// index so the 8 lanes of a quarter-warp hit 8 distinct 16-byte bank groups; a lane with that bit
+// set therefore receives the row with its two halves exchanged (dims 8..15 first).  Callers keep q
+// and the accumulator in the same exchanged order (see swap_halves) instead of selecting per load.
 template <int DH>
 __device__ __forceinline__ void load_row(const unsigned char *tile, int t, float (&r)[DH]) {
     if constexpr (DH == 16) {
         const int sw = (t >> 2) & 1;
-        const uint4 a = *reinterpret_cast<const uint4 *>(tile + t * 32 + sw * 16);
-        const uint4 b = *reinterpret_cast<const uint4 *>(tile + t * 32 + (sw ^ 1) * 16);
-        const uint4 lo = sw ? b : a, hi = sw ? a : b;
+        const uint4 lo = *reinterpret_cast<const uint4 *>(tile + t * 32 + sw * 16);
+        const uint4 hi = *reinterpret_cast<const uint4 *>(tile + t * 32 + (sw ^ 1) * 16);
         const __half2 *pl = reinterpret_cast<const __half2 *>(&lo), *ph = reinterpret_cast<const __half2 *>(&hi);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -118,6 +119,28 @@ __device__ __forceinline__ void load_row(const unsigned char *tile, int t, float
             r[2 * i] = f.x, r[2 * i + 1] = f.y;
         }
     }
+}
+
+// Exchanges the two 8-element halves of a 16-element register row on lanes whose rows arrive exchanged.
+template <int DH>
+__device__ __forceinline__ void swap_halves(float (&r)[DH], int t) {
+    if constexpr (DH == 16) {
+        if ((t >> 2) & 1) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float x = r[j];
+                r[j] = r[8 + j];
+                r[8 + j] = x;
+            }
+        }
+    }
+}
+
+// 2^x on the special-function unit (ex2.approx.ftz): max relative error 2^-22, -inf -> 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // Sum v[0..DH) over the 16 lanes of a half-warp.  On return lane t holds, in v[i], the total of
@@ -198,6 +221,8 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
 
     const bool is_producer = tid >= n_cons;
     uint32_t it = 0;  // KV blocks processed so far by this CTA (producer and consumers count alike)
+    int stage = 0;    // it % NS, kept incrementally (no integer division in the block loop)
+    uint32_t phase = 0;  // (it / NS) & 1
 
     for (int item = blockIdx.x; item < P.n_items; item += gridDim.x) {
         if (*s_abort) break;  // a bounded wait ran out: stop taking work (status word says why)
@@ -245,9 +270,8 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
                         atomicOr(P.status, DEV_STATUS_BAD_BLOCK);
                         phys = 0;
                     }
-                    const int s = it % NS;
-                    const uint32_t round = it / NS;
-                    if (round > 0 && !*s_abort) mbar_wait_bounded(&empty_bar[s], (round - 1) & 1, P.status, s_abort);
+                    const int s = stage;
+                    if (it >= (uint32_t)NS && !*s_abort) mbar_wait_bounded(&empty_bar[s], phase ^ 1u, P.status, s_abort);
                     if (!*s_abort) {
                         mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
                         const unsigned char *src = reinterpret_cast<const unsigned char *>(P.kv) +
@@ -255,6 +279,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
                         bulk_g2s(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s]);
                     }
                 }
+                if (++stage == NS) stage = 0, phase ^= 1u;
             }
             continue;
         }
@@ -332,11 +357,14 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             }
         }
 
+        swap_halves<DH>(q, t);  // match the order in which load_row delivers rows on this lane
+        swap_halves<DH>(o, t);
         bool aborted = false;
         for (int j = 0; j < nb; j++, it++) {
-            const int s = it % NS;
-            const uint32_t round = it / NS;
-            if (!aborted && !mbar_wait_bounded(&full_bar[s], round & 1, P.status, s_abort)) aborted = true;
+            const int s = stage;
+            const uint32_t ph = phase;
+            if (++stage == NS) stage = 0, phase ^= 1u;
+            if (!aborted && !mbar_wait_bounded(&full_bar[s], ph, P.status, s_abort)) aborted = true;
             if (aborted) continue;  // keep counting blocks, touch nothing
             const int tok = (b0 + j) * BT + t;
             if (active && tok < len_cached) {
@@ -347,14 +375,14 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
 #pragma unroll
                 for (int d = 0; d < DH; d++) sc = fmaf(q[d], kr[d], sc);
                 if (sc > m) {  // new running maximum: rescale the private state
-                    const float corr = exp2f(m - sc);  // m = -inf on the first token -> 0
+                    const float corr = fast_exp2(m - sc);  // m = -inf on the first token -> 0
                     l *= corr;
 #pragma unroll
                     for (int d = 0; d < DH; d++) o[d] *= corr;
                     m = sc;
                 }
                 load_row<DH>(ktile + TILE, t, vr);
-                const float pexp = exp2f(sc - m);
+                const float pexp = fast_exp2(sc - m);
                 l += pexp;
 #pragma unroll
                 for (int d = 0; d < DH; d++) o[d] = fmaf(pexp, vr[d], o[d]);
@@ -366,6 +394,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
         // waiting for it) but stores nothing; the item loop ends at its next iteration.
 
         // ---- merge the 16 token lanes of each head (warp shuffles) ----
+        swap_halves<DH>(o, t);  // back to natural dimension order
         float M = m;
 #pragma unroll
         for (int off = 8; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
@@ -452,7 +481,13 @@ static int pick_head_group(int H, int DH, int forced) {
 template <int DH>
 static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int threads, size_t smem, int grid) {
     auto kern = fused ? attn_decode_kernel<DH, true> : attn_decode_kernel<DH, false>;
-    JGPT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // Opt in to > 48 KiB of dynamic shared memory once per kernel, device and size.
+    static int opted[2][16] = {};
+    int &have = opted[fused ? 1 : 0][p->ctx->device & 15];
+    if ((int)smem > have) {
+        JGPT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        have = (int)smem;
+    }
     kern<<<grid, threads, smem, p->ctx->stream>>>(P);
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
@@ -471,8 +506,18 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
     P.HG = pick_head_group(p->heads, DH, p->head_group);
     P.n_hg = p->heads / P.HG;
-    P.chunk_blocks = p->chunk_blocks;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
+    if (p->chunk_blocks > 0) {
+        P.chunk_blocks = p->chunk_blocks;
+    } else {
+        // Automatic split: per-CTA set-up (barriers, q + RoPE, table fetch, merge) is amortised over the
+        // chunk, so chunks are as long as possible while the launch still offers about 1.5 CTAs per SM.
+        const long long total_blocks = (long long)n_layers * n * (p->heads / P.HG) * max_blocks;
+        const long long want_items = 3ll * p->ctx->sm_count / 2;
+        int cb = 32;
+        while (cb > 4 && total_blocks / cb < want_items) cb >>= 1;
+        P.chunk_blocks = cb;
+    }
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
     P.stages = p->stages;

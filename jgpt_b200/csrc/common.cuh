@@ -94,7 +94,7 @@ struct Pool {
     std::vector<SeqState> seqs;
     uint64_t clock = 0;
     // launch tuning (read once from the environment at creation)
-    int chunk_blocks = 8;
+    int chunk_blocks = 0;  // 0 = automatic
     int stages = 4;
     int persistent = 0;
     int head_group = 0;  // 0 = automatic

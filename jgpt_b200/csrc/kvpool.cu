@@ -292,7 +292,7 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     p->ctx = c;
     p->layers = layers, p->heads = heads, p->dhead = dhead, p->n_blocks = n_blocks, p->max_seqs = max_seqs;
     p->max_blocks_per_seq = max_blocks_per_seq, p->max_positions = max_positions, p->rope_base = rope_base;
-    p->chunk_blocks = std::min(32, std::max(1, env_int("JGPT_B200_CHUNK_BLOCKS", 8)));
+    p->chunk_blocks = std::min(32, std::max(0, env_int("JGPT_B200_CHUNK_BLOCKS", 0)));  // 0 = automatic
     p->stages = std::min(8, std::max(2, env_int("JGPT_B200_STAGES", 4)));
     p->persistent = env_int("JGPT_B200_PERSISTENT", 0);
     p->head_group = env_int("JGPT_B200_HEAD_GROUP", 0);
@@ -300,8 +300,9 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     cudaError_t e = cudaMalloc(&p->kv, p->kv_bytes);
     if (e != cudaSuccess) {
         cudaGetLastError();
+        const uint64_t bytes = p->kv_bytes;
         delete p;
-        return fail(JGPT_ERR_OUT_OF_MEMORY, "KV pool of %llu bytes does not fit: %s", (unsigned long long)p->kv_bytes,
+        return fail(JGPT_ERR_OUT_OF_MEMORY, "KV pool of %llu bytes does not fit: %s", (unsigned long long)bytes,
                     cudaGetErrorString(e));
     }
     JGPT_CUDA_TRY(cudaMemsetAsync(p->kv, 0, p->kv_bytes, c->stream));

@@ -231,4 +231,44 @@ int32_t jgpt_event_elapsed_ms(uint64_t start, uint64_t stop, float *ms_out) {
     return JGPT_OK;
 }
 
+// ---- CUDA graphs (TensorOpsGPU.cudaStreamBeginCapture0 / cudaStreamEndCaptureAndInstantiate0 /
+// cudaGraphExecLaunch0 / cudaGraphExecDestroy0, src/main/cpp/jgpt_cuda_jni_ops_graph.inl:185-460) ----
+int32_t jgpt_graph_begin_capture(jgpt_ctx h) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    return JGPT_OK;
+}
+
+int32_t jgpt_graph_end_capture(jgpt_ctx h, uint64_t *graph_exec_out) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(graph_exec_out, JGPT_ERR_INVALID_ARGUMENT, "null output");
+    JGPT_CUDA_TRY(make_current(c));
+    cudaGraph_t g = nullptr;
+    JGPT_CUDA_TRY(cudaStreamEndCapture(c->stream, &g));
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(JGPT_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    *graph_exec_out = reinterpret_cast<uint64_t>(ex);
+    return JGPT_OK;
+}
+
+int32_t jgpt_graph_launch(jgpt_ctx h, uint64_t graph_exec) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(graph_exec, JGPT_ERR_INVALID_ARGUMENT, "null graph");
+    JGPT_CUDA_TRY(make_current(c));
+    JGPT_CUDA_TRY(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph_exec), c->stream));
+    return JGPT_OK;
+}
+
+int32_t jgpt_graph_destroy(uint64_t graph_exec) {
+    if (!graph_exec) return JGPT_OK;
+    JGPT_CUDA_TRY(cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(graph_exec)));
+    return JGPT_OK;
+}
+
 }  // extern "C"

@@ -41,6 +41,17 @@ class Context:
         buf.copy_from(arr)
         return buf
 
+    def capture(self, fn) -> "Graph":
+        """Records everything ``fn()`` enqueues on this context into a CUDA graph."""
+        B.check(self._lib.jgpt_graph_begin_capture(self.handle))
+        try:
+            fn()
+        finally:
+            h = C.c_uint64()
+            rc = self._lib.jgpt_graph_end_capture(self.handle, C.byref(h))
+        B.check(rc)
+        return Graph(self, h.value)
+
     def close(self):
         if self.handle:
             self._lib.jgpt_ctx_destroy(self.handle)
@@ -51,6 +62,19 @@ class Context:
 
     def __exit__(self, *a):
         self.close()
+
+
+class Graph:
+    def __init__(self, ctx: Context, handle: int):
+        self.ctx, self.handle = ctx, handle
+
+    def launch(self):
+        B.check(self.ctx._lib.jgpt_graph_launch(self.ctx.handle, self.handle))
+
+    def close(self):
+        if self.handle:
+            self.ctx._lib.jgpt_graph_destroy(self.handle)
+            self.handle = 0
 
 
 class Event:

@@ -1,0 +1,110 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol the header declares, entry points
+fail loudly without a GPU (no fallback), the allocator specification behaves, the CPU arm of the benchmark
+prints a well-formed line."""
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from jgpt_b200 import binding as B
+
+    decl = B.declared_functions()
+    names = [n for n, _, _ in decl]
+    assert len(names) >= 40 and len(set(names)) == len(names)
+    lib = C.CDLL(B.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/jgpt_b200.h but not exported"
+    # nothing else with the public prefix is exported behind the header's back
+    out = subprocess.run(["nm", "-D", "--defined-only", B.LIB_PATH], capture_output=True, text=True).stdout
+    exported = {l.split()[-1] for l in out.splitlines() if " T " in l and l.split()[-1].startswith("jgpt_")}
+    assert exported == set(names), exported ^ set(names)
+
+
+def test_no_gpu_means_loud_failure_not_fallback():
+    """On a machine without a usable GPU creating a context raises (the reference's requireCuda throws
+    IllegalStateException); with a GPU this test has nothing to check."""
+    import jgpt_b200 as J
+    from jgpt_b200 import binding as B
+
+    n = C.c_int32()
+    assert B.load().jgpt_device_count(C.byref(n)) == 0
+    if n.value == 0:
+        with pytest.raises(RuntimeError, match="no CPU fallback"):
+            J.Context(0)
+
+
+def test_bad_handles_and_arguments_are_rejected_without_a_gpu():
+    from jgpt_b200 import binding as B
+
+    lib = B.load()
+    out = C.c_uint64()
+    assert lib.jgpt_sync(12345) == B.ERR_BAD_HANDLE
+    assert lib.jgpt_kvpool_create(12345, 1, 1, 16, 16, 1, 1, 1, 16, 10000.0, C.byref(out)) == B.ERR_BAD_HANDLE
+    assert lib.jgpt_seq_alloc(999, C.byref(C.c_int32())) == B.ERR_BAD_HANDLE
+    assert b"handle" in lib.jgpt_last_error()
+    assert lib.jgpt_ctx_create(0, None) == B.ERR_INVALID_ARGUMENT
+
+
+def test_product_package_never_touches_the_oracle():
+    """The shipped package must not import, load or link the oracle (or any CPU fallback)."""
+    pkg = os.path.join(ROOT, "jgpt_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+    from jgpt_b200 import binding as B
+
+    ldd = subprocess.run(["ldd", B.LIB_PATH], capture_output=True, text=True).stdout
+    assert "oracle" not in ldd and "torch" not in ldd
+
+
+def test_allocator_specification_basics():
+    a = O.PagedAllocatorRef(n_blocks=6, block_tokens=16, max_seqs=3, max_blocks_per_seq=4)
+    s0, s1 = a.seq_alloc(), a.seq_alloc()
+    assert (s0, s1) == (0, 1)
+    assert a.reserve(s0, 17) and a.tables[s0] == [0, 1]
+    assert a.reserve(s1, 1) and a.tables[s1] == [2]
+    assert a.reserve(s0, 20) and a.tables[s0] == [0, 1]  # already covered
+    assert not a.reserve(s1, 16 * 5)  # per-sequence limit
+    assert not a.reserve(s1, 16 * 4 + 1)
+    assert a.reserve(s1, 64) and a.tables[s1] == [2, 3, 4, 5]
+    assert not a.reserve(s0, 33)  # pool exhausted, all or nothing
+    assert a.tables[s0] == [0, 1]
+    a.seq_free(s1)
+    assert a.free == [2, 3, 4, 5]
+    assert a.reserve(s0, 48) and a.tables[s0] == [0, 1, 5]  # most recently freed block first
+    assert a.append_index(s0, 37) == (5, 5)
+    assert a.seq_alloc() == 1
+
+
+def test_reference_arm_prints_the_contract_line():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["config"]["workload"].startswith("kv_append")
+    # a non-zero rank exits 0 without output
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
+                       capture_output=True, text=True, timeout=60, env=env)
+    assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+def test_algorithmic_bytes_figure():
+    sys.path.insert(0, ROOT)
+    import bench
+
+    assert bench.ALG_BYTES_LAYER == 100_876_288 and bench.ALG_BYTES_STEP == 1_210_515_456
