@@ -189,6 +189,29 @@ JGPT_API int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, 
                                               const int32_t *seq_ids_host, const int32_t *rope_pos_host,
                                               const int32_t *lens_host, int32_t n, float *out_host);
 
+/* Decode attention that allocates nothing.  No counterpart in the reference.
+ *
+ * Same computation as jgpt_attn_decode for ONE layer, but the split-K scratch (partial softmax
+ * states and arrival counters) lives in a fixed array inside the library instead of memory that
+ * jgpt_attn_decode obtains with cudaMalloc when a launch first needs it.  It is meant for hosts
+ * that must not allocate while generating: a process that has already given the whole GPU to its
+ * own buffers (a late cudaMalloc may fail there, and every cudaMalloc/cudaFree stalls the device).
+ * The call makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ *   - Limits: n * ceil(ceil(max_len/16)/chunk) * heads * (dhead+2) <= 1,048,576 partial words (4 MiB)
+ *     and n * head_groups <= 4,096 counters.  Larger requests return JGPT_ERR_INVALID_ARGUMENT with a
+ *     message that states both numbers.  Every GPU that loads the library holds the 4 MiB + 16 KiB
+ *     array until the process exits.
+ *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress); make
+ *     that first call before any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents: the call
+ *     clears the counters it uses on the stream before launching.  Two calls that overlap on the
+ *     GPU (different contexts or streams on the same device) race on it; keep them stream ordered. */
+JGPT_API int32_t jgpt_attn_decode_static_scratch(jgpt_kvpool pool, int32_t layer, const float *q_dev,
+                                                 const int32_t *seq_ids_dev, const int32_t *rope_pos_dev,
+                                                 const int32_t *lens_dev, int32_t n, int32_t max_len,
+                                                 float *out_dev);
+
 #ifdef __cplusplus
 }
 #endif

@@ -622,3 +622,114 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention with its split-K scratch in a fixed, library-owned device array.
+//
+// jgpt_attn_decode sizes its split-K scratch (partial softmax states + arrival counters) with
+// cudaMalloc the first time a launch needs more than it has.  Some hosts cannot tolerate that on the
+// generation path: a process that has already handed the whole GPU to its own buffers (a trainer
+// that samples text between optimizer steps with the device full, a server that sizes its KV pool to
+// whatever memory is left) can see that late cudaMalloc fail, and any cudaMalloc/cudaFree stalls the
+// device while it runs.  This variant never allocates: its scratch is the array below, which every
+// GPU that loads the library holds from load until the process exits.
+//
+// Limits, stated: kStaticPartialFloats fp32 partial words (4 MiB) and kStaticTickets counters
+// (16 KiB) per device.  One layer per call.  Requests that need more are rejected.
+// ------------------------------------------------------------------------------------------------
+namespace jgpt {
+
+constexpr size_t kStaticPartialFloats = size_t(1) << 20;  // 4 MiB of (m, l, o[dhead]) partials
+constexpr size_t kStaticTickets = 4096;                   // arrival counters, one per (sequence row, head group)
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never an address to pass to a kernel.
+static __device__ __align__(256) float g_decode_static_scratch[kStaticPartialFloats + kStaticTickets];
+
+constexpr int kStaticMaxDevices = 64;
+static float *g_static_scratch_addr[kStaticMaxDevices] = {};  // per device, resolved on first use
+
+// Resolves the array's device address for the context's device (which must be current).
+static int32_t static_scratch_for(const Ctx *c, float **partials, int **tickets) {
+    JGPT_REQUIRE(c->device >= 0 && c->device < kStaticMaxDevices, JGPT_ERR_UNSUPPORTED,
+                 "device index %d is beyond the %d devices the static scratch table covers", c->device, kStaticMaxDevices);
+    if (!g_static_scratch_addr[c->device]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(JGPT_ERR_CUDA, "cudaGetSymbolAddress(static decode scratch) on device %d: %s", c->device,
+                        cudaGetErrorString(e));
+        g_static_scratch_addr[c->device] = static_cast<float *>(p);
+    }
+    *partials = g_static_scratch_addr[c->device];
+    *tickets = reinterpret_cast<int *>(g_static_scratch_addr[c->device] + kStaticPartialFloats);
+    return JGPT_OK;
+}
+
+static int32_t launch_attn_decode_static(Pool *p, int layer, const float *q, const int *seq_ids, const int *rope_pos,
+                                         const int *lens, int n, int max_len, float *out) {
+    DecodeParams P;
+    memset(&P, 0, sizeof(P));
+    const int DH = p->dhead;
+    P.kv = p->kv, P.table = p->d_table, P.rope = p->d_rope;
+    P.q = q, P.k_new = nullptr, P.v_new = nullptr, P.out = out;
+    P.seq_ids = seq_ids, P.rope_pos = rope_pos, P.lens = lens;
+    P.status = p->ctx->d_status;
+    P.n = n, P.H = p->heads, P.layer0 = layer, P.n_layers = 1, P.mbs = p->max_blocks_per_seq;
+    P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
+    P.HG = pick_head_group(p->heads, DH, p->head_group);
+    P.n_hg = p->heads / P.HG;
+    const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
+    if (p->chunk_blocks > 0) {
+        P.chunk_blocks = p->chunk_blocks;
+    } else {
+        const long long total_blocks = (long long)n * P.n_hg * max_blocks;
+        const long long want_items = 3ll * p->ctx->sm_count / 2;
+        int cb = 32;
+        while (cb > 4 && total_blocks / cb < want_items) cb >>= 1;
+        P.chunk_blocks = cb;
+    }
+    P.max_len = max_blocks * kBlockTokens;
+    P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
+    P.stages = p->stages;
+    P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
+    const long long items = (long long)n * P.n_hg * P.max_chunks;
+    JGPT_REQUIRE(items < (1ll << 31), JGPT_ERR_INVALID_ARGUMENT, "too many work items (%lld)", items);
+    P.n_items = (int)items;
+    const unsigned long long need_partials = (unsigned long long)n * P.max_chunks * p->heads * (DH + 2);
+    const unsigned long long need_tickets = (unsigned long long)n * P.n_hg;
+    JGPT_REQUIRE(need_partials <= kStaticPartialFloats && need_tickets <= kStaticTickets, JGPT_ERR_INVALID_ARGUMENT,
+                 "request needs %llu partial words and %llu counters; the static scratch holds %llu and %llu "
+                 "(lower n or max_len, or use jgpt_attn_decode)",
+                 need_partials, need_tickets, (unsigned long long)kStaticPartialFloats, (unsigned long long)kStaticTickets);
+    int32_t rc = static_scratch_for(p->ctx, &P.partials, &P.tickets);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left.  Partials are always written before they are read;
+    // the counters must start at zero (they reset themselves, but not if an earlier launch gave up half way).
+    JGPT_CUDA_TRY(cudaMemsetAsync(P.tickets, 0, sizeof(int) * need_tickets, p->ctx->stream));
+    const int n_cons = ((kBlockTokens * P.HG + 31) / 32) * 32;
+    const int threads = n_cons + 32;
+    const size_t smem = (size_t)P.HG * 2 * kBlockTokens * DH * 2 * P.stages;
+    switch (DH) {
+        case 4: return launch_decode_t<4>(p, P, false, threads, smem, P.n_items);
+        case 8: return launch_decode_t<8>(p, P, false, threads, smem, P.n_items);
+        case 16: return launch_decode_t<16>(p, P, false, threads, smem, P.n_items);
+        case 32: return launch_decode_t<32>(p, P, false, threads, smem, P.n_items);
+        default: return fail(JGPT_ERR_UNSUPPORTED, "dhead %d not supported", DH);
+    }
+}
+
+}  // namespace jgpt
+
+extern "C" int32_t jgpt_attn_decode_static_scratch(jgpt_kvpool pool, int32_t layer, const float *q_dev,
+                                                   const int32_t *seq_ids_dev, const int32_t *rope_pos_dev,
+                                                   const int32_t *lens_dev, int32_t n, int32_t max_len, float *out_dev) {
+    Pool *p = pool_registry().get(pool);
+    JGPT_REQUIRE(p, JGPT_ERR_BAD_HANDLE, "bad kvpool handle");
+    JGPT_CUDA_TRY(make_current(p->ctx));
+    JGPT_REQUIRE(layer >= 0 && layer < p->layers, JGPT_ERR_OUT_OF_RANGE, "layer %d outside [0,%d)", layer, p->layers);
+    if (n == 0) return JGPT_OK;
+    JGPT_REQUIRE(n > 0 && q_dev && seq_ids_dev && rope_pos_dev && lens_dev && out_dev, JGPT_ERR_INVALID_ARGUMENT,
+                 "null pointer or negative count");
+    JGPT_REQUIRE(max_len >= 1, JGPT_ERR_INVALID_ARGUMENT, "max_len must be >= 1");
+    return launch_attn_decode_static(p, layer, q_dev, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len, out_dev);
+}

@@ -104,6 +104,11 @@ class KvPool:
         B.check(self._lib.jgpt_attn_decode(self.handle, layer0, n_layers, _ptr(q_dev), _ptr(seq_ids_dev),
                                            _ptr(rope_pos_dev), _ptr(lens_dev), n, max_len, _ptr(out_dev)))
 
+    def attn_decode_static_scratch(self, layer, q_dev, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len, out_dev):
+        """Single-layer decode attention that never allocates (scratch in a fixed array of the library)."""
+        B.check(self._lib.jgpt_attn_decode_static_scratch(self.handle, layer, _ptr(q_dev), _ptr(seq_ids_dev),
+                                                          _ptr(rope_pos_dev), _ptr(lens_dev), n, max_len, _ptr(out_dev)))
+
     def attn_decode_append(self, layer0, n_layers, q_dev, k_dev, v_dev, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len,
                            out_dev):
         B.check(self._lib.jgpt_attn_decode_append(self.handle, layer0, n_layers, _ptr(q_dev), _ptr(k_dev), _ptr(v_dev),
