@@ -189,6 +189,17 @@ JGPT_API int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, 
                                               const int32_t *seq_ids_host, const int32_t *rope_pos_host,
                                               const int32_t *lens_host, int32_t n, float *out_host);
 
+/* Causal prefill attention that fills the cache.  Replaces attn_fwd_run_core + masked softmax
+ * (C/jgpt_cuda_extra_kernels_launches.inl:1840-1870, 239-276) and the reference's own FA-2 forward
+ * (:1916-2050), fused with RoPE and the append of :1085-1099.
+ * n_seqs sequences, sequence i contributing S_i = seq_starts[i+1]-seq_starts[i] consecutive rows of
+ * q/k/v [n_tokens, heads*dhead] (fp32, before RoPE); row r of sequence i sits at cache slot r and
+ * RoPE position rope_offsets[i] + r.  seq_starts_host has n_seqs+1 entries (host). */
+JGPT_API int32_t jgpt_attn_prefill(jgpt_kvpool pool, int32_t layer, const float *q_dev, const float *k_dev,
+                                   const float *v_dev, const int32_t *seq_ids_host,
+                                   const int32_t *seq_starts_host, const int32_t *rope_offsets_host,
+                                   int32_t n_seqs, float *out_dev);
+
 /* Decode attention that allocates nothing.  No counterpart in the reference.
  *
  * Same computation as jgpt_attn_decode for ONE layer, but the split-K scratch (partial softmax

@@ -13,57 +13,11 @@
 // The kernel is HBM-bound (about 1 FLOP per byte at dhead 16): what matters is bytes in flight
 // per SM (stages x slab bytes x resident CTAs) and few, large, 16-byte-aligned transactions.
 #include "common.cuh"
+#include "ptx.cuh"
 
 #include <algorithm>
 
 namespace jgpt {
-
-// ------------------------------------------------------------------------------------------
-// PTX helpers: mbarrier + bulk async copy (non-multicast, local global memory only)
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after kWaitSpins polls (each poll may itself block for a while in
-// hardware), records the failure in the status word and tells the caller to bail out.
-constexpr uint32_t kWaitSpins = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, int *status, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < kWaitSpins; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;  // somebody else already gave up
-    }
-    atomicOr(status, DEV_STATUS_WAIT_TIMEOUT);
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(smem_dst)),
-                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
 
 struct DecodeParams {
     __half *kv;
@@ -134,13 +88,6 @@ __device__ __forceinline__ void swap_halves(float (&r)[DH], int t) {
             }
         }
     }
-}
-
-// 2^x on the special-function unit (ex2.approx.ftz): max relative error 2^-22, -inf -> 0.
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
 }
 
 // Sum v[0..DH) over the 16 lanes of a half-warp.  On return lane t holds, in v[i], the total of

@@ -80,6 +80,8 @@ struct Pool {
     uint64_t n_tickets = 0;
     int *d_evict_list = nullptr;  // freed block ids for the scrub kernel
     int evict_cap = 0;
+    void *d_prefill_desc = nullptr;  // per-sequence descriptors of a prefill call
+    int prefill_desc_cap = 0;
     // staging for the host-buffer entry points (grow-only)
     float *d_stage_f = nullptr;
     uint64_t stage_f_floats = 0;

@@ -336,6 +336,7 @@ int32_t jgpt_kvpool_destroy(jgpt_kvpool h) {
     pool_registry().remove(p);
     cudaFree(p->kv), cudaFree(p->d_table), cudaFree(p->d_rope), cudaFree(p->d_partials), cudaFree(p->d_tickets);
     cudaFree(p->d_evict_list), cudaFree(p->d_stage_f), cudaFree(p->d_stage_i);
+    cudaFree(p->d_prefill_desc);
     cudaFreeHost(p->h_stage_f), cudaFreeHost(p->h_stage_i);
     delete p;
     return JGPT_OK;

@@ -104,6 +104,16 @@ class KvPool:
         B.check(self._lib.jgpt_attn_decode(self.handle, layer0, n_layers, _ptr(q_dev), _ptr(seq_ids_dev),
                                            _ptr(rope_pos_dev), _ptr(lens_dev), n, max_len, _ptr(out_dev)))
 
+    def attn_prefill(self, layer, q_dev, k_dev, v_dev, seq_ids, seq_starts, rope_offsets, out_dev):
+        """Causal prefill attention over packed prompts that also fills the cache (host index arrays)."""
+        seq_ids = np.ascontiguousarray(seq_ids, np.int32)
+        seq_starts = np.ascontiguousarray(seq_starts, np.int32)
+        rope_offsets = np.ascontiguousarray(rope_offsets, np.int32)
+        if seq_starts.size != seq_ids.size + 1 or rope_offsets.size != seq_ids.size:
+            raise ValueError("seq_starts needs n_seqs + 1 entries, rope_offsets n_seqs")
+        B.check(self._lib.jgpt_attn_prefill(self.handle, layer, _ptr(q_dev), _ptr(k_dev), _ptr(v_dev), seq_ids.ctypes.data,
+                                            seq_starts.ctypes.data, rope_offsets.ctypes.data, seq_ids.size, _ptr(out_dev)))
+
     def attn_decode_static_scratch(self, layer, q_dev, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len, out_dev):
         """Single-layer decode attention that never allocates (scratch in a fixed array of the library)."""
         B.check(self._lib.jgpt_attn_decode_static_scratch(self.handle, layer, _ptr(q_dev), _ptr(seq_ids_dev),
