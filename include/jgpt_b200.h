@@ -35,6 +35,7 @@ extern "C" {
 
 typedef uint64_t jgpt_ctx;    /* one GPU + one stream                    */
 typedef uint64_t jgpt_kvpool; /* paged fp16 K/V store of one model       */
+typedef uint64_t jgpt_model;  /* device-resident weights + step workspace */
 
 
 enum {
@@ -199,6 +200,58 @@ JGPT_API int32_t jgpt_attn_prefill(jgpt_kvpool pool, int32_t layer, const float 
                                    const float *v_dev, const int32_t *seq_ids_host,
                                    const int32_t *seq_starts_host, const int32_t *rope_offsets_host,
                                    int32_t n_seqs, float *out_dev);
+
+/* ---------------------------------------------------------------------------------------------
+ * Model + forward step.  Replaces GPTModel weights upload (J/model/GPTModel.java:241-293),
+ * loadWeights (:1944-1965) and GptKvForward.forwardPrefillGpu / forwardDecodeGpu
+ * (J/model/GptKvForward.java:46-90, 131-170).
+ * ------------------------------------------------------------------------------------------- */
+JGPT_API int32_t jgpt_model_create(jgpt_ctx ctx, int32_t vocab, int32_t max_seq_len, int32_t d_model,
+                                   int32_t heads, int32_t layers, int32_t d_ff, float rms_eps,
+                                   int32_t max_rows, jgpt_model *out);
+JGPT_API int32_t jgpt_model_destroy(jgpt_model model);
+/* Tensor idx in GPTModel.getParameters() order (:1928-1938): tok, pos, per layer
+ * Wq,Wk,Wv,Wo,W1,W2,W3,norm1,norm2, then normFinal, lmHead.  host fp32, n_floats must match. */
+JGPT_API int32_t jgpt_model_num_tensors(jgpt_model model, int32_t *n_out);
+JGPT_API int32_t jgpt_model_set_tensor(jgpt_model model, int32_t idx, const float *host, uint64_t n_floats);
+/* veles.weights.v1 file (J/model/GptModelWeightsLoader.java:58-81). */
+JGPT_API int32_t jgpt_model_load_weights(jgpt_model model, const char *path);
+
+/* forwardPrefill(ids [1,S], cache, ropeOffset) -> logits [S, vocab] (host).  Error contract of
+ * J/model/GptKvForward.java:47-60.  logits_host [S, vocab], last_logits_host [vocab] and next_token_host
+ * (greedy argmax of the last row) may each be NULL.  Sets the sequence length to S.  max_rows of
+ * jgpt_model_create bounds the rows (tokens) of one forward call. */
+JGPT_API int32_t jgpt_forward_prefill(jgpt_model model, jgpt_kvpool pool, int32_t seq, const int32_t *ids_host,
+                                      int32_t S, int32_t rope_offset, float *logits_host,
+                                      float *last_logits_host, int32_t *next_token_host);
+/* The same for n prompts packed back to back (the reference loops over sequences: its prefill is
+ * batch-1 only, J/model/GptKvForward.java:14-16).  Sequence i owns rows [seq_starts[i], seq_starts[i+1])
+ * of ids_host.  all_logits_host [rows, vocab] only for n == 1; last_logits_host [n, vocab] and
+ * next_tokens_host [n] (greedy argmax of each last row) may be NULL. */
+JGPT_API int32_t jgpt_forward_prefill_batch(jgpt_model model, jgpt_kvpool pool, const int32_t *seq_ids_host,
+                                            const int32_t *seq_starts_host, const int32_t *ids_host,
+                                            const int32_t *rope_offsets_host, int32_t n, float *all_logits_host,
+                                            float *last_logits_host, int32_t *next_tokens_host);
+/* Batched forwardDecode: for i in [0,n) token ids[i] of sequence seq_ids[i] with
+ * cacheLenBefore[i] (must equal the stored length, else JGPT_ERR_ILLEGAL_STATE; full ->
+ * JGPT_ERR_ILLEGAL_STATE) and ropePosition[i] (J/model/GptKvForward.java:131-141).
+ * logits_host [n, vocab] may be NULL; next_tokens_host [n] (greedy argmax on the device, ties ->
+ * lowest id, J/model/GptAutoregressiveGenerator.java:288-299) may be NULL.  Lengths become +1. */
+JGPT_API int32_t jgpt_forward_decode(jgpt_model model, jgpt_kvpool pool, const int32_t *seq_ids_host,
+                                     const int32_t *ids_host, const int32_t *cache_len_before_host,
+                                     const int32_t *rope_pos_host, int32_t n, float *logits_host,
+                                     int32_t *next_tokens_host);
+/* sampleNextToken on host logits (J/model/GptAutoregressiveGenerator.java:208-286): temperature, stable
+ * top-k by (logit desc, index asc), softmax, inverse CDF with the caller's uniform draw u01 (the
+ * reference draws from an unseeded ThreadLocalRandom); greedy with lowest-index ties when temperature <= 0. */
+JGPT_API int32_t jgpt_sample_next_token(const float *logits_host, int32_t vocab, float temperature, int32_t top_k,
+                                        float u01, int32_t *token_out);
+/* GPTModel.generateGpuKv, greedy (temperature <= 0) (J/model/GptAutoregressiveGenerator.java:108-206):
+ * out_host [S + max_new]; prompt kept, stop on sampled id 0 with a zero tail, sliding-window
+ * re-prefill when the context overflows.  n_sampled_out = number of sampled tokens. */
+JGPT_API int32_t jgpt_generate_greedy(jgpt_model model, jgpt_kvpool pool, const int32_t *prompt_host, int32_t S,
+                                      int32_t max_new, int32_t *out_host, int32_t *n_sampled_out);
+
 
 /* Decode attention that allocates nothing.  No counterpart in the reference.
  *

@@ -8,3 +8,4 @@ ctypes because no JDK is available where it is tested; a JNI / FFM binding maps 
 from .binding import JgptError, PoolExhausted, load  # noqa: F401
 from .runtime import Context, DeviceBuffer  # noqa: F401
 from .kv_cache import KvPool, KvCacheGpu  # noqa: F401
+from .model import GPTModel  # noqa: F401

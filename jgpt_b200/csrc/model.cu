@@ -1,0 +1,691 @@
+// Model weights on the device and the forward step around the attention kernels: embedding + learned
+// positions, RMSNorm, fp32 projections, SwiGLU, LM head, greedy argmax, and the generation loop.
+//
+// The dense ops keep fp32 operands and accumulate every output element over k in ascending order in one
+// thread, so a projection is reproducible against a scalar CPU loop (the reference runs the same GEMMs
+// through cuBLAS under TF32 math: src/main/cpp/jgpt_cuda_jni_init_matmul.inl:67, 794, 892).
+#include "common.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+
+namespace jgpt {
+
+struct LayerW {
+    float *wq, *wk, *wv, *wo, *w1, *w2, *w3, *norm1, *norm2;
+};
+
+struct Model {
+    Ctx *ctx = nullptr;
+    int vocab = 0, max_seq = 0, d_model = 0, heads = 0, layers = 0, d_ff = 0, max_rows = 0;
+    float eps = 1e-5f;
+    float *tok = nullptr, *pos = nullptr, *norm_final = nullptr, *lm_head = nullptr;
+    std::vector<LayerW> L;
+    // workspace for up to max_rows rows
+    float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *att = nullptr, *h1 = nullptr, *g = nullptr;
+    float *logits = nullptr;  // [logit_rows, vocab]
+    int logit_rows = 0;
+    int *d_idx = nullptr;     // [5][max_rows]: ids, pos rows, seq ids, rope pos, lens
+    int *h_idx = nullptr;     // pinned mirror
+    int *d_next = nullptr;    // [max_rows] argmax
+    int *h_next = nullptr;    // pinned
+    int *d_rowsel = nullptr;  // [max_rows] rows whose logits are wanted
+    int strict = 1;           // 1: mul + add (two roundings, as a scalar loop compiled without contraction); 0: FMA
+};
+
+Registry<Model> &model_registry() {
+    static Registry<Model> r;
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Kernels
+// ------------------------------------------------------------------------------------------------
+
+// x[r,:] = tok[id[r],:] + pos[posrow[r],:]   (embedding_token_fwd_kernel + add_position_embedding_broadcast_kernel,
+// src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:937-955, 1020-1032)
+__global__ void __launch_bounds__(128) embed_pos_kernel(const float *__restrict__ tok, const float *__restrict__ pos,
+                                                        const int *__restrict__ ids, const int *__restrict__ posrow,
+                                                        float *__restrict__ x, int D) {
+    const int r = blockIdx.x;
+    const float4 *t = reinterpret_cast<const float4 *>(tok + (size_t)ids[r] * D);
+    const float4 *p = reinterpret_cast<const float4 *>(pos + (size_t)posrow[r] * D);
+    float4 *o = reinterpret_cast<float4 *>(x + (size_t)r * D);
+    for (int j = threadIdx.x; j < D / 4; j += blockDim.x) {
+        const float4 a = t[j], b = p[j];
+        o[j] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+    }
+}
+
+// RMSNorm, one block per row (rms_norm_fwd_block_kernel, same file :694-713):
+// rms = sqrtf(sum(x^2)/D + eps); inv = (rms > 0 && finite) ? 1/rms : 0; y = x * inv * gamma.
+__global__ void __launch_bounds__(128) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                      float *__restrict__ y, int D, float eps) {
+    __shared__ float red[4];
+    const float *xr = x + (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < D; j += blockDim.x) ss += xr[j] * xr[j];
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = red[0] + red[1] + red[2] + red[3];
+    const float rms = sqrtf(ss / (float)D + eps);
+    const float inv = (rms > 0.f && isfinite(rms)) ? (1.f / rms) : 0.f;
+    float *yr = y + (size_t)blockIdx.x * D;
+    for (int j = threadIdx.x; j < D; j += blockDim.x) yr[j] = xr[j] * inv * gamma[j];
+}
+
+// act = h1 * (g * sigmoid(g)), sigmoid clamped to 1 / 0 at |g| >= 20 (sigmoid_kernel :799-815, mul_kernel :832).
+__global__ void __launch_bounds__(256) swiglu_kernel(float *__restrict__ h1, const float *__restrict__ g, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float gv = g[i];
+    float s;
+    if (gv >= 20.f) s = 1.f;
+    else if (gv <= -20.f) s = 0.f;
+    else s = 1.f / (1.f + expf(-gv));
+    h1[i] = h1[i] * (gv * s);
+}
+
+// Up to three products sharing A in one launch: C_z[M,N] = A[M,K] . W_z[K,N] (+ R_z), z = blockIdx.z.
+// Row-major fp32; every C element is accumulated over k = 0..K-1 in order by one thread.
+struct GemmBatch {
+    const float *W[3];
+    float *C[3];
+    const float *R[3];  // optional residual added after the accumulation
+};
+
+template <int BM, int BN, int TM, int TN, bool STRICT>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_kernel(const float *__restrict__ A, const GemmBatch B, int M, int K,
+                                                                     int N, const int *__restrict__ rowsel) {
+    constexpr int BK = 16;
+    constexpr int NT = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 1];
+    __shared__ __align__(16) float Ws[BK][BN];
+    const float *__restrict__ W = B.W[blockIdx.z];
+    float *C = B.C[blockIdx.z];        // C and R may be the same buffer (x += A.W): each element is read
+    const float *R = B.R[blockIdx.z];  // and then written by the one thread that owns it
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int e = tid; e < BM * BK; e += NT) {
+            const int r = e / BK, kk = e % BK;
+            const int m = m0 + r;
+            float val = 0.f;
+            if (m < M && k0 + kk < K) {
+                const int src_row = rowsel ? rowsel[m] : m;
+                val = A[(size_t)src_row * K + k0 + kk];
+            }
+            As[kk][r] = val;
+        }
+        for (int e = tid; e < BK * BN; e += NT) {
+            const int kk = e / BN, c = e % BN;
+            Ws[kk][c] = (k0 + kk < K && n0 + c < N) ? W[(size_t)(k0 + kk) * N + n0 + c] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; i++) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; j++) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) {
+                    if (STRICT) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], w[j]));
+                    else acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; j++) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            float val = acc[i][j];
+            if (R) val = __fadd_rn(R[(size_t)m * N + n], val);
+            C[(size_t)m * N + n] = val;
+        }
+    }
+}
+
+// Greedy argmax per row, ties -> lowest index (argmaxLogitsGreedy,
+// src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:288-299).
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ out) {
+    __shared__ float bv[8];
+    __shared__ int bi[8];
+    const float *row = logits + (size_t)blockIdx.x * V;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int j = threadIdx.x; j < V; j += blockDim.x) {
+        const float v = row[j];
+        if (v > best || (v == best && j < idx)) best = v, idx = j;
+    }
+    if (idx == 0x7fffffff) idx = 0;  // all NaN / -inf: the reference starts from index 0
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+        if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+    }
+    if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = best, bi[threadIdx.x >> 5] = idx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) best = bv[w], idx = bi[w];
+        out[blockIdx.x] = idx;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+static int32_t gemm(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
+                    const float *const *R, const int *rowsel = nullptr) {
+    GemmBatch B;
+    for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
+    cudaStream_t st = m->ctx->stream;
+    if (M <= 16) {
+        dim3 grid((N + 63) / 64, (M + 15) / 16, nb);
+        if (m->strict) gemm_kernel<16, 64, 1, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+        else gemm_kernel<16, 64, 1, 4, false><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+    } else if (M <= 128) {
+        dim3 grid((N + 63) / 64, (M + 31) / 32, nb);
+        if (m->strict) gemm_kernel<32, 64, 2, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+        else gemm_kernel<32, 64, 2, 4, false><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+    } else {
+        dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
+        if (m->strict) gemm_kernel<64, 64, 4, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+        else gemm_kernel<64, 64, 4, 4, false><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+    }
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
+static int num_tensors(const Model *m) { return 4 + 9 * m->layers; }
+
+static float *tensor_ptr(Model *m, int idx, uint64_t *count) {
+    const uint64_t D = m->d_model, F = m->d_ff, V = m->vocab;
+    const int n = num_tensors(m);
+    if (idx == 0) { *count = V * D; return m->tok; }
+    if (idx == 1) { *count = (uint64_t)m->max_seq * D; return m->pos; }
+    if (idx == n - 2) { *count = D; return m->norm_final; }
+    if (idx == n - 1) { *count = D * V; return m->lm_head; }
+    LayerW &y = m->L[(size_t)((idx - 2) / 9)];
+    switch ((idx - 2) % 9) {
+        case 0: *count = D * D; return y.wq;
+        case 1: *count = D * D; return y.wk;
+        case 2: *count = D * D; return y.wv;
+        case 3: *count = D * D; return y.wo;
+        case 4: *count = D * F; return y.w1;
+        case 5: *count = F * D; return y.w2;
+        case 6: *count = D * F; return y.w3;
+        case 7: *count = D; return y.norm1;
+        default: *count = D; return y.norm2;
+    }
+}
+
+static int32_t ensure_logits(Model *m, int rows) {
+    if (rows <= m->logit_rows) return JGPT_OK;
+    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    if (m->logits) JGPT_CUDA_TRY(cudaFree(m->logits));
+    m->logits = nullptr, m->logit_rows = 0;
+    JGPT_CUDA_TRY(cudaMalloc(&m->logits, sizeof(float) * (size_t)rows * m->vocab));
+    m->logit_rows = rows;
+    return JGPT_OK;
+}
+
+// One decoder block over `rows` rows already in m->x.  Attention is supplied by the caller.
+template <class AttnFn>
+static int32_t run_layers(Model *m, int rows, AttnFn &&attn) {
+    const int D = m->d_model, F = m->d_ff;
+    cudaStream_t st = m->ctx->stream;
+    for (int l = 0; l < m->layers; l++) {
+        const LayerW &y = m->L[(size_t)l];
+        rmsnorm_kernel<<<rows, 128, 0, st>>>(m->x, y.norm1, m->xn, D, m->eps);
+        const float *Wqkv[3] = {y.wq, y.wk, y.wv};
+        float *Cqkv[3] = {m->q, m->k, m->v};
+        int32_t rc = gemm(m, m->xn, rows, D, D, 3, Wqkv, Cqkv, nullptr);
+        if (rc) return rc;
+        rc = attn(l);
+        if (rc) return rc;
+        const float *Wo[1] = {y.wo};
+        float *Co[1] = {m->x};
+        const float *Ro[1] = {m->x};  // x1 = x + attn.Wo (each element read then written by the same thread)
+        rc = gemm(m, m->att, rows, D, D, 1, Wo, Co, Ro);
+        if (rc) return rc;
+        rmsnorm_kernel<<<rows, 128, 0, st>>>(m->x, y.norm2, m->xn, D, m->eps);
+        const float *W13[2] = {y.w1, y.w3};
+        float *C13[2] = {m->h1, m->g};
+        rc = gemm(m, m->xn, rows, D, F, 2, W13, C13, nullptr);
+        if (rc) return rc;
+        const long long nf = (long long)rows * F;
+        swiglu_kernel<<<(unsigned)((nf + 255) / 256), 256, 0, st>>>(m->h1, m->g, nf);
+        const float *W2[1] = {y.w2};
+        rc = gemm(m, m->h1, rows, F, D, 1, W2, Co, Ro);
+        if (rc) return rc;
+    }
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
+// Final norm + LM head over the rows listed in d_rowsel[0..n_sel) (or all rows), then argmax.
+static int32_t lm_head(Model *m, int rows, int n_sel) {
+    const int D = m->d_model;
+    cudaStream_t st = m->ctx->stream;
+    rmsnorm_kernel<<<rows, 128, 0, st>>>(m->x, m->norm_final, m->xn, D, m->eps);
+    const int out_rows = n_sel > 0 ? n_sel : rows;
+    int32_t rc = ensure_logits(m, out_rows);
+    if (rc) return rc;
+    const float *W[1] = {m->lm_head};
+    float *C[1] = {m->logits};
+    rc = gemm(m, m->xn, out_rows, D, m->vocab, 1, W, C, nullptr, n_sel > 0 ? m->d_rowsel : nullptr);
+    if (rc) return rc;
+    argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
+}  // namespace jgpt
+
+using namespace jgpt;
+
+#define GET_MODEL(m, h)                                         \
+    Model *m = model_registry().get(h);                         \
+    JGPT_REQUIRE(m, JGPT_ERR_BAD_HANDLE, "bad model handle");   \
+    JGPT_CUDA_TRY(make_current(m->ctx))
+
+static int32_t check_pool(const Model *m, const Pool *p) {
+    JGPT_REQUIRE(p, JGPT_ERR_BAD_HANDLE, "bad kvpool handle");
+    JGPT_REQUIRE(p->ctx == m->ctx, JGPT_ERR_INVALID_ARGUMENT, "model and KV pool live on different contexts");
+    // GptKvForward: "KvCacheGpu layer count mismatch" -> IllegalArgumentException
+    JGPT_REQUIRE(p->layers == m->layers && p->heads == m->heads && p->dhead == m->d_model / m->heads, JGPT_ERR_INVALID_ARGUMENT,
+                 "KV pool geometry (layers %d, heads %d, dhead %d) does not match the model", p->layers, p->heads, p->dhead);
+    return JGPT_OK;
+}
+
+extern "C" {
+
+int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int32_t d_model, int32_t heads, int32_t layers,
+                          int32_t d_ff, float rms_eps, int32_t max_rows, jgpt_model *out) {
+    Ctx *c = ctx_registry().get(ctxh);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(out, JGPT_ERR_INVALID_ARGUMENT, "out is null");
+    JGPT_REQUIRE(vocab > 0 && max_seq_len > 0 && d_model > 0 && heads > 0 && layers > 0 && d_ff > 0 && max_rows > 0,
+                 JGPT_ERR_INVALID_ARGUMENT, "model dimensions must be positive");
+    JGPT_REQUIRE(d_model % heads == 0, JGPT_ERR_INVALID_ARGUMENT, "d_model must be divisible by num_heads");
+    JGPT_REQUIRE(d_model % 4 == 0, JGPT_ERR_UNSUPPORTED, "d_model must be a multiple of 4");
+    JGPT_CUDA_TRY(make_current(c));
+    Model *m = new Model();
+    m->ctx = c, m->vocab = vocab, m->max_seq = max_seq_len, m->d_model = d_model, m->heads = heads, m->layers = layers;
+    m->d_ff = d_ff, m->eps = rms_eps, m->max_rows = max_rows;
+    m->strict = env_int("JGPT_B200_STRICT_GEMM", 1);
+    const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
+    auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
+    JGPT_CUDA_TRY(A(&m->tok, V * D));
+    JGPT_CUDA_TRY(A(&m->pos, (size_t)max_seq_len * D));
+    JGPT_CUDA_TRY(A(&m->norm_final, D));
+    JGPT_CUDA_TRY(A(&m->lm_head, D * V));
+    m->L.resize((size_t)layers);
+    for (auto &y : m->L) {
+        JGPT_CUDA_TRY(A(&y.wq, D * D));
+        JGPT_CUDA_TRY(A(&y.wk, D * D));
+        JGPT_CUDA_TRY(A(&y.wv, D * D));
+        JGPT_CUDA_TRY(A(&y.wo, D * D));
+        JGPT_CUDA_TRY(A(&y.w1, D * F));
+        JGPT_CUDA_TRY(A(&y.w2, F * D));
+        JGPT_CUDA_TRY(A(&y.w3, D * F));
+        JGPT_CUDA_TRY(A(&y.norm1, D));
+        JGPT_CUDA_TRY(A(&y.norm2, D));
+    }
+    JGPT_CUDA_TRY(A(&m->x, R * D));
+    JGPT_CUDA_TRY(A(&m->xn, R * D));
+    JGPT_CUDA_TRY(A(&m->q, R * D));
+    JGPT_CUDA_TRY(A(&m->k, R * D));
+    JGPT_CUDA_TRY(A(&m->v, R * D));
+    JGPT_CUDA_TRY(A(&m->att, R * D));
+    JGPT_CUDA_TRY(A(&m->h1, R * F));
+    JGPT_CUDA_TRY(A(&m->g, R * F));
+    JGPT_CUDA_TRY(cudaMalloc(&m->d_idx, sizeof(int) * 5 * R));
+    JGPT_CUDA_TRY(cudaHostAlloc(&m->h_idx, sizeof(int) * 5 * R, cudaHostAllocDefault));
+    JGPT_CUDA_TRY(cudaMalloc(&m->d_next, sizeof(int) * R));
+    JGPT_CUDA_TRY(cudaHostAlloc(&m->h_next, sizeof(int) * R, cudaHostAllocDefault));
+    JGPT_CUDA_TRY(cudaMalloc(&m->d_rowsel, sizeof(int) * R));
+    *out = model_registry().add(m);
+    return JGPT_OK;
+}
+
+int32_t jgpt_model_destroy(jgpt_model h) {
+    GET_MODEL(m, h);
+    cudaStreamSynchronize(m->ctx->stream);
+    model_registry().remove(m);
+    cudaFree(m->tok), cudaFree(m->pos), cudaFree(m->norm_final), cudaFree(m->lm_head);
+    for (auto &y : m->L) {
+        cudaFree(y.wq), cudaFree(y.wk), cudaFree(y.wv), cudaFree(y.wo), cudaFree(y.w1), cudaFree(y.w2), cudaFree(y.w3);
+        cudaFree(y.norm1), cudaFree(y.norm2);
+    }
+    cudaFree(m->x), cudaFree(m->xn), cudaFree(m->q), cudaFree(m->k), cudaFree(m->v), cudaFree(m->att), cudaFree(m->h1);
+    cudaFree(m->g), cudaFree(m->logits), cudaFree(m->d_idx), cudaFree(m->d_next), cudaFree(m->d_rowsel);
+    cudaFreeHost(m->h_idx), cudaFreeHost(m->h_next);
+    delete m;
+    return JGPT_OK;
+}
+
+int32_t jgpt_model_num_tensors(jgpt_model h, int32_t *n_out) {
+    GET_MODEL(m, h);
+    JGPT_REQUIRE(n_out, JGPT_ERR_INVALID_ARGUMENT, "null output");
+    *n_out = num_tensors(m);
+    return JGPT_OK;
+}
+
+int32_t jgpt_model_set_tensor(jgpt_model h, int32_t idx, const float *host, uint64_t n_floats) {
+    GET_MODEL(m, h);
+    JGPT_REQUIRE(idx >= 0 && idx < num_tensors(m), JGPT_ERR_OUT_OF_RANGE, "tensor %d outside [0,%d)", idx, num_tensors(m));
+    uint64_t count = 0;
+    float *dst = tensor_ptr(m, idx, &count);
+    JGPT_REQUIRE(host && n_floats == count, JGPT_ERR_INVALID_ARGUMENT, "tensor %d holds %llu floats, got %llu", idx,
+                 (unsigned long long)count, (unsigned long long)n_floats);
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dst, host, sizeof(float) * count, cudaMemcpyHostToDevice, m->ctx->stream));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    return JGPT_OK;
+}
+
+// veles.weights.v1 (reader: src/main/java/com/veles/llm/jgpt/model/GptModelWeightsLoader.java:58-81;
+// writer: training/LlmTrainerCheckpointIo.java:129-140): Java writeUTF tag, int32 BE tensor count, per tensor
+// int32 BE rank, dims, big-endian fp32 payload.
+int32_t jgpt_model_load_weights(jgpt_model h, const char *path) {
+    GET_MODEL(m, h);
+    JGPT_REQUIRE(path, JGPT_ERR_INVALID_ARGUMENT, "null path");
+    FILE *f = fopen(path, "rb");
+    if (!f) return fail(JGPT_ERR_IO, "cannot open %s", path);
+    auto rd32 = [&](uint32_t *v) {
+        unsigned char b[4];
+        if (fread(b, 1, 4, f) != 4) return false;
+        *v = ((uint32_t)b[0] << 24) | ((uint32_t)b[1] << 16) | ((uint32_t)b[2] << 8) | b[3];
+        return true;
+    };
+    unsigned char hdr[18];
+    if (fread(hdr, 1, 18, f) != 18 || hdr[0] != 0 || hdr[1] != 16 || memcmp(hdr + 2, "veles.weights.v1", 16) != 0) {
+        fclose(f);
+        return fail(JGPT_ERR_IO, "%s is not a veles.weights.v1 file", path);
+    }
+    uint32_t n = 0;
+    if (!rd32(&n) || (int)n != num_tensors(m)) {
+        fclose(f);
+        return fail(JGPT_ERR_INVALID_ARGUMENT, "%s holds %u tensors, the model has %d", path, n, num_tensors(m));
+    }
+    std::vector<float> buf;
+    for (int i = 0; i < (int)n; i++) {
+        uint64_t count = 0;
+        float *dst = tensor_ptr(m, i, &count);
+        uint32_t rank = 0;
+        uint64_t prod = 1;
+        bool ok = rd32(&rank) && rank >= 1 && rank <= 4;
+        for (uint32_t d = 0; ok && d < rank; d++) {
+            uint32_t dim = 0;
+            ok = rd32(&dim);
+            prod *= dim;
+        }
+        if (!ok || prod != count) {
+            fclose(f);
+            return fail(JGPT_ERR_INVALID_ARGUMENT, "%s: tensor %d has %llu elements, expected %llu", path, i,
+                        (unsigned long long)prod, (unsigned long long)count);
+        }
+        buf.resize(count);
+        if (fread(buf.data(), 4, count, f) != count) {
+            fclose(f);
+            return fail(JGPT_ERR_IO, "%s: truncated in tensor %d", path, i);
+        }
+        for (uint64_t j = 0; j < count; j++) {
+            uint32_t u;
+            memcpy(&u, &buf[j], 4);
+            u = __builtin_bswap32(u);
+            memcpy(&buf[j], &u, 4);
+        }
+        cudaError_t e = cudaMemcpy(dst, buf.data(), sizeof(float) * count, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            fclose(f);
+            return fail(JGPT_ERR_CUDA, "upload of tensor %d: %s", i, cudaGetErrorString(e));
+        }
+    }
+    fclose(f);
+    return JGPT_OK;
+}
+
+// Batched prefill: n sequences, sequence i = rows [seq_starts[i], seq_starts[i+1]) of ids_host, RoPE /
+// position rows rope_offsets[i] + r, cache slots 0..S_i-1.  last_logits_host [n, vocab] and
+// next_tokens_host [n] (argmax of the last row) may be NULL.  Sets every sequence's length to S_i.
+int32_t jgpt_forward_prefill_batch(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_ids_host, const int32_t *seq_starts_host,
+                                   const int32_t *ids_host, const int32_t *rope_offsets_host, int32_t n, float *all_logits_host,
+                                   float *last_logits_host, int32_t *next_tokens_host) {
+    GET_MODEL(m, h);
+    Pool *p = pool_registry().get(poolh);
+    int32_t rc = check_pool(m, p);
+    if (rc) return rc;
+    JGPT_REQUIRE(n >= 1 && seq_ids_host && seq_starts_host && ids_host && rope_offsets_host, JGPT_ERR_INVALID_ARGUMENT,
+                 "null pointer or empty batch");
+    const int rows = seq_starts_host[n];
+    JGPT_REQUIRE(seq_starts_host[0] == 0 && rows >= 1, JGPT_ERR_INVALID_ARGUMENT, "seq_starts must begin at 0");
+    JGPT_REQUIRE(rows <= m->max_rows, JGPT_ERR_INVALID_ARGUMENT, "%d prompt rows exceed the model workspace (%d rows)", rows,
+                 m->max_rows);
+    JGPT_REQUIRE(!all_logits_host || n == 1, JGPT_ERR_INVALID_ARGUMENT, "all-row logits are available for one sequence at a time");
+    int *ids = m->h_idx, *posrow = m->h_idx + rows;  // packed [2][rows]
+    for (int i = 0; i < n; i++) {
+        const int s = seq_ids_host[i], S = seq_starts_host[i + 1] - seq_starts_host[i], ro = rope_offsets_host[i];
+        JGPT_REQUIRE(s >= 0 && s < p->max_seqs && p->seqs[(size_t)s].used, JGPT_ERR_OUT_OF_RANGE, "sequence %d is not allocated", s);
+        // forwardPrefill: seq_len > max_seq_len -> IllegalArgumentException; position rows must stay inside the table
+        JGPT_REQUIRE(S >= 1 && S <= m->max_seq, JGPT_ERR_INVALID_ARGUMENT, "seq_len %d > max_seq_len %d", S, m->max_seq);
+        JGPT_REQUIRE(ro >= 0 && ro + S <= m->max_seq, JGPT_ERR_INVALID_ARGUMENT, "position rows [%d, %d) outside the table of %d", ro,
+                     ro + S, m->max_seq);
+        for (int r = 0; r < S; r++) {
+            const int id = ids_host[seq_starts_host[i] + r];
+            JGPT_REQUIRE(id >= 0 && id < m->vocab, JGPT_ERR_INVALID_ARGUMENT, "token id %d outside [0,%d)", id, m->vocab);
+            ids[seq_starts_host[i] + r] = id;
+            posrow[seq_starts_host[i] + r] = ro + r;
+        }
+    }
+    for (int i = 0; i < n; i++) {
+        rc = jgpt_seq_reserve(poolh, seq_ids_host[i], seq_starts_host[i + 1] - seq_starts_host[i]);
+        if (rc) return rc;
+    }
+    cudaStream_t st = m->ctx->stream;
+    JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 2 * (size_t)rows, cudaMemcpyHostToDevice, st));
+    embed_pos_kernel<<<rows, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + rows, m->x, m->d_model);
+    rc = run_layers(m, rows, [&](int l) {
+        return launch_attn_prefill(p, l, m->q, m->k, m->v, seq_ids_host, seq_starts_host, rope_offsets_host, n, m->att);
+    });
+    if (rc) return rc;
+    int n_sel = 0;
+    if (!all_logits_host) {
+        std::vector<int> sel((size_t)n);
+        for (int i = 0; i < n; i++) sel[(size_t)i] = seq_starts_host[i + 1] - 1;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_rowsel, sel.data(), sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+        n_sel = n;
+    }
+    rc = lm_head(m, rows, n_sel);
+    if (rc) return rc;
+    const int out_rows = n_sel ? n_sel : rows;
+    if (all_logits_host)
+        JGPT_CUDA_TRY(cudaMemcpyAsync(all_logits_host, m->logits, sizeof(float) * (size_t)rows * m->vocab, cudaMemcpyDeviceToHost, st));
+    if (last_logits_host) {
+        const float *src = all_logits_host ? m->logits + (size_t)(rows - 1) * m->vocab : m->logits;
+        const int nrow = all_logits_host ? 1 : n;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(last_logits_host, src, sizeof(float) * (size_t)nrow * m->vocab, cudaMemcpyDeviceToHost, st));
+    }
+    JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)out_rows, cudaMemcpyDeviceToHost, st));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+    if (next_tokens_host)
+        for (int i = 0; i < n; i++) next_tokens_host[i] = all_logits_host ? m->h_next[rows - 1] : m->h_next[i];
+    for (int i = 0; i < n; i++) {  // cache.setLength(seqLen)
+        rc = jgpt_seq_set_length(poolh, seq_ids_host[i], seq_starts_host[i + 1] - seq_starts_host[i]);
+        if (rc) return rc;
+    }
+    return JGPT_OK;
+}
+
+int32_t jgpt_forward_prefill(jgpt_model h, jgpt_kvpool poolh, int32_t seq, const int32_t *ids_host, int32_t S, int32_t rope_offset,
+                             float *logits_host, float *last_logits_host, int32_t *next_token_host) {
+    const int32_t starts[2] = {0, S};
+    JGPT_REQUIRE(S >= 1, JGPT_ERR_INVALID_ARGUMENT, "empty prompt");
+    return jgpt_forward_prefill_batch(h, poolh, &seq, starts, ids_host, &rope_offset, 1, logits_host, last_logits_host,
+                                      next_token_host);
+}
+
+int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_ids_host, const int32_t *ids_host,
+                            const int32_t *cache_len_before_host, const int32_t *rope_pos_host, int32_t n, float *logits_host,
+                            int32_t *next_tokens_host) {
+    GET_MODEL(m, h);
+    Pool *p = pool_registry().get(poolh);
+    int32_t rc = check_pool(m, p);
+    if (rc) return rc;
+    JGPT_REQUIRE(n >= 1 && seq_ids_host && ids_host && cache_len_before_host && rope_pos_host, JGPT_ERR_INVALID_ARGUMENT,
+                 "null pointer or empty batch");
+    JGPT_REQUIRE(n <= m->max_rows, JGPT_ERR_INVALID_ARGUMENT, "%d rows exceed the model workspace (%d rows)", n, m->max_rows);
+    const int R = n;  // packed [5][n]: ids, position rows, sequence ids, RoPE positions, lengths
+    int *ids = m->h_idx, *posrow = ids + R, *sid = posrow + R, *rp = sid + R, *lens = rp + R;
+    int max_len = 1;
+    for (int i = 0; i < n; i++) {
+        const int s = seq_ids_host[i];
+        JGPT_REQUIRE(s >= 0 && s < p->max_seqs && p->seqs[(size_t)s].used, JGPT_ERR_OUT_OF_RANGE, "sequence %d is not allocated", s);
+        for (int j = 0; j < i; j++)
+            JGPT_REQUIRE(seq_ids_host[j] != s, JGPT_ERR_INVALID_ARGUMENT, "sequence %d appears twice in one decode step", s);
+        // forwardDecode: cache.length() != cacheLenBefore -> IllegalStateException; full cache -> IllegalStateException
+        JGPT_REQUIRE(p->seqs[(size_t)s].len == cache_len_before_host[i], JGPT_ERR_ILLEGAL_STATE, "KV cache length %d != cacheLenBefore %d",
+                     p->seqs[(size_t)s].len, cache_len_before_host[i]);
+        JGPT_REQUIRE(cache_len_before_host[i] < m->max_seq && cache_len_before_host[i] < p->max_blocks_per_seq * kBlockTokens,
+                     JGPT_ERR_ILLEGAL_STATE, "KV cache of sequence %d is full (%d tokens)", s, cache_len_before_host[i]);
+        JGPT_REQUIRE(ids_host[i] >= 0 && ids_host[i] < m->vocab, JGPT_ERR_INVALID_ARGUMENT, "token id %d outside [0,%d)", ids_host[i],
+                     m->vocab);
+        JGPT_REQUIRE(rope_pos_host[i] >= 0 && rope_pos_host[i] < m->max_seq && rope_pos_host[i] < p->max_positions,
+                     JGPT_ERR_INVALID_ARGUMENT, "position %d outside the table of %d rows", rope_pos_host[i], m->max_seq);
+        ids[i] = ids_host[i], posrow[i] = rope_pos_host[i], sid[i] = s, rp[i] = rope_pos_host[i], lens[i] = cache_len_before_host[i] + 1;
+        max_len = std::max(max_len, lens[i]);
+    }
+    for (int i = 0; i < n; i++) {
+        rc = jgpt_seq_reserve(poolh, seq_ids_host[i], cache_len_before_host[i] + 1);
+        if (rc) return rc;
+    }
+    cudaStream_t st = m->ctx->stream;
+    JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+    embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model);
+    rc = run_layers(m, n, [&](int l) {
+        return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, max_len, m->att);
+    });
+    if (rc) return rc;
+    rc = lm_head(m, n, 0);
+    if (rc) return rc;
+    if (logits_host)
+        JGPT_CUDA_TRY(cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * (size_t)n * m->vocab, cudaMemcpyDeviceToHost, st));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+    if (next_tokens_host)
+        for (int i = 0; i < n; i++) next_tokens_host[i] = m->h_next[i];
+    for (int i = 0; i < n; i++) {  // cache.setLength(cacheLenBefore + 1)
+        rc = jgpt_seq_set_length(poolh, seq_ids_host[i], cache_len_before_host[i] + 1);
+        if (rc) return rc;
+    }
+    return JGPT_OK;
+}
+
+// sampleNextToken on host logits (src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:208-286):
+// temperature divide, stable top-k by (logit desc, index asc), softmax, inverse CDF with the supplied uniform
+// draw (the reference draws from an unseeded ThreadLocalRandom); greedy when temperature <= 0.
+int32_t jgpt_sample_next_token(const float *logits_host, int32_t vocab, float temperature, int32_t top_k, float u01,
+                               int32_t *token_out) {
+    JGPT_REQUIRE(logits_host && vocab > 0 && token_out, JGPT_ERR_INVALID_ARGUMENT, "null pointer or empty vocabulary");
+    std::vector<float> z(logits_host, logits_host + vocab);
+    if (temperature != 1.0f && temperature > 0)
+        for (auto &x : z) x /= temperature;
+    if (top_k > 0 && top_k < vocab) {
+        std::vector<int> order((size_t)vocab);
+        for (int i = 0; i < vocab; i++) order[(size_t)i] = i;
+        std::partial_sort(order.begin(), order.begin() + top_k, order.end(),
+                          [&](int a, int b) { return z[(size_t)a] > z[(size_t)b] || (z[(size_t)a] == z[(size_t)b] && a < b); });
+        std::vector<char> keep((size_t)vocab, 0);
+        for (int i = 0; i < top_k; i++) keep[(size_t)order[(size_t)i]] = 1;
+        for (int i = 0; i < vocab; i++)
+            if (!keep[(size_t)i]) z[(size_t)i] = -INFINITY;
+    }
+    if (temperature <= 0.f) {
+        int best = 0;
+        for (int i = 1; i < vocab; i++)
+            if (z[(size_t)i] > z[(size_t)best]) best = i;
+        *token_out = best;
+        return JGPT_OK;
+    }
+    float mx = -INFINITY, sum = 0.f, cum = 0.f;
+    for (float x : z) mx = std::max(mx, x);
+    for (auto &x : z) x = (float)std::exp((double)(x - mx)), sum += x;
+    for (auto &x : z) x /= sum;
+    *token_out = vocab - 1;
+    for (int i = 0; i < vocab; i++) {
+        cum += z[(size_t)i];
+        if (u01 <= cum) {
+            *token_out = i;
+            break;
+        }
+    }
+    return JGPT_OK;
+}
+
+// GPTModel.generateGpuKv with temperature <= 0 (GptAutoregressiveGenerator.java:108-206).
+int32_t jgpt_generate_greedy(jgpt_model h, jgpt_kvpool poolh, const int32_t *prompt_host, int32_t S, int32_t max_new,
+                             int32_t *out_host, int32_t *n_sampled_out) {
+    GET_MODEL(m, h);
+    Pool *p = pool_registry().get(poolh);
+    int32_t rc = check_pool(m, p);
+    if (rc) return rc;
+    JGPT_REQUIRE(prompt_host && out_host && S >= 1 && max_new >= 0, JGPT_ERR_INVALID_ARGUMENT, "bad prompt or output buffer");
+    for (int i = 0; i < S + max_new; i++) out_host[i] = i < S ? prompt_host[i] : 0;
+    if (n_sampled_out) *n_sampled_out = 0;
+    if (max_new == 0) return JGPT_OK;
+    int32_t seq = -1;
+    rc = jgpt_seq_alloc(poolh, &seq);  // new KvCacheGpu(...)
+    if (rc) return rc;
+    int n = 0;
+    int32_t tok = 0;
+    rc = jgpt_forward_prefill(h, poolh, seq, prompt_host, S, 0, nullptr, nullptr, &tok);
+    if (rc == JGPT_OK) {
+        out_host[S] = tok, n = 1;
+        for (int j = 1; j < max_new && tok != 0; j++) {
+            const int cur = S + j;
+            if (cur > m->max_seq) {  // sliding window: clear, re-prefill out[cur-maxSeq : maxSeq) at ropeOffset = start
+                const int start = cur - m->max_seq, len = m->max_seq - start;
+                if (len <= 0) {
+                    rc = fail(JGPT_ERR_ILLEGAL_STATE, "sliding window: startIdx=%d maxSeqLen=%d", start, m->max_seq);
+                    break;
+                }
+                rc = jgpt_seq_clear(poolh, seq, 0);
+                if (rc) break;
+                rc = jgpt_forward_prefill(h, poolh, seq, out_host + start, len, start, nullptr, nullptr, &tok);
+            } else {
+                const int32_t prev = out_host[S + j - 1], len_before = p->seqs[(size_t)seq].len, rope = S + j - 1;
+                rc = jgpt_forward_decode(h, poolh, &seq, &prev, &len_before, &rope, 1, nullptr, &tok);
+            }
+            if (rc) break;
+            out_host[cur] = tok, n++;
+        }
+    }
+    const std::string keep = last_error_ref();
+    jgpt_seq_free(poolh, seq);  // cache.close()
+    if (rc) last_error_ref() = keep;
+    if (n_sampled_out) *n_sampled_out = n;
+    return rc;
+}
+
+}  // extern "C"
