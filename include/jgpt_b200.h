@@ -253,6 +253,32 @@ JGPT_API int32_t jgpt_generate_greedy(jgpt_model model, jgpt_kvpool pool, const 
                                       int32_t max_new, int32_t *out_host, int32_t *n_sampled_out);
 
 
+/* ---------------------------------------------------------------------------------------------
+ * Continuous-batching scheduler (one model + one pool on one GPU).  The reference generates one
+ * sequence per call with a fresh KvCacheGpu (J/model/GptAutoregressiveGenerator.java:108-206); the
+ * per-sequence rules are kept (greedy argmax, lowest-index ties, stop on sampled id 0), the batching
+ * policy is new and deterministic: FIFO admission that reserves ceil((prompt + max_new - 1)/16)
+ * blocks up front, LRU eviction of finished sequences when the pool or the sequence slots run
+ * short, one batched prefill for the requests admitted in a step, one batched decode step for the
+ * requests already running.
+ * ------------------------------------------------------------------------------------------- */
+JGPT_API int32_t jgpt_sched_create(jgpt_model model, jgpt_kvpool pool, int32_t max_running,
+                                   int32_t max_rows_per_call, int32_t max_seq_len, uint64_t *sched_out);
+JGPT_API int32_t jgpt_sched_destroy(uint64_t sched);
+/* Queue a request: prompt of S ids, up to max_new sampled tokens.  JGPT_ERR_INVALID_ARGUMENT when
+ * S + max_new - 1 exceeds the context (there is no sliding window while batching). */
+JGPT_API int32_t jgpt_sched_submit(uint64_t sched, const int32_t *prompt_host, int32_t S, int32_t max_new,
+                                   int32_t *req_id_out);
+/* One step.  pairs_out receives (request id, token) for each token sampled in this step. */
+JGPT_API int32_t jgpt_sched_step(uint64_t sched, int32_t *pairs_out, int32_t cap_pairs, int32_t *n_pairs_out,
+                                 int32_t *n_running_out, int32_t *n_waiting_out);
+/* Tokens sampled so far for a request; state 0 waiting, 1 running, 2 finished; its sequence slot. */
+JGPT_API int32_t jgpt_sched_result(uint64_t sched, int32_t req_id, int32_t *tokens_out, int32_t cap,
+                                   int32_t *n_out, int32_t *state_out, int32_t *seq_out);
+/* Event log, flat (type, a, b) triples: 1 admit(request, sequence slot), 2 evict(sequence slot,
+ * request), 3 finish(request, tokens sampled). */
+JGPT_API int32_t jgpt_sched_events(uint64_t sched, int32_t *out, int32_t cap_ints, int32_t *n_ints_out);
+
 /* Decode attention that allocates nothing.  No counterpart in the reference.
  *
  * Same computation as jgpt_attn_decode for ONE layer, but the split-K scratch (partial softmax

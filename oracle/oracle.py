@@ -418,4 +418,84 @@ class PagedAllocatorRef:
         return victims
 
 
+class ContinuousBatchRef:
+    """Written specification of the continuous-batching policy, driven by precomputed per-request token
+    streams (a request's tokens do not depend on what it is batched with).
+
+    step(): FIFO admission reserving ceil((prompt + max_new - 1)/bt) blocks at once, evicting finished
+    sequences least-recently-used first (one at a time, lower slot on ties) until blocks and a sequence slot
+    are available, no overtaking; the admitted requests get their first token (prefill); the requests that
+    were already running get one more token; a request finishes at max_new tokens or on token 0.
+    Events: (1, request, slot) admit, (2, slot, request) evict, (3, request, n_tokens) finish."""
+
+    def __init__(self, alloc: PagedAllocatorRef, max_running, max_rows, streams):
+        self.a, self.max_running, self.max_rows, self.streams = alloc, min(max_running, max_rows), max_rows, streams
+        self.reqs, self.waiting, self.running, self.events = [], [], [], []
+        self.owner = {}
+
+    def submit(self, prompt_len, max_new):
+        self.reqs.append(dict(S=prompt_len, max_new=max_new, out=[], seq=-1, state=0))
+        self.waiting.append(len(self.reqs) - 1)
+        return len(self.reqs) - 1
+
+    def _make_room(self, need):
+        a = self.a
+        while True:
+            slot_ok = len(a.tables) < a.max_seqs
+            if len(a.free) >= need and slot_ok:
+                return True
+            cand = sorted((t, s) for s, t in a.tick.items() if a.evictable[s])
+            if not cand:
+                return False
+            victim = cand[0][1]
+            self.events.append((2, victim, self.owner.pop(victim)))
+            a.seq_free(victim)
+
+    def step(self):
+        a, produced = self.a, []
+        decoding = list(self.running)
+        admitted = []
+        while self.waiting and len(self.running) < self.max_running:
+            rid = self.waiting[0]
+            r = self.reqs[rid]
+            need = -(-(r["S"] + r["max_new"] - 1) // a.bt)
+            if not self._make_room(need):
+                break
+            seq = a.seq_alloc()
+            assert a.reserve(seq, r["S"] + r["max_new"] - 1)
+            r["seq"], r["state"] = seq, 1
+            self.owner[seq] = rid
+            self.waiting.pop(0)
+            self.running.append(rid)
+            admitted.append(rid)
+            self.events.append((1, rid, seq))
+        for rid in admitted:  # prefill: set_length in admission order
+            r = self.reqs[rid]
+            a.touch(r["seq"])
+            a.length[r["seq"]] = r["S"]
+        for rid in admitted:
+            r = self.reqs[rid]
+            r["out"].append(int(self.streams[rid][0]))
+            produced.append((rid, r["out"][-1]))
+        for rid in decoding:
+            r = self.reqs[rid]
+            a.touch(r["seq"])
+            a.length[r["seq"]] += 1
+        for rid in decoding:
+            r = self.reqs[rid]
+            r["out"].append(int(self.streams[rid][len(r["out"])]))
+            produced.append((rid, r["out"][-1]))
+        still = []
+        for rid in self.running:
+            r = self.reqs[rid]
+            if len(r["out"]) >= r["max_new"] or r["out"][-1] == 0:
+                r["state"] = 2
+                a.mark_evictable(r["seq"])
+                self.events.append((3, rid, len(r["out"])))
+            else:
+                still.append(rid)
+        self.running = still
+        return produced
+
+
 _ = OrderedDict  # (kept for callers that build ordered fixtures)
