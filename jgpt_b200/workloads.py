@@ -1,0 +1,213 @@
+"""GPU-side runners for the secondary benchmark workloads (`bench.py --workload ...`): the JGPT-35M greedy
+decode, the batch-32 x 1024 prefill, continuous batching of 256 requests and the long-context decode
+attention.  Each returns a dict that bench.py prints as one JSON line.  Inputs are seeded synthetic tensors
+of the stated shapes (there is no trained checkpoint or dataset)."""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+
+from .kv_cache import KvPool
+from .model import GPTModel
+from .runtime import Event
+from .scheduler import ContinuousBatcher, gather_step_tokens, shard_requests
+
+VOCAB, CTX, D_MODEL, HEADS, LAYERS, D_FF, EPS = 8000, 1024, 384, 24, 12, 768, 1e-5
+DHEAD = D_MODEL // HEADS
+
+
+def jgpt35m_parameters(seed=0, std=0.02, max_seq=CTX):
+    """Parameter tensors in file order: every matrix N(0, std) from numpy default_rng(seed), RMSNorm gammas 1."""
+    rng = np.random.default_rng(seed)
+    shapes = [(VOCAB, D_MODEL), (max_seq, D_MODEL)]
+    for _ in range(LAYERS):
+        shapes += [(D_MODEL, D_MODEL)] * 4 + [(D_MODEL, D_FF), (D_FF, D_MODEL), (D_MODEL, D_FF), (D_MODEL,), (D_MODEL,)]
+    shapes += [(D_MODEL,), (D_MODEL, VOCAB)]
+    return [rng.normal(0.0, std, size=s).astype(np.float32) if len(s) == 2 else np.ones(s, np.float32) for s in shapes]
+
+
+def make_model(ctx, max_rows, max_seq=CTX):
+    m = GPTModel(ctx, VOCAB, max_seq, D_MODEL, HEADS, LAYERS, D_FF, rmsNormEps=EPS, maxRows=max_rows)
+    m.setParameters(jgpt35m_parameters(max_seq=max_seq))
+    return m
+
+
+def run_decode35m(ctx, steps_new=128, prompt_len=64, repeats=3):
+    """Batch 1: prompt of 64 ids (seed 1), 128 greedy tokens with the KV cache, through generateGpuKv."""
+    model = make_model(ctx, max_rows=CTX)
+    pool = model.newPool(n_blocks=CTX // 16, max_seqs=1)
+    prompt = np.random.default_rng(1).integers(0, VOCAB, prompt_len).astype(np.int32)
+    try:
+        model.generateGpuKv(prompt, 8, pool=pool)  # warm-up (module load, scratch sizing)
+        best_total = best_prefill = 1e30
+        out = None
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            out1 = model.generateGpuKv(prompt, 1, pool=pool)
+            t1 = time.perf_counter()
+            out = model.generateGpuKv(prompt, steps_new, pool=pool)
+            t2 = time.perf_counter()
+            best_prefill = min(best_prefill, t1 - t0)
+            best_total = min(best_total, t2 - t1)
+            assert out[prompt_len] == out1[prompt_len]
+        n_sampled = int(np.count_nonzero(out[prompt_len:])) if 0 in out[prompt_len:] else steps_new
+        decode_s = max(best_total - best_prefill, 1e-9)
+        return {
+            "workload": "JGPT-35M greedy decode, batch 1, prompt 64 (seed 1) + 128 new tokens, weights N(0,0.02) seed 0",
+            "tokens_sampled": n_sampled, "prefill_ms": best_prefill * 1e3, "total_ms": best_total * 1e3,
+            "decode_ms_per_token": decode_s / max(steps_new - 1, 1) * 1e3,
+            "decode_tokens_per_s": (steps_new - 1) / decode_s, "first_tokens": out[prompt_len:prompt_len + 8].tolist(),
+            "timing": "host wall clock around generateGpuKv (every step synchronises to read the sampled id), best of %d" % repeats,
+        }
+    finally:
+        pool.close(), model.close()
+
+
+def run_prefill(ctx, batch=32, seq_len=1024, repeats=3):
+    """Batch 32 x 1024 prompt tokens through the full model; the paged cache of all 12 layers is written."""
+    model = make_model(ctx, max_rows=batch * seq_len)
+    pool = model.newPool(n_blocks=batch * seq_len // 16, max_seqs=batch)
+    rng = np.random.default_rng(7)
+    prompts = [rng.integers(0, VOCAB, seq_len).astype(np.int32) for _ in range(batch)]
+    seqs = [pool.seq_alloc() for _ in range(batch)]
+    try:
+        model.forwardPrefillBatch(pool, seqs, prompts)  # warm-up
+        e0, e1 = Event(ctx), Event(ctx)
+        best = 1e30
+        for _ in range(repeats):
+            for s in seqs:
+                pool.clear(s, zero_fill=False)
+            ctx.synchronize()
+            e0.record()
+            _, nxt = model.forwardPrefillBatch(pool, seqs, prompts)
+            e1.record()
+            best = min(best, e0.elapsed_ms(e1))
+        # attention alone on the same shapes
+        n_rows = batch * seq_len
+        q = ctx.alloc((n_rows, D_MODEL))
+        q.copy_from(rng.standard_normal((n_rows, D_MODEL), dtype=np.float32))
+        out = ctx.alloc((n_rows, D_MODEL))
+        starts = np.arange(batch + 1, dtype=np.int32) * seq_len
+        ro = np.zeros(batch, np.int32)
+        for _ in range(2):
+            pool.attn_prefill(0, q, q, q, seqs, starts, ro, out)
+        ctx.synchronize()
+        e0.record()
+        for layer in range(LAYERS):
+            pool.attn_prefill(layer, q, q, q, seqs, starts, ro, out)
+        e1.record()
+        attn_ms = e0.elapsed_ms(e1)
+        flops = 12 * batch * HEADS * 2.0 * seq_len * seq_len * DHEAD  # causal: (4 S^2 Dh)/2 per (seq, head), 12 layers
+        return {
+            "workload": f"causal prefill filling the paged cache: batch {batch} x {seq_len}, 12 layers, 24 heads, d_head 16 (ids seed 7)",
+            "full_model_ms": best, "prompt_tokens_per_s": n_rows / (best * 1e-3),
+            "attention_append_12_layers_ms": attn_ms, "attention_tflops_causal": flops / (attn_ms * 1e-3) / 1e12,
+            "next_tokens_head": nxt[:4].tolist(), "timing": "CUDA events on the library stream, best of %d" % repeats,
+        }
+    finally:
+        pool.close(), model.close()
+
+
+def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool_fraction=0.6, max_steps=100_000):
+    """256 requests (seed 2): prompt U[32,512], target U[64,1024] new tokens clipped to the 1024 context; pool sized
+    at 60 % of the rank's total block demand; requests dealt round-robin to the ranks; sampled ids all-gathered."""
+    rng = np.random.default_rng(2)
+    p_len = rng.integers(32, 513, n_requests)
+    t_len = rng.integers(64, 1025, n_requests)
+    t_len = np.minimum(t_len, CTX - p_len + 1)
+    prompts = [rng.integers(0, VOCAB, int(n)).astype(np.int32) for n in p_len]
+    mine = shard_requests(n_requests, world, rank)
+    demand = sum(-(-(int(p_len[i]) + int(t_len[i]) - 1) // 16) for i in mine)
+    n_blocks = max(int(pool_fraction * demand), CTX // 16)
+    model = make_model(ctx, max_rows=4096)
+    pool = model.newPool(n_blocks=n_blocks, max_seqs=len(mine) + 1)
+    sched = ContinuousBatcher(model, pool, max_running=len(mine), max_rows_per_call=4096)
+    try:
+        for i in mine:
+            sched.submit(prompts[i], int(t_len[i]))
+        ctx.synchronize()
+        total_tokens, steps, done = 0, 0, False
+        t0 = time.perf_counter()
+        while steps < max_steps:
+            if not done:
+                pairs, nr, nw = sched.step()
+                done = nr == 0 and nw == 0
+            else:
+                pairs = np.zeros((0, 2), np.int32)
+            local = [(mine[int(r)], int(t)) for r, t in pairs]
+            allp = gather_step_tokens(local + ([(-1, 1)] if done else []), world, rank, max_pairs=-(-n_requests // world) + 2, dist=dist, device=device)
+            total_tokens += sum(1 for r, _ in allp if r >= 0)
+            steps += 1
+            if sum(1 for r, _ in allp if r < 0) == world:
+                break
+        el = time.perf_counter() - t0
+        ev = sched.events()
+        return {
+            "workload": f"continuous batching: {n_requests} requests (seed 2), prompt U[32,512], target U[64,1024] clipped to the "
+                        f"1024 context, KV pool {pool_fraction:.0%} of demand, round-robin over {world} GPU(s), token ids all-gathered",
+            "generated_tokens": total_tokens, "steps": steps, "seconds": el, "tokens_per_s": total_tokens / el,
+            "pool_blocks_rank0": n_blocks, "demand_blocks_rank0": demand, "evictions_rank0": sum(1 for e in ev if e[0] == 2),
+            "timing": "host wall clock over the whole run (prefills included)",
+        }
+    finally:
+        sched.close(), pool.close(), model.close()
+
+
+def run_longctx(ctx, rank, world, n_seqs_total=512, steps=20, warmup=3):
+    """Decode attention + append at long context: 512 sequences (seed 3) with lengths U[1024, 8192], RoPE positions
+    to 8192, dealt in contiguous shards to the ranks; one fused 12-layer launch per step."""
+    rng = np.random.default_rng(3)
+    lens_all = rng.integers(1024, 8193, n_seqs_total).astype(np.int32)
+    per = n_seqs_total // world
+    lens = lens_all[rank * per:(rank + 1) * per]
+    n = lens.size
+    blocks = [-(-int(l) // 16) for l in lens]
+    pool = KvPool(ctx, LAYERS, HEADS, DHEAD, sum(blocks), n, 512, max_positions=8192)
+    try:
+        seqs = []
+        for b in blocks:
+            s = pool.seq_alloc()
+            pool.reserve(s, b * 16)
+            seqs.append(s)
+        # fill with N(0,1) through the append kernel, one 32768-row slab reused for every chunk of tokens
+        slab_rows = 32768
+        ks = ctx.from_host(rng.standard_normal((slab_rows, D_MODEL), dtype=np.float32))
+        vs = ctx.from_host(rng.standard_normal((slab_rows, D_MODEL), dtype=np.float32))
+        seq_of = np.repeat(np.asarray(seqs, np.int32), lens)
+        pos_of = np.concatenate([np.arange(l, dtype=np.int32) for l in lens])
+        sd, pd = ctx.alloc((slab_rows,), np.int32), ctx.alloc((slab_rows,), np.int32)
+        for c0 in range(0, seq_of.size, slab_rows):
+            c1 = min(c0 + slab_rows, seq_of.size)
+            pad = slab_rows - (c1 - c0)
+            sd.copy_from(np.pad(seq_of[c0:c1], (0, pad)))
+            pd.copy_from(np.pad(pos_of[c0:c1], (0, pad)))
+            for layer in range(LAYERS):
+                pool.append(layer, ks, vs, sd, pd, pd, c1 - c0)
+        ctx.synchronize()
+        q = ctx.from_host(rng.standard_normal((LAYERS, n, D_MODEL), dtype=np.float32))
+        k = ctx.from_host(rng.standard_normal((LAYERS, n, D_MODEL), dtype=np.float32))
+        v = ctx.from_host(rng.standard_normal((LAYERS, n, D_MODEL), dtype=np.float32))
+        out = ctx.alloc((LAYERS, n, D_MODEL))
+        seq_d, lens_d = ctx.from_host(np.asarray(seqs, np.int32)), ctx.from_host(lens)
+        rope_d = ctx.from_host(lens - 1)
+        max_len = int(lens.max())
+
+        def step():
+            pool.attn_decode_append(0, LAYERS, q, k, v, seq_d, rope_d, lens_d, n, max_len, out)
+
+        for _ in range(warmup):
+            step()
+        ctx.synchronize()
+        e0, e1 = Event(ctx), Event(ctx)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        ms = e0.elapsed_ms(e1) / steps
+        ctx.synchronize()
+        alg = LAYERS * (int(sum(HEADS * (int(l) * DHEAD * 4 + DHEAD * 4 + DHEAD * 4) for l in lens)) + 4 * sum(blocks))
+        return {"n_seqs_rank": n, "mean_len": float(lens.mean()), "pool_GB": pool.storage()[1] / 1e9, "ms_per_step": ms,
+                "algorithmic_bytes_per_step": alg, "GBps": alg / (ms * 1e-3) / 1e9, "tokens_per_s_rank": n / (ms * 1e-3)}
+    finally:
+        pool.close()
