@@ -1,9 +1,11 @@
 // Model weights on the device and the forward step around the attention kernels: embedding + learned
 // positions, RMSNorm, fp32 projections, SwiGLU, LM head, greedy argmax, and the generation loop.
 //
-// The dense ops keep fp32 operands and accumulate every output element over k in ascending order in one
-// thread, so a projection is reproducible against a scalar CPU loop (the reference runs the same GEMMs
-// through cuBLAS under TF32 math: src/main/cpp/jgpt_cuda_jni_init_matmul.inl:67, 794, 892).
+// Projections keep fp32 operands.  Default: tensor cores with split-TF32 operands (fp32-level accuracy; the
+// reference runs the same GEMMs through cuBLAS under plain TF32 math,
+// src/main/cpp/jgpt_cuda_jni_init_matmul.inl:67, 794, 892).  JGPT_B200_STRICT_GEMM=1 selects a scalar kernel
+// that accumulates every output element over k in ascending order in one thread (mul, then add), which is
+// bit-reproducible against a scalar CPU loop.
 #include "common.cuh"
 
 #include <algorithm>
@@ -31,7 +33,7 @@ struct Model {
     int *d_next = nullptr;    // [max_rows] argmax
     int *h_next = nullptr;    // pinned
     int *d_rowsel = nullptr;  // [max_rows] rows whose logits are wanted
-    int strict = 1;           // 1: mul + add (two roundings, as a scalar loop compiled without contraction); 0: FMA
+    int strict = 0;           // 0: tensor-core 3xTF32 projections; 1: k-ordered scalar fp32 (mul + add, two roundings)
 };
 
 Registry<Model> &model_registry() {
@@ -164,6 +166,129 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_kernel(const float
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Tensor-core projections with fp32-level accuracy ("3xTF32"): each fp32 operand is split into a TF32
+// high part and a TF32 low part, and C += Ah.Bh + Ah.Bl + Al.Bh with fp32 accumulation
+// (mma.sync m16n8k8).  The dropped Al.Bl term and the truncation of the low parts are ~2^-21 relative,
+// i.e. the result differs from a k-ordered fp32 loop by rounding noise only, where plain TF32 (what the
+// reference runs its cuBLAS GEMMs with) is ~2^-11.  A tile: BM x 32 (row major, stride 36 floats),
+// W tile: 32 x BN (stride BN + 8): both fragment loads are bank-conflict free.  cp.async double buffering.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const float rem = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rem));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 128 threads = 4 warps laid out WARPS_M x WARPS_N over the BM x BN tile; needs K % 4 == 0 and N % 4 == 0.
+template <int BM, int BN, int WARPS_M, int WARPS_N>
+__global__ void __launch_bounds__(128) gemm_tc_kernel(const float *__restrict__ A, const GemmBatch B, int M, int K, int N,
+                                                      const int *__restrict__ rowsel) {
+    constexpr int BK = 32, AS = BK + 4, WS = BN + 8;
+    constexpr int WM = BM / WARPS_M, WN = BN / WARPS_N;  // warp tile
+    constexpr int MT = WM / 16, NT = WN / 8;
+    static_assert(WARPS_M * WARPS_N == 4 && WM % 16 == 0 && WN % 8 == 0, "bad warp layout");
+    __shared__ __align__(16) float As[2][BM][AS];
+    __shared__ __align__(16) float Ws[2][BK][WS];
+    const float *__restrict__ W = B.W[blockIdx.z];
+    float *C = B.C[blockIdx.z];
+    const float *R = B.R[blockIdx.z];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int wm = warp / WARPS_N, wn = warp % WARPS_N;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+
+    auto load_tiles = [&](int buf, int k0) {
+        for (int e = tid; e < BM * (BK / 4); e += 128) {  // A: BM rows x 8 chunks of 4 floats
+            const int r = e / (BK / 4), c4 = (e % (BK / 4)) * 4;
+            const int m = m0 + r;
+            const bool ok = m < M && k0 + c4 < K;
+            const int src_row = ok ? (rowsel ? rowsel[m] : m) : 0;
+            cp_async16(&As[buf][r][c4], A + (size_t)src_row * K + (ok ? k0 + c4 : 0), ok);
+        }
+        for (int e = tid; e < BK * (BN / 4); e += 128) {  // W: 32 rows x BN/4 chunks
+            const int kk = e / (BN / 4), c4 = (e % (BN / 4)) * 4;
+            const bool ok = k0 + kk < K && n0 + c4 < N;
+            cp_async16(&Ws[buf][kk][c4], W + (ok ? (size_t)(k0 + kk) * N + n0 + c4 : 0), ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f;
+
+    const int nk = (K + BK - 1) / BK;
+    load_tiles(0, 0);
+    for (int kt = 0; kt < nk; kt++) {
+        const int buf = kt & 1;
+        if (kt + 1 < nk) {
+            load_tiles(buf ^ 1, (kt + 1) * BK);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < BK; ks += 8) {
+            uint32_t ah[MT][4], al[MT][4];
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+                const int r = wm * WM + i * 16 + g;
+                split_tf32(As[buf][r][ks + t], ah[i][0], al[i][0]);
+                split_tf32(As[buf][r + 8][ks + t], ah[i][1], al[i][1]);
+                split_tf32(As[buf][r][ks + t + 4], ah[i][2], al[i][2]);
+                split_tf32(As[buf][r + 8][ks + t + 4], ah[i][3], al[i][3]);
+            }
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                const int c = wn * WN + j * 8 + g;
+                uint32_t bh0, bl0, bh1, bl1;
+                split_tf32(Ws[buf][ks + t][c], bh0, bl0);
+                split_tf32(Ws[buf][ks + t + 4][c], bh1, bl1);
+#pragma unroll
+                for (int i = 0; i < MT; i++) {
+                    mma_tf32(acc[i][j], al[i], bh0, bh1);  // small terms first
+                    mma_tf32(acc[i][j], ah[i], bl0, bl1);
+                    mma_tf32(acc[i][j], ah[i], bh0, bh1);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            const int n = n0 + wn * WN + j * 8 + 2 * t;
+            if (n >= N) continue;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; hrow++) {
+                const int m = m0 + wm * WM + i * 16 + g + hrow * 8;
+                if (m >= M) continue;
+                float2 val = make_float2(acc[i][j][2 * hrow], acc[i][j][2 * hrow + 1]);
+                if (R) {
+                    const float2 r2 = *reinterpret_cast<const float2 *>(R + (size_t)m * N + n);
+                    val.x += r2.x, val.y += r2.y;
+                }
+                *reinterpret_cast<float2 *>(C + (size_t)m * N + n) = val;
+            }
+        }
+}
+
 // Greedy argmax per row, ties -> lowest index (argmaxLogitsGreedy,
 // src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:288-299).
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ out) {
@@ -200,6 +325,20 @@ static int32_t gemm(Model *m, const float *A, int M, int K, int N, int nb, const
     GemmBatch B;
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
     cudaStream_t st = m->ctx->stream;
+    if (!m->strict && K % 4 == 0 && N % 4 == 0) {  // tensor cores, 3xTF32
+        if (M <= 16) {
+            dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
+            gemm_tc_kernel<16, 32, 1, 4><<<grid, 128, 0, st>>>(A, B, M, K, N, rowsel);
+        } else if (M <= 512) {
+            dim3 grid((N + 31) / 32, (M + 31) / 32, nb);
+            gemm_tc_kernel<32, 32, 2, 2><<<grid, 128, 0, st>>>(A, B, M, K, N, rowsel);
+        } else {
+            dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
+            gemm_tc_kernel<64, 64, 2, 2><<<grid, 128, 0, st>>>(A, B, M, K, N, rowsel);
+        }
+        JGPT_CUDA_TRY(cudaGetLastError());
+        return JGPT_OK;
+    }
     if (M <= 16) {
         dim3 grid((N + 63) / 64, (M + 15) / 16, nb);
         if (m->strict) gemm_kernel<16, 64, 1, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
@@ -334,7 +473,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     Model *m = new Model();
     m->ctx = c, m->vocab = vocab, m->max_seq = max_seq_len, m->d_model = d_model, m->heads = heads, m->layers = layers;
     m->d_ff = d_ff, m->eps = rms_eps, m->max_rows = max_rows;
-    m->strict = env_int("JGPT_B200_STRICT_GEMM", 1);
+    m->strict = env_int("JGPT_B200_STRICT_GEMM", 0);
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
