@@ -394,6 +394,8 @@ def run_secondary(args, rank, world, local_rank):
             line["cpu_baseline"] = {"value": 1.0 / dec, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
                                     "sample": "prompt 64 + 16 decode steps of the oracle (fp32, contiguous cache)",
                                     "prefill_ms": (t1 - t0) * 1e3, "first_tokens": out[64:72].tolist()}
+    elif args.workload == "decodestep":
+        line.update(W.run_decode_step(ctx, batch=args.batch, steps=max(args.steps if args.steps != 256 else 50, 2)))
     elif args.workload == "prefill":
         line.update(W.run_prefill(ctx))
     elif args.workload == "contbatch":
@@ -428,7 +430,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--quick", action="store_true", help="device-resident timing only (used under a profiler)")
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "prefill", "contbatch", "longctx"],
+    ap.add_argument("--batch", type=int, default=64, help="sequences per step for --workload decodestep")
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx"],
                     help="microbench (default) is the headline KV-append + decode-attention step; the others are the "
                          "remaining named configurations (reported, not the contract line)")
     args = ap.parse_args()

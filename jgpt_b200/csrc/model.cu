@@ -191,15 +191,21 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // 128 threads = 4 warps laid out WARPS_M x WARPS_N over the BM x BN tile; needs K % 4 == 0 and N % 4 == 0.
-template <int BM, int BN, int WARPS_M, int WARPS_N>
+template <int BM, int BN, int STAGES>
+constexpr size_t gemm_tc_smem_bytes() { return sizeof(float) * (size_t)STAGES * (BM * (32 + 4) + 32 * (BN + 8)); }
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const float *__restrict__ A, const GemmBatch B, int M, int K, int N,
                                                       const int *__restrict__ rowsel) {
     constexpr int BK = 32, AS = BK + 4, WS = BN + 8;
     constexpr int WM = BM / WARPS_M, WN = BN / WARPS_N;  // warp tile
     constexpr int MT = WM / 16, NT = WN / 8;
-    static_assert(WARPS_M * WARPS_N == 4 && WM % 16 == 0 && WN % 8 == 0, "bad warp layout");
-    __shared__ __align__(16) float As[2][BM][AS];
-    __shared__ __align__(16) float Ws[2][BK][WS];
+    static_assert(WARPS_M * WARPS_N == 4 && WM % 16 == 0 && WN % 8 == 0 && STAGES >= 2, "bad tile configuration");
+    // STAGES k-tiles in flight: at decode sizes the whole product is a handful of tiles, so the kernel's time
+    // is one memory latency plus the MMAs instead of one latency per tile.
+    extern __shared__ __align__(16) float gemm_smem[];
+    float (*As)[BM][AS] = reinterpret_cast<float (*)[BM][AS]>(gemm_smem);
+    float (*Ws)[BK][WS] = reinterpret_cast<float (*)[BK][WS]>(gemm_smem + (size_t)STAGES * BM * AS);
     const float *__restrict__ W = B.W[blockIdx.z];
     float *C = B.C[blockIdx.z];
     const float *R = B.R[blockIdx.z];
@@ -223,25 +229,30 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const float *__restrict__ 
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    float acc[MT][NT][4];
+    // Two accumulators per output tile: the big term (Ah.Bh) and the two correction terms.  They are summed in
+    // the epilogue; keeping them apart shortens the dependent MMA chain per k-tile from 12 to 8 / 4 instructions.
+    float acc[MT][NT][4], cor[MT][NT][4];
 #pragma unroll
     for (int i = 0; i < MT; i++)
 #pragma unroll
         for (int j = 0; j < NT; j++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f;
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f, cor[i][j][e] = 0.f;
 
     const int nk = (K + BK - 1) / BK;
-    load_tiles(0, 0);
+    // Prologue: STAGES-1 tiles in flight.  Every iteration commits exactly one group (an empty one past the
+    // end), so "all but the newest STAGES-2 groups are complete" always means "tile kt has landed".
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        if (s < nk) load_tiles(s, s * BK);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (int kt = 0; kt < nk; kt++) {
-        const int buf = kt & 1;
-        if (kt + 1 < nk) {
-            load_tiles(buf ^ 1, (kt + 1) * BK);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();
+        const int buf = kt % STAGES;
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();  // tile kt visible to all; everyone is done with the buffer refilled below (read at kt-1)
+        if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
 #pragma unroll
         for (int ks = 0; ks < BK; ks += 8) {
             uint32_t ah[MT][4], al[MT][4];
@@ -261,13 +272,12 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const float *__restrict__ 
                 split_tf32(Ws[buf][ks + t + 4][c], bh1, bl1);
 #pragma unroll
                 for (int i = 0; i < MT; i++) {
-                    mma_tf32(acc[i][j], al[i], bh0, bh1);  // small terms first
-                    mma_tf32(acc[i][j], ah[i], bl0, bl1);
+                    mma_tf32(cor[i][j], al[i], bh0, bh1);
                     mma_tf32(acc[i][j], ah[i], bh0, bh1);
+                    mma_tf32(cor[i][j], ah[i], bl0, bl1);
                 }
             }
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < MT; i++)
@@ -279,7 +289,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const float *__restrict__ 
             for (int hrow = 0; hrow < 2; hrow++) {
                 const int m = m0 + wm * WM + i * 16 + g + hrow * 8;
                 if (m >= M) continue;
-                float2 val = make_float2(acc[i][j][2 * hrow], acc[i][j][2 * hrow + 1]);
+                float2 val = make_float2(acc[i][j][2 * hrow] + cor[i][j][2 * hrow], acc[i][j][2 * hrow + 1] + cor[i][j][2 * hrow + 1]);
                 if (R) {
                     const float2 r2 = *reinterpret_cast<const float2 *>(R + (size_t)m * N + n);
                     val.x += r2.x, val.y += r2.y;
@@ -326,15 +336,22 @@ static int32_t gemm(Model *m, const float *A, int M, int K, int N, int nb, const
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
     cudaStream_t st = m->ctx->stream;
     if (!m->strict && K % 4 == 0 && N % 4 == 0) {  // tensor cores, 3xTF32
-        if (M <= 16) {
+        // Decode-sized M: small tiles (many CTAs) and a deep pipeline (latency); prefill-sized M: 64x64 tiles.
+        static bool opted[64] = {};  // per device: the 64x64 tile needs more than 48 KiB of dynamic shared memory
+        if (!opted[m->ctx->device & 63]) {
+            JGPT_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)gemm_tc_smem_bytes<64, 64, 3>()));
+            opted[m->ctx->device & 63] = true;
+        }
+        if (M <= 96) {
             dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
-            gemm_tc_kernel<16, 32, 1, 4><<<grid, 128, 0, st>>>(A, B, M, K, N, rowsel);
+            gemm_tc_kernel<16, 32, 1, 4, 5><<<grid, 128, gemm_tc_smem_bytes<16, 32, 5>(), st>>>(A, B, M, K, N, rowsel);
         } else if (M <= 512) {
             dim3 grid((N + 31) / 32, (M + 31) / 32, nb);
-            gemm_tc_kernel<32, 32, 2, 2><<<grid, 128, 0, st>>>(A, B, M, K, N, rowsel);
+            gemm_tc_kernel<32, 32, 2, 2, 4><<<grid, 128, gemm_tc_smem_bytes<32, 32, 4>(), st>>>(A, B, M, K, N, rowsel);
         } else {
             dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
-            gemm_tc_kernel<64, 64, 2, 2><<<grid, 128, 0, st>>>(A, B, M, K, N, rowsel);
+            gemm_tc_kernel<64, 64, 2, 2, 3><<<grid, 128, gemm_tc_smem_bytes<64, 64, 3>(), st>>>(A, B, M, K, N, rowsel);
         }
         JGPT_CUDA_TRY(cudaGetLastError());
         return JGPT_OK;

@@ -64,6 +64,36 @@ def run_decode35m(ctx, steps_new=128, prompt_len=64, repeats=3):
         pool.close(), model.close()
 
 
+def run_decode_step(ctx, batch=64, ctx_len=512, steps=50):
+    """Batched decode steps of the full model: `batch` sequences prefilled with `ctx_len` ids, then `steps`
+    forwardDecode steps (sampled ids fed back).  Host clock around the step (it synchronises to read the ids)."""
+    model = make_model(ctx, max_rows=8192)
+    pool = model.newPool(n_blocks=batch * (-(-(ctx_len + steps + 8) // 16)), max_seqs=batch)
+    rng = np.random.default_rng(0)
+    seqs = [pool.seq_alloc() for _ in range(batch)]
+    prompts = [rng.integers(0, VOCAB, ctx_len).astype(np.int32) for _ in range(batch)]
+    per_call = max(1, 8192 // ctx_len)
+    try:
+        toks = np.zeros(batch, np.int32)
+        for i in range(0, batch, per_call):
+            _, toks[i:i + per_call] = model.forwardPrefillBatch(pool, seqs[i:i + per_call], prompts[i:i + per_call])
+        lens = np.full(batch, ctx_len, np.int32)
+        for _ in range(3):
+            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            lens += 1
+        ctx.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            lens += 1
+        el = (time.perf_counter() - t0) / steps
+        return {"workload": f"JGPT-35M batched decode step: batch {batch}, context {ctx_len}+, sampled ids fed back",
+                "ms_per_step": el * 1e3, "tokens_per_s": batch / el, "steps": steps,
+                "timing": "host wall clock around forwardDecodeBatch (each step reads the sampled ids back)"}
+    finally:
+        pool.close(), model.close()
+
+
 def run_prefill(ctx, batch=32, seq_len=1024, repeats=3):
     """Batch 32 x 1024 prompt tokens through the full model; the paged cache of all 12 layers is written."""
     model = make_model(ctx, max_rows=batch * seq_len)
