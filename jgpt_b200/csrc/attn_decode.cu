@@ -32,9 +32,12 @@ struct DecodeParams {
     int n, H, HG, n_hg, layer0, n_layers, mbs, n_blocks, max_seqs, max_positions;
     int chunk_blocks, max_chunks, n_items, stages, max_len;
     float scale_log2e;
+    int dynamic;    // 1: CTAs claim work items from counters[0]; 0: item = blockIdx.x + k * gridDim.x
+    int *counters;  // [0] next item, [1] CTAs that have finished (the last one resets both)
 };
 
 constexpr int kMaxStages = 8;
+constexpr int kItemRing = 4;
 
 // Loads one token row of DH halfs from a shared-memory tile into fp32 registers.  For DH = 16
 // (two 16-byte halves per row) the order of the two loads alternates with bit 2 of the token
@@ -148,6 +151,11 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ int s_last;
     __shared__ int s_abort_mem;
+    // Dynamic mode: the producer warp claims work items from a global counter and hands their ids to the
+    // consumers through this small ring, so a resident CTA keeps its copy pipeline full across items and the
+    // launch has no wave quantisation (items are a few KV blocks each, claimed as CTAs become free).
+    __shared__ int item_ring[kItemRing];
+    __shared__ uint64_t item_full[kItemRing], item_empty[kItemRing];
     volatile int *s_abort = &s_abort_mem;
 
     const int tid = threadIdx.x;
@@ -161,6 +169,10 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], (uint32_t)n_cons_warps);
         }
+        for (int s = 0; s < kItemRing; s++) {
+            mbar_init(&item_full[s], 1);
+            mbar_init(&item_empty[s], (uint32_t)n_cons_warps);
+        }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -170,9 +182,108 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     uint32_t it = 0;  // KV blocks processed so far by this CTA (producer and consumers count alike)
     int stage = 0;    // it % NS, kept incrementally (no integer division in the block loop)
     uint32_t phase = 0;  // (it / NS) & 1
+    int next_static = blockIdx.x;
+    int rslot = 0, rcount = 0;  // item ring position (each side keeps its own)
+    uint32_t rphase = 0;
 
-    for (int item = blockIdx.x; item < P.n_items; item += gridDim.x) {
+    if (is_producer) {
+        // ---------------- producer warp ----------------
+        // Walks its work items, publishes each item id to the consumers and issues one bulk copy per KV block.
+        // The next item is prepared while the current one is being copied (claim -> lengths -> block-table
+        // entries are three dependent global-memory round trips): the steps are spread over the first copy
+        // issues of the current item so their latency never leaves the copy ring empty.
+        const int lane = tid & 31;
+        int raw = 0;                 // pending claim (lane 0 holds the atomic's result in dynamic mode)
+        int nid = -1, n_i = 0, n_z = 0, n_hg = 0, n_c = 0, n_len = 0, n_seq = 0;  // next item, partly resolved
+        int cur_nb = 0, cur_entry = 0, nxt_nb = 0, nxt_entry = 0;
+        size_t cur_base = 0, nxt_base = 0;
+        auto step_claim = [&]() {
+            if (P.dynamic) {
+                raw = -1;
+                if (lane == 0) raw = atomicAdd(P.counters, 1);
+            } else {
+                raw = next_static;
+                next_static += gridDim.x;
+            }
+        };
+        auto step_resolve = [&]() {  // item id known: publish it, start loading its length and sequence id
+            nid = P.dynamic ? __shfl_sync(0xffffffffu, raw, 0) : raw;
+            if (nid >= P.n_items) nid = -1;
+            if (P.dynamic) {
+                if (lane == 0) {
+                    if (rcount >= kItemRing && !*s_abort) mbar_wait_bounded(&item_empty[rslot], rphase ^ 1u, P.status, s_abort);
+                    item_ring[rslot] = nid;
+                    mbar_arrive(&item_full[rslot]);
+                }
+                rcount++;
+                if (++rslot == kItemRing) rslot = 0, rphase ^= 1u;
+            }
+            if (nid >= 0) {
+                int r = nid;
+                n_c = r % P.max_chunks, r /= P.max_chunks;
+                n_hg = r % P.n_hg, r /= P.n_hg;
+                n_i = r % P.n, n_z = r / P.n;
+                n_len = P.lens[n_i];
+                n_seq = P.seq_ids[n_i];
+            }
+        };
+        auto step_table = [&]() {  // length known: block range of the chunk, start loading its table entries
+            nxt_nb = 0, nxt_entry = 0;
+            if (nid < 0) return;
+            const int len = min(n_len, P.max_len);
+            const int nblk = len > 0 ? (len + BT - 1) / BT : 0;
+            const int nsplit = (nblk + P.chunk_blocks - 1) / P.chunk_blocks;  // balanced chunks, see the consumers
+            const int b0 = n_c < nsplit ? (int)((long long)n_c * nblk / nsplit) : nblk;
+            const int b1 = n_c < nsplit ? (int)((long long)(n_c + 1) * nblk / nsplit) : nblk;
+            if (b0 >= b1 || n_seq < 0 || n_seq >= P.max_seqs) return;  // empty chunk: the consumers skip it too
+            nxt_nb = b1 - b0;
+            if (lane < nxt_nb) nxt_entry = P.table[(size_t)n_seq * P.mbs + b0 + lane];
+            nxt_base = (((size_t)(P.layer0 + n_z) * P.n_blocks) * P.H + (size_t)n_hg * P.HG) * (size_t)HEAD_BYTES;
+        };
+        step_claim(), step_resolve(), step_table();
+        while (nid >= 0 && !*s_abort) {
+            cur_nb = nxt_nb, cur_entry = nxt_entry, cur_base = nxt_base;
+            step_claim();
+            int pending = 2;  // step_resolve, step_table still to run for the next item
+            for (int j = 0; j < cur_nb; j++, it++) {
+                int phys = __shfl_sync(0xffffffffu, cur_entry, j);
+                if (lane == 0) {
+                    if (phys < 0 || phys >= P.n_blocks) {
+                        atomicOr(P.status, DEV_STATUS_BAD_BLOCK);
+                        phys = 0;
+                    }
+                    const int s = stage;
+                    if (it >= (uint32_t)NS && !*s_abort) mbar_wait_bounded(&empty_bar[s], phase ^ 1u, P.status, s_abort);
+                    if (!*s_abort) {
+                        mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
+                        const unsigned char *src = reinterpret_cast<const unsigned char *>(P.kv) + cur_base +
+                                                   (size_t)phys * P.H * (size_t)HEAD_BYTES;
+                        bulk_g2s(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s]);
+                    }
+                }
+                if (++stage == NS) stage = 0, phase ^= 1u;
+                if (pending == 2 && j >= 1) step_resolve(), pending = 1;
+                else if (pending == 1 && j >= 3) step_table(), pending = 0;
+            }
+            if (pending == 2) step_resolve(), pending = 1;
+            if (pending == 1) step_table();
+        }
+    } else
+    for (;;) {
         if (*s_abort) break;  // a bounded wait ran out: stop taking work (status word says why)
+        int item;
+        if (!P.dynamic) {
+            item = next_static;
+            next_static += gridDim.x;
+            if (item >= P.n_items) break;
+        } else {
+            if (!mbar_wait_bounded(&item_full[rslot], rphase, P.status, s_abort)) break;
+            item = item_ring[rslot];
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&item_empty[rslot]);
+            if (++rslot == kItemRing) rslot = 0, rphase ^= 1u;
+            if (item < 0) break;
+        }
         // item -> (z = layer slab, i = sequence row, hg = head group, c = chunk); chunk is fastest.
         int r = item;
         const int c = r % P.max_chunks;
@@ -187,9 +298,10 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             len = P.max_len;
         }
         const int nblk = len > 0 ? (len + BT - 1) / BT : 0;
+        // The sequence's blocks are cut into nsplit chunks of equal size (+-1), none longer than chunk_blocks.
         const int nsplit = (nblk + P.chunk_blocks - 1) / P.chunk_blocks;
-        const int b0 = c * P.chunk_blocks;
-        const int b1 = min(b0 + P.chunk_blocks, nblk);
+        const int b0 = c < nsplit ? (int)((long long)c * nblk / nsplit) : nblk;
+        const int b1 = c < nsplit ? (int)((long long)(c + 1) * nblk / nsplit) : nblk;
         const int seq = P.seq_ids[i];
         const bool seq_ok = seq >= 0 && seq < P.max_seqs;
         if (!seq_ok && tid == 0) atomicOr(P.status, DEV_STATUS_BAD_SEQ);
@@ -198,38 +310,12 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
 
         if (b0 >= b1 || !seq_ok) {
             // Empty chunk.  A sequence without any key (len <= 0) gets a zero output row.
-            if ((nblk == 0 || !seq_ok) && c == 0 && !is_producer)
+            if ((nblk == 0 || !seq_ok) && c == 0)
                 for (int e = tid; e < P.HG * DH; e += n_cons) P.out[row + (size_t)head0 * DH + e] = 0.f;
             continue;
         }
         const int nb = b1 - b0;
         const size_t layer_base = (size_t)(P.layer0 + z) * P.n_blocks;
-
-        if (is_producer) {
-            // ---------------- producer warp ----------------
-            const int lane = tid & 31;
-            int entry = 0;
-            if (lane < nb) entry = P.table[(size_t)seq * P.mbs + b0 + lane];
-            for (int j = 0; j < nb; j++, it++) {
-                int phys = __shfl_sync(0xffffffffu, entry, j);
-                if (lane == 0) {
-                    if (phys < 0 || phys >= P.n_blocks) {
-                        atomicOr(P.status, DEV_STATUS_BAD_BLOCK);
-                        phys = 0;
-                    }
-                    const int s = stage;
-                    if (it >= (uint32_t)NS && !*s_abort) mbar_wait_bounded(&empty_bar[s], phase ^ 1u, P.status, s_abort);
-                    if (!*s_abort) {
-                        mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
-                        const unsigned char *src = reinterpret_cast<const unsigned char *>(P.kv) +
-                                                   ((layer_base + phys) * P.H + head0) * (size_t)HEAD_BYTES;
-                        bulk_g2s(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s]);
-                    }
-                }
-                if (++stage == NS) stage = 0, phase ^= 1u;
-            }
-            continue;
-        }
 
         // ---------------- consumers ----------------
         const int hl = tid / BT, t = tid % BT;
@@ -413,6 +499,16 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             for (uint32_t spin = 0; spin < (1u << 16); spin++)
                 if (mbar_try_wait(&full_bar[idx % NS], (idx / NS) & 1)) break;
     }
+    // Dynamic mode: the last CTA to leave puts both counters back to zero for the next launch (by then every
+    // CTA has drawn its sentinel, so nobody touches the item counter any more).
+    if (P.dynamic && tid == 0) {
+        __threadfence();
+        if (atomicAdd(P.counters + 1, 1) == (int)gridDim.x - 1) {
+            P.counters[0] = 0;
+            P.counters[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 // Largest divisor of H whose slab (HG * 64 * DH bytes) stays within 24 KiB and 480 consumer threads.
@@ -454,12 +550,17 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.HG = pick_head_group(p->heads, DH, p->head_group);
     P.n_hg = p->heads / P.HG;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
+    // Work distribution.  Default (persistent <= 0): one CTA per work item, the hardware block scheduler hands
+    // items to SMs as CTAs retire.  persistent = k > 0: k CTAs per SM claim items from a global counter (kept
+    // for experiments: on B200 it measured 4-15 % slower than the plain grid at every chunk length).
+    const long long total_blocks = (long long)n_layers * n * (p->heads / P.HG) * max_blocks;
+    const int per_sm = p->persistent > 0 ? p->persistent : 2;
+    const long long slots = (long long)per_sm * p->ctx->sm_count;
+    const bool dynamic = p->persistent > 0;
     if (p->chunk_blocks > 0) {
         P.chunk_blocks = p->chunk_blocks;
     } else {
-        // Automatic split: per-CTA set-up (barriers, q + RoPE, table fetch, merge) is amortised over the
-        // chunk, so chunks are as long as possible while the launch still offers about 1.5 CTAs per SM.
-        const long long total_blocks = (long long)n_layers * n * (p->heads / P.HG) * max_blocks;
+        // Few items: one CTA per item; chunks as long as possible while the launch still offers ~1.5 CTAs per SM.
         const long long want_items = 3ll * p->ctx->sm_count / 2;
         int cb = 32;
         while (cb > 4 && total_blocks / cb < want_items) cb >>= 1;
@@ -483,7 +584,11 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     const size_t stage_bytes = (size_t)P.HG * 2 * kBlockTokens * DH * 2;
     const size_t smem = stage_bytes * P.stages;
     int grid = P.n_items;
-    if (p->persistent > 0) grid = std::min(P.n_items, p->ctx->sm_count * p->persistent);
+    if (dynamic && (long long)P.n_items > slots) {
+        grid = (int)slots;
+        P.dynamic = 1;
+        P.counters = p->d_item_counters;
+    }
     const bool fused = k_new != nullptr;
     switch (DH) {
         case 4: return launch_decode_t<4>(p, P, fused, threads, smem, grid);
@@ -555,15 +660,55 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     cudaStream_t st = p->ctx->stream;
     float *dq = p->d_stage_f, *dk = dq + slab, *dv = dk + slab, *dout = dv + slab;
     int *dseq = p->d_stage_i, *drp = dseq + n, *dlen = drp + n;
-    JGPT_CUDA_TRY(cudaMemcpyAsync(dq, q_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
-    JGPT_CUDA_TRY(cudaMemcpyAsync(dk, k_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
-    JGPT_CUDA_TRY(cudaMemcpyAsync(dv, v_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
     JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
     JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
     JGPT_CUDA_TRY(cudaMemcpyAsync(dlen, lens_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
-    rc = launch_attn_decode(p, layer0, n_layers, dq, dk, dv, dseq, drp, dlen, n, max_len, dout);
-    if (rc) return rc;
-    JGPT_CUDA_TRY(cudaMemcpyAsync(out_host, dout, sizeof(float) * slab, cudaMemcpyDeviceToHost, st));
+    // The layers of one call are independent, so the call is pipelined in groups of layers: while group g is
+    // in the kernel, the inputs of group g+1 cross PCIe on the inbound copy engine and the outputs of group g-1
+    // leave on the outbound one (three streams ordered by events).  One group = the plain path.
+    constexpr int kMaxGroups = 4;
+    const int groups = std::min(kMaxGroups, n_layers);
+    if (groups == 1) {
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dq, q_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dk, k_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dv, v_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+        rc = launch_attn_decode(p, layer0, n_layers, dq, dk, dv, dseq, drp, dlen, n, max_len, dout);
+        if (rc) return rc;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(out_host, dout, sizeof(float) * slab, cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+        return JGPT_OK;
+    }
+    if (!p->s_in) {
+        JGPT_CUDA_TRY(cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking));
+        JGPT_CUDA_TRY(cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking));
+        for (int g = 0; g < kMaxGroups; g++) {
+            JGPT_CUDA_TRY(cudaEventCreateWithFlags(&p->ev_in[g], cudaEventDisableTiming));
+            JGPT_CUDA_TRY(cudaEventCreateWithFlags(&p->ev_done[g], cudaEventDisableTiming));
+        }
+        JGPT_CUDA_TRY(cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming));
+    }
+    // the staging buffers may still be in use by earlier work on the main stream
+    JGPT_CUDA_TRY(cudaEventRecord(p->ev_start, st));
+    JGPT_CUDA_TRY(cudaStreamWaitEvent(p->s_in, p->ev_start, 0));
+    const size_t per_layer = (size_t)n * p->heads * p->dhead;
+    const int base = n_layers / groups, extra = n_layers % groups;
+    int l0 = 0;
+    for (int g = 0; g < groups; g++) {
+        const int nl = base + (g < extra ? 1 : 0);
+        const size_t off = (size_t)l0 * per_layer, cnt = (size_t)nl * per_layer;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dq + off, q_host + off, sizeof(float) * cnt, cudaMemcpyHostToDevice, p->s_in));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dk + off, k_host + off, sizeof(float) * cnt, cudaMemcpyHostToDevice, p->s_in));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dv + off, v_host + off, sizeof(float) * cnt, cudaMemcpyHostToDevice, p->s_in));
+        JGPT_CUDA_TRY(cudaEventRecord(p->ev_in[g], p->s_in));
+        JGPT_CUDA_TRY(cudaStreamWaitEvent(st, p->ev_in[g], 0));
+        rc = launch_attn_decode(p, layer0 + l0, nl, dq + off, dk + off, dv + off, dseq, drp, dlen, n, max_len, dout + off);
+        if (rc) return rc;
+        JGPT_CUDA_TRY(cudaEventRecord(p->ev_done[g], st));
+        JGPT_CUDA_TRY(cudaStreamWaitEvent(p->s_out, p->ev_done[g], 0));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(out_host + off, dout + off, sizeof(float) * cnt, cudaMemcpyDeviceToHost, p->s_out));
+        l0 += nl;
+    }
+    JGPT_CUDA_TRY(cudaStreamSynchronize(p->s_out));
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
     return JGPT_OK;
 }

@@ -77,9 +77,13 @@ struct Pool {
     float *d_partials = nullptr;  // split-K scratch
     uint64_t partials_floats = 0;
     int *d_tickets = nullptr;     // split-K arrival counters (self-resetting)
+    int *d_item_counters = nullptr;  // [2] work-queue counters of the dynamic decode launch (self-resetting)
     uint64_t n_tickets = 0;
     int *d_evict_list = nullptr;  // freed block ids for the scrub kernel
     int evict_cap = 0;
+    // copy streams + events of the pipelined host-buffer entry point (created on first use)
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t ev_in[4] = {}, ev_done[4] = {}, ev_start = nullptr;
     void *d_prefill_desc = nullptr;  // per-sequence descriptors of a prefill call
     int prefill_desc_cap = 0;
     // staging for the host-buffer entry points (grow-only)
@@ -98,7 +102,7 @@ struct Pool {
     // launch tuning (read once from the environment at creation)
     int chunk_blocks = 0;  // 0 = automatic
     int stages = 4;
-    int persistent = 0;
+    int persistent = -1;  // < 0: automatic
     int head_group = 0;  // 0 = automatic
 };
 

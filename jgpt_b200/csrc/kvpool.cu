@@ -294,7 +294,7 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     p->max_blocks_per_seq = max_blocks_per_seq, p->max_positions = max_positions, p->rope_base = rope_base;
     p->chunk_blocks = std::min(32, std::max(0, env_int("JGPT_B200_CHUNK_BLOCKS", 0)));  // 0 = automatic
     p->stages = std::min(8, std::max(2, env_int("JGPT_B200_STAGES", 4)));
-    p->persistent = env_int("JGPT_B200_PERSISTENT", 0);
+    p->persistent = env_int("JGPT_B200_PERSISTENT", -1);
     p->head_group = env_int("JGPT_B200_HEAD_GROUP", 0);
     p->kv_bytes = (uint64_t)layers * n_blocks * heads * 2 * kBlockTokens * dhead * sizeof(__half);
     cudaError_t e = cudaMalloc(&p->kv, p->kv_bytes);
@@ -309,6 +309,8 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     const size_t tn = (size_t)max_seqs * max_blocks_per_seq;
     JGPT_CUDA_TRY(cudaMalloc(&p->d_table, sizeof(int) * tn));
     JGPT_CUDA_TRY(cudaMemsetAsync(p->d_table, 0xFF, sizeof(int) * tn, c->stream));
+    JGPT_CUDA_TRY(cudaMalloc(&p->d_item_counters, sizeof(int) * 2));
+    JGPT_CUDA_TRY(cudaMemsetAsync(p->d_item_counters, 0, sizeof(int) * 2, c->stream));
     // RoPE table on the host with the reference's formula (rope_4d_kernel,
     // src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:1151-1154): theta = (float)p / powf(base, 2j/dhead).
     {
@@ -337,6 +339,11 @@ int32_t jgpt_kvpool_destroy(jgpt_kvpool h) {
     cudaFree(p->kv), cudaFree(p->d_table), cudaFree(p->d_rope), cudaFree(p->d_partials), cudaFree(p->d_tickets);
     cudaFree(p->d_evict_list), cudaFree(p->d_stage_f), cudaFree(p->d_stage_i);
     cudaFree(p->d_prefill_desc);
+    cudaFree(p->d_item_counters);
+    if (p->s_in) {
+        cudaStreamDestroy(p->s_in), cudaStreamDestroy(p->s_out), cudaEventDestroy(p->ev_start);
+        for (int g = 0; g < 4; g++) cudaEventDestroy(p->ev_in[g]), cudaEventDestroy(p->ev_done[g]);
+    }
     cudaFreeHost(p->h_stage_f), cudaFreeHost(p->h_stage_i);
     delete p;
     return JGPT_OK;

@@ -53,10 +53,11 @@ def test_decode_attention_matches_oracle_ragged(ctx, Dh, H):
         case.close()
 
 
-@pytest.mark.parametrize("chunk_blocks,stages,persistent", [(1, 2, 0), (4, 3, 0), (8, 4, 1), (32, 8, 2)])
+@pytest.mark.parametrize("chunk_blocks,stages,persistent", [(1, 2, 0), (4, 3, 0), (8, 4, 1), (32, 8, 2), (1, 3, 2), (2, 4, 1)])
 def test_split_and_pipeline_settings_agree(ctx, chunk_blocks, stages, persistent):
-    """Every split / pipeline configuration gives the oracle's answer (split-K merge, ring wrap-around,
-    persistent CTAs walking several work items)."""
+    """Every split / pipeline configuration gives the oracle's answer (split-K merge, ring wrap-around, one CTA
+    per item, and the dynamic work queue: with 1- or 2-block items the launch has more items than resident
+    CTAs, so CTAs claim several items each through the item ring)."""
     os.environ["JGPT_B200_CHUNK_BLOCKS"] = str(chunk_blocks)
     os.environ["JGPT_B200_STAGES"] = str(stages)
     os.environ["JGPT_B200_PERSISTENT"] = str(persistent)
