@@ -104,6 +104,7 @@ struct Pool {
     int stages = 4;
     int persistent = -1;  // < 0: automatic
     int head_group = 0;  // 0 = automatic
+    int decode_mma = 0;  // 1: tensor-core consumer in the decode kernel (dhead 16)
 };
 
 struct Model;

@@ -296,6 +296,7 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     p->stages = std::min(8, std::max(2, env_int("JGPT_B200_STAGES", 4)));
     p->persistent = env_int("JGPT_B200_PERSISTENT", -1);
     p->head_group = env_int("JGPT_B200_HEAD_GROUP", 0);
+    p->decode_mma = env_int("JGPT_B200_DECODE_MMA", 0);
     p->kv_bytes = (uint64_t)layers * n_blocks * heads * 2 * kBlockTokens * dhead * sizeof(__half);
     cudaError_t e = cudaMalloc(&p->kv, p->kv_bytes);
     if (e != cudaSuccess) {

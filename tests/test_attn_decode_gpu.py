@@ -85,6 +85,52 @@ def test_split_and_pipeline_settings_agree(ctx, chunk_blocks, stages, persistent
         case.close()
 
 
+@pytest.mark.parametrize("fused", [False, True])
+def test_tensor_core_consumer_matches_oracle(ctx, fused):
+    """JGPT_B200_DECODE_MMA=1: scores and P.V on mma.sync with fp16 hi/lo split operands (d_head 16).  Same tolerance
+    as the scalar consumer; ragged lengths, split-K, odd head count, dead slots in the last block poisoned with NaN."""
+    os.environ["JGPT_B200_DECODE_MMA"] = "1"
+    os.environ["JGPT_B200_CHUNK_BLOCKS"] = "4"
+    try:
+        lens0 = [1, 15, 16, 17, 33, 130, 257, 700]
+        case = PagedCase(ctx, lens0, H=5, Dh=16, layers=1, seed=51, spare_tokens=2)
+    finally:
+        os.environ.pop("JGPT_B200_DECODE_MMA"), os.environ.pop("JGPT_B200_CHUNK_BLOCKS")
+    try:
+        rng = np.random.default_rng(52)
+        n, H, Dh = case.n, 5, 16
+        lens = np.array(lens0, np.int32)
+        # poison everything beyond each sequence's tokens: the kernel must not let it reach the output
+        ptr, nbytes = case.pool.storage()
+        raw = np.empty(nbytes // 2, np.uint16)
+        from jgpt_b200 import binding as B
+        B.check(ctx._lib.jgpt_d2h(ctx.handle, raw.ctypes.data, ptr, nbytes))
+        tiles = raw.reshape(1, case.n_blocks, H, 2, 16, Dh)
+        for i, l in enumerate(lens0):
+            blk, slot = case.tables[i][l // 16], l % 16
+            if l // 16 < len(case.tables[i]):
+                tiles[0, blk, :, :, slot:, :] = 0x7E00  # fp16 NaN
+        B.check(ctx._lib.jgpt_h2d(ctx.handle, ptr, raw.ctypes.data, nbytes))
+        q = rng.standard_normal((n, H * Dh)).astype(np.float32)
+        out = ctx.alloc((n, H * Dh))
+        if fused:
+            k, v = (rng.standard_normal((n, H * Dh)).astype(np.float32) for _ in range(2))
+            rope = (lens + 1).astype(np.int32)
+            case.pool.attn_decode_append(0, 1, ctx.from_host(q), ctx.from_host(k), ctx.from_host(v), case.seq_ids_dev(),
+                                         ctx.from_host(rope), ctx.from_host(lens + 1), n, int(lens.max()) + 1, out)
+            want = O.decode_attn_batch(q, k, v, case.kc[0], case.vc[0], lens, rope, H, Dh, case.max_seq, kv_fp16=True)
+        else:
+            rope = (lens - 1).astype(np.int32)
+            case.pool.attn_decode(0, 1, ctx.from_host(q), case.seq_ids_dev(), ctx.from_host(rope), ctx.from_host(lens), n,
+                                  int(lens.max()), out)
+            want = _oracle_decode(case, 0, q, lens0, rope)
+        ctx.synchronize()
+        got = out.to_host()
+        assert np.isfinite(got).all() and np.abs(got - want).max() < TOL, np.abs(got - want).max()
+    finally:
+        case.close()
+
+
 @pytest.mark.parametrize("Dh,H", [(16, 24), (8, 4)])
 def test_fused_append_decode_matches_oracle_step_by_step(ctx, Dh, H):
     """Three decode steps of the fused kernel == oracle append + attend (payload bit-exact, outputs within TOL),
