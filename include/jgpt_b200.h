@@ -206,6 +206,13 @@ JGPT_API int32_t jgpt_attn_prefill(jgpt_kvpool pool, int32_t layer, const float 
  * loadWeights (:1944-1965) and GptKvForward.forwardPrefillGpu / forwardDecodeGpu
  * (J/model/GptKvForward.java:46-90, 131-170).
  * ------------------------------------------------------------------------------------------- */
+/* C[M,N] = A[M,K] . B[K,N], row-major fp32 device buffers, ordered on the context's stream: the
+ * projection primitive of the forward step (TensorOpsGPU.matmulGpuDevice, J/TensorOpsGPU.java:1393;
+ * native GEMM src/main/cpp/jgpt_cuda_jni_init_matmul.inl:67).  fp32-level accuracy (split-TF32
+ * operands on the tensor cores; tcgen05 + tensor memory for prefill-sized M). */
+JGPT_API int32_t jgpt_matmul_device(jgpt_ctx ctx, const float *a_dev, const float *b_dev, float *c_dev,
+                                    int32_t M, int32_t K, int32_t N);
+
 JGPT_API int32_t jgpt_model_create(jgpt_ctx ctx, int32_t vocab, int32_t max_seq_len, int32_t d_model,
                                    int32_t heads, int32_t layers, int32_t d_ff, float rms_eps,
                                    int32_t max_rows, jgpt_model *out);

@@ -7,10 +7,12 @@
 // that accumulates every output element over k in ascending order in one thread (mul, then add), which is
 // bit-reproducible against a scalar CPU loop.
 #include "common.cuh"
+#include "gemm_umma.cuh"
 
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <unordered_map>
 
 namespace jgpt {
 
@@ -34,7 +36,17 @@ struct Model {
     int *h_next = nullptr;    // pinned
     int *d_rowsel = nullptr;  // [max_rows] rows whose logits are wanted
     int strict = 0;           // 0: tensor-core 3xTF32 projections; 1: k-ordered scalar fp32 (mul + add, two roundings)
+    // Prefill-sized products (M >= umma_min_rows) run on the tcgen05 kernel over pre-tiled operand images.
+    int umma_min_rows = 1024;  // JGPT_B200_UMMA_MIN_ROWS; 0: never
+    std::unordered_map<const float *, float *> wimg;  // weight images by source pointer; dropped when weights change
+    float *aimg = nullptr;    // activation image (grow-only)
+    uint64_t aimg_floats = 0;
 };
+
+static void drop_weight_images(Model *m) {
+    for (auto &kv : m->wimg) cudaFree(kv.second);
+    m->wimg.clear();
+}
 
 Registry<Model> &model_registry() {
     static Registry<Model> r;
@@ -330,18 +342,19 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
-static int32_t gemm(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
-                    const float *const *R, const int *rowsel = nullptr) {
+// The mma.sync / scalar kernels (any M; what decode-sized products use).
+static int32_t gemm_small(Ctx *ctx, int strict, const float *A, int M, int K, int N, int nb, const float *const *W,
+                          float *const *C, const float *const *R, const int *rowsel) {
     GemmBatch B;
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
-    cudaStream_t st = m->ctx->stream;
-    if (!m->strict && K % 4 == 0 && N % 4 == 0) {  // tensor cores, 3xTF32
+    cudaStream_t st = ctx->stream;
+    if (!strict && K % 4 == 0 && N % 4 == 0) {  // tensor cores, 3xTF32
         // Decode-sized M: small tiles (many CTAs) and a deep pipeline (latency); prefill-sized M: 64x64 tiles.
         static bool opted[64] = {};  // per device: the 64x64 tile needs more than 48 KiB of dynamic shared memory
-        if (!opted[m->ctx->device & 63]) {
+        if (!opted[ctx->device & 63]) {
             JGPT_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)gemm_tc_smem_bytes<64, 64, 3>()));
-            opted[m->ctx->device & 63] = true;
+            opted[ctx->device & 63] = true;
         }
         if (M <= 96) {
             dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
@@ -358,19 +371,56 @@ static int32_t gemm(Model *m, const float *A, int M, int K, int N, int nb, const
     }
     if (M <= 16) {
         dim3 grid((N + 63) / 64, (M + 15) / 16, nb);
-        if (m->strict) gemm_kernel<16, 64, 1, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+        if (strict) gemm_kernel<16, 64, 1, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
         else gemm_kernel<16, 64, 1, 4, false><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
     } else if (M <= 128) {
         dim3 grid((N + 63) / 64, (M + 31) / 32, nb);
-        if (m->strict) gemm_kernel<32, 64, 2, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+        if (strict) gemm_kernel<32, 64, 2, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
         else gemm_kernel<32, 64, 2, 4, false><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
     } else {
         dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
-        if (m->strict) gemm_kernel<64, 64, 4, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
+        if (strict) gemm_kernel<64, 64, 4, 4, true><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
         else gemm_kernel<64, 64, 4, 4, false><<<grid, 256, 0, st>>>(A, B, M, K, N, rowsel);
     }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
+}
+
+// Prefill-sized products: pack A into its image, look up (or build once) the weight images, run the tcgen05
+// kernel.  Everything is ordered on the context's stream.
+static int32_t gemm_umma(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
+                         const float *const *R, const int *rowsel) {
+    cudaStream_t st = m->ctx->stream;
+    const uint64_t need = umma::image_floats(M, K, umma::BM);
+    if (need > m->aimg_floats) {
+        JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+        if (m->aimg) JGPT_CUDA_TRY(cudaFree(m->aimg));
+        m->aimg = nullptr, m->aimg_floats = 0;
+        JGPT_CUDA_TRY(cudaMalloc(&m->aimg, sizeof(float) * need));
+        m->aimg_floats = need;
+    }
+    umma::Batch b{};
+    for (int z = 0; z < nb; z++) {
+        auto it = m->wimg.find(W[z]);
+        if (it == m->wimg.end()) {
+            float *img = nullptr;
+            JGPT_CUDA_TRY(cudaMalloc(&img, sizeof(float) * umma::image_floats(N, K, umma::BN)));
+            it = m->wimg.emplace(W[z], img).first;
+            int32_t rc = umma::pack_weight(W[z], K, N, img, st);
+            if (rc) return rc;
+        }
+        b.Wimg[z] = it->second, b.C[z] = C[z], b.R[z] = R ? R[z] : nullptr;
+    }
+    int32_t rc = umma::pack_activations(A, rowsel, M, K, m->aimg, st);
+    if (rc) return rc;
+    return umma::launch(m->aimg, b, nb, M, K, N, m->ctx->d_status, st);
+}
+
+static int32_t gemm(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
+                    const float *const *R, const int *rowsel = nullptr) {
+    if (!m->strict && m->umma_min_rows > 0 && M >= m->umma_min_rows && umma::shape_ok(K, N))
+        return gemm_umma(m, A, M, K, N, nb, W, C, R, rowsel);
+    return gemm_small(m->ctx, m->strict, A, M, K, N, nb, W, C, R, rowsel);
 }
 
 static int num_tensors(const Model *m) { return 4 + 9 * m->layers; }
@@ -477,6 +527,40 @@ static int32_t check_pool(const Model *m, const Pool *p) {
 
 extern "C" {
 
+// C[M,N] = A[M,K] . B[K,N], row-major fp32 device buffers, ordered on the context's stream
+// (TensorOpsGPU.matmulGpuDevice, src/main/java/com/veles/llm/jgpt/TensorOpsGPU.java:1393).  Products with at
+// least JGPT_B200_UMMA_MIN_ROWS rows (default 1024) and K % 16 == 0, N % 4 == 0 take the tcgen05 kernel; their
+// operand images live in stream-ordered scratch for the duration of the call.
+int32_t jgpt_matmul_device(jgpt_ctx ctxh, const float *a_dev, const float *b_dev, float *c_dev, int32_t M, int32_t K, int32_t N) {
+    Ctx *c = ctx_registry().get(ctxh);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_REQUIRE(a_dev && b_dev && c_dev, JGPT_ERR_INVALID_ARGUMENT, "null buffer");
+    JGPT_REQUIRE(M > 0 && K > 0 && N > 0, JGPT_ERR_INVALID_ARGUMENT, "matmul dimensions must be positive (M=%d K=%d N=%d)", M, K, N);
+    JGPT_CUDA_TRY(make_current(c));
+    const float *W[1] = {b_dev};
+    float *C[1] = {c_dev};
+    const int min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 1024);
+    const int strict = env_int("JGPT_B200_STRICT_GEMM", 0);
+    if (strict || min_rows <= 0 || M < min_rows || !umma::shape_ok(K, N))
+        return gemm_small(c, strict, a_dev, M, K, N, 1, W, C, nullptr, nullptr);
+    cudaStream_t st = c->stream;
+    float *aimg = nullptr, *wimg = nullptr;
+    JGPT_CUDA_TRY(cudaMallocAsync(&aimg, sizeof(float) * umma::image_floats(M, K, umma::BM), st));
+    cudaError_t e = cudaMallocAsync(&wimg, sizeof(float) * umma::image_floats(N, K, umma::BN), st);
+    if (e != cudaSuccess) {
+        cudaFreeAsync(aimg, st);
+        return fail(JGPT_ERR_OUT_OF_MEMORY, "matmul scratch: %s", cudaGetErrorString(e));
+    }
+    umma::Batch b{};
+    b.Wimg[0] = wimg, b.C[0] = c_dev, b.R[0] = nullptr;
+    int32_t rc = umma::pack_weight(b_dev, K, N, wimg, st);
+    if (!rc) rc = umma::pack_activations(a_dev, nullptr, M, K, aimg, st);
+    if (!rc) rc = umma::launch(aimg, b, 1, M, K, N, c->d_status, st);
+    cudaFreeAsync(aimg, st);
+    cudaFreeAsync(wimg, st);
+    return rc;
+}
+
 int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int32_t d_model, int32_t heads, int32_t layers,
                           int32_t d_ff, float rms_eps, int32_t max_rows, jgpt_model *out) {
     Ctx *c = ctx_registry().get(ctxh);
@@ -491,6 +575,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->ctx = c, m->vocab = vocab, m->max_seq = max_seq_len, m->d_model = d_model, m->heads = heads, m->layers = layers;
     m->d_ff = d_ff, m->eps = rms_eps, m->max_rows = max_rows;
     m->strict = env_int("JGPT_B200_STRICT_GEMM", 0);
+    m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 1024);
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -538,6 +623,8 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     cudaFree(m->x), cudaFree(m->xn), cudaFree(m->q), cudaFree(m->k), cudaFree(m->v), cudaFree(m->att), cudaFree(m->h1);
     cudaFree(m->g), cudaFree(m->logits), cudaFree(m->d_idx), cudaFree(m->d_next), cudaFree(m->d_rowsel);
     cudaFreeHost(m->h_idx), cudaFreeHost(m->h_next);
+    drop_weight_images(m);
+    cudaFree(m->aimg);
     delete m;
     return JGPT_OK;
 }
@@ -558,6 +645,7 @@ int32_t jgpt_model_set_tensor(jgpt_model h, int32_t idx, const float *host, uint
                  (unsigned long long)count, (unsigned long long)n_floats);
     JGPT_CUDA_TRY(cudaMemcpyAsync(dst, host, sizeof(float) * count, cudaMemcpyHostToDevice, m->ctx->stream));
     JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    drop_weight_images(m);  // rebuilt from the new values on the next prefill-sized product
     return JGPT_OK;
 }
 
@@ -585,6 +673,8 @@ int32_t jgpt_model_load_weights(jgpt_model h, const char *path) {
         fclose(f);
         return fail(JGPT_ERR_INVALID_ARGUMENT, "%s holds %u tensors, the model has %d", path, n, num_tensors(m));
     }
+    cudaStreamSynchronize(m->ctx->stream);
+    drop_weight_images(m);
     std::vector<float> buf;
     for (int i = 0; i < (int)n; i++) {
         uint64_t count = 0;

@@ -41,6 +41,10 @@ class Context:
         buf.copy_from(arr)
         return buf
 
+    def matmul(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", M: int, K: int, N: int):
+        """``TensorOpsGPU.matmulGpuDevice(a, b, c, M, K, N)``: C[M,N] = A[M,K] . B[K,N] on device buffers."""
+        B.check(self._lib.jgpt_matmul_device(self.handle, a.ptr, b.ptr, c.ptr, M, K, N))
+
     def capture(self, fn) -> "Graph":
         """Records everything ``fn()`` enqueues on this context into a CUDA graph."""
         B.check(self._lib.jgpt_graph_begin_capture(self.handle))
