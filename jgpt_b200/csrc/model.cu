@@ -38,14 +38,16 @@ struct Model {
     int strict = 0;           // 0: tensor-core 3xTF32 projections; 1: k-ordered scalar fp32 (mul + add, two roundings)
     // Prefill-sized products (M >= umma_min_rows) run on the tcgen05 kernel over pre-tiled operand images.
     int umma_min_rows = 1024;  // JGPT_B200_UMMA_MIN_ROWS; 0: never
-    std::unordered_map<const float *, float *> wimg;  // weight images by source pointer; dropped when weights change
-    float *aimg = nullptr;    // activation image (grow-only)
-    uint64_t aimg_floats = 0;
+    std::unordered_map<const float *, float *> wimg;   // weight images by source pointer; dropped when weights change
+    std::unordered_map<const float *, float *> wpair;  // W1/W3 pair images by W1's pointer
+    float *aimg = nullptr, *aimg2 = nullptr;  // activation images (grow-only): [rows, d_model]-sized and [rows, d_ff]-sized
+    uint64_t aimg_floats = 0, aimg2_floats = 0;
 };
 
 static void drop_weight_images(Model *m) {
     for (auto &kv : m->wimg) cudaFree(kv.second);
-    m->wimg.clear();
+    for (auto &kv : m->wpair) cudaFree(kv.second);
+    m->wimg.clear(), m->wpair.clear();
 }
 
 Registry<Model> &model_registry() {
@@ -388,30 +390,52 @@ static int32_t gemm_small(Ctx *ctx, int strict, const float *A, int M, int K, in
 
 // Prefill-sized products: pack A into its image, look up (or build once) the weight images, run the tcgen05
 // kernel.  Everything is ordered on the context's stream.
+static int32_t ensure_image(Model *m, float **buf, uint64_t *cap, uint64_t need) {
+    if (need <= *cap) return JGPT_OK;
+    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    if (*buf) JGPT_CUDA_TRY(cudaFree(*buf));
+    *buf = nullptr, *cap = 0;
+    JGPT_CUDA_TRY(cudaMalloc(buf, sizeof(float) * need));
+    *cap = need;
+    return JGPT_OK;
+}
+static int32_t weight_image(Model *m, const float *W, int K, int N, const float **out) {
+    auto it = m->wimg.find(W);
+    if (it == m->wimg.end()) {
+        float *img = nullptr;
+        JGPT_CUDA_TRY(cudaMalloc(&img, sizeof(float) * umma::weight_image_floats(K, N)));
+        it = m->wimg.emplace(W, img).first;
+        int32_t rc = umma::pack_weight(W, K, N, img, m->ctx->stream);
+        if (rc) return rc;
+    }
+    *out = it->second;
+    return JGPT_OK;
+}
+static int32_t weight_pair_image(Model *m, const float *W1, const float *W3, int K, int F, const float **out) {
+    auto it = m->wpair.find(W1);
+    if (it == m->wpair.end()) {
+        float *img = nullptr;
+        JGPT_CUDA_TRY(cudaMalloc(&img, sizeof(float) * umma::image_floats(2 * F, K, 256)));
+        it = m->wpair.emplace(W1, img).first;
+        int32_t rc = umma::pack_weight_pair(W1, W3, K, F, img, m->ctx->stream);
+        if (rc) return rc;
+    }
+    *out = it->second;
+    return JGPT_OK;
+}
+
 static int32_t gemm_umma(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
                          const float *const *R, const int *rowsel) {
     cudaStream_t st = m->ctx->stream;
-    const uint64_t need = umma::image_floats(M, K, umma::BM);
-    if (need > m->aimg_floats) {
-        JGPT_CUDA_TRY(cudaStreamSynchronize(st));
-        if (m->aimg) JGPT_CUDA_TRY(cudaFree(m->aimg));
-        m->aimg = nullptr, m->aimg_floats = 0;
-        JGPT_CUDA_TRY(cudaMalloc(&m->aimg, sizeof(float) * need));
-        m->aimg_floats = need;
-    }
+    int32_t rc = ensure_image(m, &m->aimg, &m->aimg_floats, umma::activation_image_floats(M, K));
+    if (rc) return rc;
     umma::Batch b{};
     for (int z = 0; z < nb; z++) {
-        auto it = m->wimg.find(W[z]);
-        if (it == m->wimg.end()) {
-            float *img = nullptr;
-            JGPT_CUDA_TRY(cudaMalloc(&img, sizeof(float) * umma::image_floats(N, K, umma::BN)));
-            it = m->wimg.emplace(W[z], img).first;
-            int32_t rc = umma::pack_weight(W[z], K, N, img, st);
-            if (rc) return rc;
-        }
-        b.Wimg[z] = it->second, b.C[z] = C[z], b.R[z] = R ? R[z] : nullptr;
+        rc = weight_image(m, W[z], K, N, &b.Wimg[z]);
+        if (rc) return rc;
+        b.C[z] = C[z], b.R[z] = R ? R[z] : nullptr;
     }
-    int32_t rc = umma::pack_activations(A, rowsel, M, K, m->aimg, st);
+    rc = umma::pack_activations(A, rowsel, M, K, m->aimg, st);
     if (rc) return rc;
     return umma::launch(m->aimg, b, nb, M, K, N, m->ctx->d_status, st);
 }
@@ -457,9 +481,61 @@ static int32_t ensure_logits(Model *m, int rows) {
 }
 
 // One decoder block over `rows` rows already in m->x.  Attention is supplied by the caller.
+// The same decoder blocks for prefill-sized `rows`: every projection on the tcgen05 kernel, activations handed
+// from producer to consumer as operand images (RMSNorm writes one, the W1/W3 product's SwiGLU epilogue writes
+// one; only the attention output is packed by a kernel of its own).
+template <class AttnFn>
+static int32_t run_layers_umma(Model *m, int rows, AttnFn &&attn) {
+    const int D = m->d_model, F = m->d_ff;
+    cudaStream_t st = m->ctx->stream;
+    int *status = m->ctx->d_status;
+    const bool fused_ffn = umma::swiglu_shape_ok(D, F);
+    int32_t rc = ensure_image(m, &m->aimg, &m->aimg_floats, umma::activation_image_floats(rows, D));
+    if (rc) return rc;
+    rc = ensure_image(m, &m->aimg2, &m->aimg2_floats, umma::activation_image_floats(rows, F));
+    if (rc) return rc;
+    for (int l = 0; l < m->layers; l++) {
+        const LayerW &y = m->L[(size_t)l];
+        umma::Batch qkv{}, wo{}, w13{}, w2{};
+        if ((rc = weight_image(m, y.wq, D, D, &qkv.Wimg[0]))) return rc;
+        if ((rc = weight_image(m, y.wk, D, D, &qkv.Wimg[1]))) return rc;
+        if ((rc = weight_image(m, y.wv, D, D, &qkv.Wimg[2]))) return rc;
+        if ((rc = weight_image(m, y.wo, D, D, &wo.Wimg[0]))) return rc;
+        if ((rc = weight_image(m, y.w2, F, D, &w2.Wimg[0]))) return rc;
+        qkv.C[0] = m->q, qkv.C[1] = m->k, qkv.C[2] = m->v;
+        wo.C[0] = m->x, wo.R[0] = m->x;  // x1 = x + attn.Wo (each element read then written by the same thread)
+        w2.C[0] = m->x, w2.R[0] = m->x;
+        if ((rc = umma::rmsnorm_pack(m->x, y.norm1, rows, D, m->eps, m->aimg, st))) return rc;
+        if ((rc = umma::launch(m->aimg, qkv, 3, rows, D, D, status, st))) return rc;
+        if ((rc = attn(l))) return rc;
+        if ((rc = umma::pack_activations(m->att, nullptr, rows, D, m->aimg, st))) return rc;
+        if ((rc = umma::launch(m->aimg, wo, 1, rows, D, D, status, st))) return rc;
+        if ((rc = umma::rmsnorm_pack(m->x, y.norm2, rows, D, m->eps, m->aimg, st))) return rc;
+        if (fused_ffn) {
+            const float *pair = nullptr;
+            if ((rc = weight_pair_image(m, y.w1, y.w3, D, F, &pair))) return rc;
+            if ((rc = umma::launch_swiglu(m->aimg, pair, rows, D, F, m->aimg2, status, st))) return rc;
+        } else {
+            if ((rc = weight_image(m, y.w1, D, F, &w13.Wimg[0]))) return rc;
+            if ((rc = weight_image(m, y.w3, D, F, &w13.Wimg[1]))) return rc;
+            w13.C[0] = m->h1, w13.C[1] = m->g;
+            if ((rc = umma::launch(m->aimg, w13, 2, rows, D, F, status, st))) return rc;
+            const long long nf = (long long)rows * F;
+            swiglu_kernel<<<(unsigned)((nf + 255) / 256), 256, 0, st>>>(m->h1, m->g, nf);
+            if ((rc = umma::pack_activations(m->h1, nullptr, rows, F, m->aimg2, st))) return rc;
+        }
+        if ((rc = umma::launch(m->aimg2, w2, 1, rows, F, D, status, st))) return rc;
+    }
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
 template <class AttnFn>
 static int32_t run_layers(Model *m, int rows, AttnFn &&attn) {
     const int D = m->d_model, F = m->d_ff;
+    if (!m->strict && m->umma_min_rows > 0 && rows >= m->umma_min_rows && umma::shape_ok(D, D) && umma::shape_ok(D, F) &&
+        umma::shape_ok(F, D) && sizeof(float) * 8 * (size_t)(D + 4) <= 48 * 1024)
+        return run_layers_umma(m, rows, attn);
     cudaStream_t st = m->ctx->stream;
     for (int l = 0; l < m->layers; l++) {
         const LayerW &y = m->L[(size_t)l];
@@ -545,8 +621,8 @@ int32_t jgpt_matmul_device(jgpt_ctx ctxh, const float *a_dev, const float *b_dev
         return gemm_small(c, strict, a_dev, M, K, N, 1, W, C, nullptr, nullptr);
     cudaStream_t st = c->stream;
     float *aimg = nullptr, *wimg = nullptr;
-    JGPT_CUDA_TRY(cudaMallocAsync(&aimg, sizeof(float) * umma::image_floats(M, K, umma::BM), st));
-    cudaError_t e = cudaMallocAsync(&wimg, sizeof(float) * umma::image_floats(N, K, umma::BN), st);
+    JGPT_CUDA_TRY(cudaMallocAsync(&aimg, sizeof(float) * umma::activation_image_floats(M, K), st));
+    cudaError_t e = cudaMallocAsync(&wimg, sizeof(float) * umma::weight_image_floats(K, N), st);
     if (e != cudaSuccess) {
         cudaFreeAsync(aimg, st);
         return fail(JGPT_ERR_OUT_OF_MEMORY, "matmul scratch: %s", cudaGetErrorString(e));
@@ -624,7 +700,7 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     cudaFree(m->g), cudaFree(m->logits), cudaFree(m->d_idx), cudaFree(m->d_next), cudaFree(m->d_rowsel);
     cudaFreeHost(m->h_idx), cudaFreeHost(m->h_next);
     drop_weight_images(m);
-    cudaFree(m->aimg);
+    cudaFree(m->aimg), cudaFree(m->aimg2);
     delete m;
     return JGPT_OK;
 }

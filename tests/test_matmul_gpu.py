@@ -2,9 +2,13 @@
 paths: the tcgen05 / tensor-memory kernel that prefill-sized products take and the mma.sync kernel for
 decode-sized ones.  Both split every fp32 operand into two TF32 parts and accumulate three products in fp32.
 
-Tolerance: max |C - C64| <= 2e-5 * max |C64| against a float64 product (K up to 2048; the tensor cores
-truncate when they add into the fp32 accumulator, which leaves about 3e-9 * K of the largest element; a
-k-ordered fp32 loop sits at about 6e-7).  Plain TF32, what the reference runs these GEMMs with, is ~1e-3."""
+Tolerance against a float64 product, relative to the largest element of C: the tensor cores truncate when
+they add into the fp32 accumulator, which leaves a bias proportional to the number of additions.  The
+mma.sync kernel keeps the two small correction products in an accumulator of their own (K / 8 additions into
+the main one: measured 3e-9 * K); the tcgen05 kernel adds all three products into one accumulator so that the
+other half of tensor memory can double-buffer the next tile (3K / 8 additions: measured 8e-9 * K).  Bounds
+used: 2e-6 + 1.5e-8 * K and 2e-6 + 5e-9 * K.  A k-ordered fp32 loop sits at about 6e-7; plain TF32, what the
+reference runs these GEMMs with, at about 1e-3."""
 import os
 
 import numpy as np
@@ -14,7 +18,14 @@ import oracle as O
 from jgpt_b200 import GPTModel, KvCacheGpu
 
 pytestmark = pytest.mark.gpu
-REL_TOL = 2e-5
+
+
+def tol_tcgen05(K):
+    return 2e-6 + 1.5e-8 * K
+
+
+def tol_mma_sync(K):
+    return 2e-6 + 5e-9 * K
 
 
 class _env:
@@ -52,6 +63,8 @@ def _matmul(ctx, a, b, min_rows):
     (129, 80, 260),      # ragged in M and N, K = 5 stages (wraps the 4-stage ring)
     (1000, 512, 8000),   # LM-head shape: N not a multiple of the 256-column tile
     (2048, 512, 2048),   # FFN up
+    (640, 384, 384),     # 192-column tiles (N % 192 == 0, N % 256 != 0), five-stage ring
+    (300, 768, 1152),    # 192-column tiles, ragged M
     (2048, 2048, 512),   # FFN down
 ])
 def test_tcgen05_path_matches_float64_and_the_mma_sync_path(ctx, M, K, N):
@@ -63,9 +76,8 @@ def test_tcgen05_path_matches_float64_and_the_mma_sync_path(ctx, M, K, N):
     big = _matmul(ctx, a, b, min_rows=1)          # tcgen05 path
     small = _matmul(ctx, a, b, min_rows=10 ** 8)  # mma.sync path
     assert np.isfinite(big).all() and np.isfinite(small).all()
-    assert np.abs(big - ref).max() <= REL_TOL * scale
-    assert np.abs(small - ref).max() <= REL_TOL * scale
-    assert np.abs(big - small).max() <= 2e-6 * scale
+    assert np.abs(big - ref).max() <= tol_tcgen05(K) * scale
+    assert np.abs(small - ref).max() <= tol_mma_sync(K) * scale
 
 
 def test_operand_layout_is_exact_on_integers(ctx):
@@ -86,7 +98,7 @@ def test_unaligned_k_falls_back_to_the_small_kernel(ctx):
     a, b = rng.standard_normal((300, 20), dtype=np.float32), rng.standard_normal((20, 36), dtype=np.float32)
     got = _matmul(ctx, a, b, min_rows=1)  # K % 16 != 0
     ref = a.astype(np.float64) @ b.astype(np.float64)
-    assert np.abs(got - ref).max() <= REL_TOL * np.abs(ref).max()
+    assert np.abs(got - ref).max() <= tol_mma_sync(20) * np.abs(ref).max()
 
 
 def test_matmul_argument_contract(ctx):
@@ -96,10 +108,12 @@ def test_matmul_argument_contract(ctx):
     d.close()
 
 
-def test_forward_step_on_the_tcgen05_projections(ctx):
-    """The whole forward step with every projection forced onto the tcgen05 kernel: logits and greedy tokens
-    as with the default kernels and as the oracle's; weight images follow a weight update."""
-    V, MS, D, H, L, F = 96, 80, 64, 4, 3, 128
+@pytest.mark.parametrize("F", [128, 96])
+def test_forward_step_on_the_tcgen05_projections(ctx, F):
+    """The whole forward step with every projection forced onto the tcgen05 kernel (d_ff 128: SwiGLU fused into
+    the W1/W3 product's epilogue; d_ff 96: separate products): logits and greedy tokens as with the default
+    kernels and as the oracle's; weight images follow a weight update."""
+    V, MS, D, H, L = 96, 80, 64, 4, 3
     om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=4, std=0.15)
     gm_def = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5)
     with _env(JGPT_B200_UMMA_MIN_ROWS=1):
@@ -110,13 +124,17 @@ def test_forward_step_on_the_tcgen05_projections(ctx):
     try:
         a, b = gm_def.forwardPrefill(ids, c1), gm_big.forwardPrefill(ids, c2)
         want = om.forward_prefill(ids, om.new_cache(kv_fp16=True))
-        assert np.abs(a - b).max() < 5e-5
-        assert np.abs(b - want).max() < 5e-4
+        # the two projection kernels differ by a few 1e-6 relative; where that moves a K/V element across an
+        # fp16 rounding boundary (N(0, 0.15) toy weights, logits of magnitude ~3) single logits move by a few
+        # 1e-4: TOL = 1e-3, well inside the 5e-3 this geometry is allowed against the fp32 oracle
+        TOL = 1e-3
+        assert np.abs(a - b).max() < TOL
+        assert np.abs(b - want).max() < TOL
         tok = int(np.argmax(b[-1]))
         for _ in range(8):
             da = gm_def.forwardDecode([tok], c1, c1.length(), c1.length())
             db = gm_big.forwardDecode([tok], c2, c2.length(), c2.length())
-            assert np.abs(da - db).max() < 5e-5
+            assert np.abs(da - db).max() < TOL
             tok = int(np.argmax(db))
         # new weights: the cached weight images must be rebuilt
         om2 = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=9, std=0.15)
@@ -124,7 +142,41 @@ def test_forward_step_on_the_tcgen05_projections(ctx):
         c2.clear()
         b2 = gm_big.forwardPrefill(ids, c2)
         want2 = om2.forward_prefill(ids, om2.new_cache(kv_fp16=True))
-        assert np.abs(b2 - want2).max() < 5e-4
+        assert np.abs(b2 - want2).max() < TOL
         om2.close()
     finally:
         c1.close(), c2.close(), gm_def.close(), gm_big.close(), om.close()
+
+
+def test_jgpt_35m_full_context_prefill_on_the_default_path_matches_oracle(ctx):
+    """1024 prompt tokens of the JGPT-35M configuration: enough rows for the forward step to pick the tcgen05
+    projections by itself.  Last-row logits within the 2e-3 budget of the fp32-cache oracle and within 5e-4 of
+    the fp16-payload oracle; the greedy next token agrees unless the oracle's own top-2 margin is below 1e-4;
+    the K/V payload of every layer sits on the oracle's fp16 values up to neighbouring-value flips."""
+    om = O.Model(8000, 1024, 384, 24, 12, 768, eps=1e-5).init_random(seed=0, std=0.02)
+    gm = GPTModel(ctx, 8000, 1024, 384, 24, 12, 768, rmsNormEps=1e-5, maxRows=1024)
+    gm.setParameters(om.tensors())
+    prompt = np.random.default_rng(2).integers(0, 8000, 1024).astype(np.int32)
+    cache = KvCacheGpu(12, 24, 16, 1024, ctx=ctx)
+    oc32, oc16 = om.new_cache(kv_fp16=False), om.new_cache(kv_fp16=True)
+    try:
+        got = gm.forwardPrefill(prompt, cache, 0)
+        want32, want16 = om.forward_prefill(prompt, oc32), om.forward_prefill(prompt, oc16)
+        assert got.shape == (1024, 8000) and cache.length() == 1024
+        assert np.abs(got - want32).max() < 2e-3
+        assert np.abs(got - want16).max() < 5e-4
+        top = np.sort(want16[-1])[::-1]
+        assert int(np.argmax(got[-1])) == int(np.argmax(want16[-1])) or top[0] - top[1] < 1e-4
+        # Layer 0 sees bit-identical inputs: only elements whose fp32 value lies within the projection's rounding
+        # noise of an fp16 boundary may land on the neighbouring value (measured 1.1 %).  Every such element
+        # perturbs all later layers, so deeper layers hold more neighbouring values (measured 75-79 % exact, with
+        # the mma.sync projections 79-85 %) - but never anything farther than one fp16 step from the oracle.
+        for layer in (0, 5, 11):
+            for got_p, want_p in ((cache.getK(layer).to_host(), oc16.k(layer)), (cache.getV(layer).to_host(), oc16.v(layer))):
+                ulp = np.maximum(np.abs(want_p), 2.0 ** -14) * 2.0 ** -10
+                # one fp16 step, plus the drift of the fp32 activations themselves below layer 0 (the same few
+                # 1e-4 the logits are allowed)
+                assert (np.abs(got_p - want_p) <= ulp + (2e-4 if layer == 0 else 1e-3)).all()
+                assert (got_p == want_p).mean() > (0.97 if layer == 0 else 0.6)
+    finally:
+        cache.close(), gm.close(), om.close()
