@@ -28,6 +28,7 @@ struct PrefillParams {
     const float2 *rope;
     const float *q, *k, *v;
     float *out;
+    float *out_image;  // != nullptr (d_head 16): write the output as the tcgen05 projection's operand image instead
     const PrefillSeq *seqs;
     int *status;
     int n_seqs, n_rows, H, layer, n_blocks, mbs, max_positions;
@@ -272,6 +273,30 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillPara
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
     const float iA = 1.f / fmaxf(lA, 1e-12f), iB = 1.f / fmaxf(lB, 1e-12f);
     const size_t D = (size_t)P.H * DH;
+    if (P.out_image) {
+        // Operand image of the next projection (see gemm_umma.cu): 128-row tiles x 16-wide k tiles, TF32 high parts
+        // then low parts; head h is k tile h.  Lane (g, t) holds columns 8j + 2t, 8j + 2t + 1: half of the 16-byte
+        // chunk 2j + t / 2, so a warp store covers eight rows x two chunks = two full 128-byte lines.
+        auto put = [&](int row, int j, float a, float b) {
+            const size_t grow = (size_t)sd.row0 + row;
+            float *tile = P.out_image + ((grow >> 7) * (size_t)P.H + h) * (size_t)(128 * 16 * 2);
+            const int rr = (int)(grow & 127), k4 = 2 * j + (t >> 1);
+            float *dst = tile + (rr >> 3) * 128 + k4 * 32 + (rr & 7) * 4 + (t & 1) * 2;
+            uint32_t ha, hb, la, lb;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(ha) : "f"(a));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(b));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(la) : "f"(a - __uint_as_float(ha)));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(b - __uint_as_float(hb)));
+            *reinterpret_cast<float2 *>(dst) = make_float2(__uint_as_float(ha), __uint_as_float(hb));
+            *reinterpret_cast<float2 *>(dst + 128 * 16) = make_float2(__uint_as_float(la), __uint_as_float(lb));
+        };
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            if (rowA < sd.S) put(rowA, j, o[j][0] * iA, o[j][1] * iA);
+            if (rowB < sd.S) put(rowB, j, o[j][2] * iB, o[j][3] * iB);
+        }
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < 2; j++) {
         if (rowA < sd.S)
@@ -341,7 +366,8 @@ __global__ void __launch_bounds__(128) attn_prefill_simt_kernel(const PrefillPar
 // Launcher
 // ------------------------------------------------------------------------------------------------
 int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v, const int *seq_ids_host,
-                            const int *seq_starts_host, const int *rope_offsets_host, int n_seqs, float *out) {
+                            const int *seq_starts_host, const int *rope_offsets_host, int n_seqs, float *out, float *out_image) {
+    JGPT_REQUIRE(!out_image || p->dhead == 16, JGPT_ERR_INVALID_ARGUMENT, "image output needs d_head 16");
     std::vector<PrefillSeq> desc((size_t)n_seqs);
     int max_S = 0;
     for (int i = 0; i < n_seqs; i++) {
@@ -369,7 +395,7 @@ int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, 
                                   p->ctx->stream));  // pageable source: staged before the call returns
     PrefillParams P;
     memset(&P, 0, sizeof(P));
-    P.kv = p->kv, P.table = p->d_table, P.rope = p->d_rope, P.q = q, P.k = k, P.v = v, P.out = out;
+    P.kv = p->kv, P.table = p->d_table, P.rope = p->d_rope, P.q = q, P.k = k, P.v = v, P.out = out, P.out_image = out_image;
     P.seqs = reinterpret_cast<const PrefillSeq *>(p->d_prefill_desc), P.status = p->ctx->d_status;
     P.n_seqs = n_seqs, P.n_rows = n_rows, P.H = p->heads, P.layer = layer, P.n_blocks = p->n_blocks;
     P.mbs = p->max_blocks_per_seq, P.max_positions = p->max_positions;

@@ -153,6 +153,6 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
                            int max_len, float *out);
 int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v,
                             const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
-                            int n_seqs, float *out);
+                            int n_seqs, float *out, float *out_image = nullptr);
 
 }  // namespace jgpt

@@ -20,8 +20,8 @@
 // Activation images are written by whatever produces the activation: the RMSNorm packer, the SwiGLU epilogue
 // of the W1/W3 product, or the plain packer (attention output).
 //
-// Roles in the 192-thread CTA: warp 0 lane 0 issues the bulk copies, warp 1 allocates tensor memory and its
-// lane 0 issues the MMAs, warps 2-5 are the epilogue (TMEM lane quarter = warp % 4).  Stages are handed over
+// Roles in the 320-thread CTA: warp 0 lane 0 issues the bulk copies, warp 1 allocates tensor memory and its
+// lane 0 issues the MMAs, warps 2-9 are the epilogue (TMEM lane quarter = warp % 4, two warps per quarter).  Stages are handed over
 // with mbarriers: full[s] by the copies' complete_tx, empty[s] and "accumulator buffer ready" by
 // tcgen05.commit, "accumulator buffer drained" by the epilogue warps.  Every wait is bounded; on expiry the status word gets DEV_STATUS_WAIT_TIMEOUT and the CTA
 // winds down through the common exit (tensor memory is always released).
@@ -36,7 +36,8 @@ constexpr int A_TILE_FLOATS = BM * BK * 2;
 constexpr uint32_t A_TILE_BYTES = A_TILE_FLOATS * 4;
 constexpr uint32_t TMEM_COLS = 512;  // two accumulator buffers of 256 columns
 constexpr uint32_t LBO = 128, SBO = 512;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;  // two per TMEM lane quarter, each draining half of the tile's columns
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 
 // ------------------------------------------------------------------------------------------------
 // Packing
@@ -278,7 +279,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(&full_bar[s], 1), mbar_init(&empty_bar[s], 1);
-        for (int b = 0; b < 2; b++) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+        for (int b = 0; b < 2; b++) mbar_init(&acc_full[b], 1), mbar_init(&acc_empty[b], EPI_WARPS);  // one arrival per epilogue warp
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -348,6 +349,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
         }
     } else {
         const int quarter = warp & 3;  // a warp reads TMEM lanes [32 * (warp % 4), +32)
+        const int half = (warp - 2) >> 2;  // which half of the tile's columns
         const int rloc = quarter * 32 + lane;
         uint32_t j = 0;
         for (int t = blockIdx.x; t < walk.total; t += gridDim.x, j++) {
@@ -363,9 +365,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
                 const int m = m_idx * BM + rloc, n0 = n_idx * BN;
                 float *__restrict__ C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);  // selects, not an indexed copy of B
                 const float *__restrict__ R = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (n0 + c0 >= N) break;  // uniform across the CTA
+#pragma unroll 2
+                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+                    if (n0 + c0 >= N) break;  // uniform across the warp
                     float v[32];
                     load_acc32(acc, quarter, c0, v);
                     if (m < M) {
@@ -389,7 +391,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
                 const int out_nkt = N / BK;
                 float *__restrict__ out = B.C[0] + (size_t)m_idx * out_nkt * A_TILE_FLOATS + chunk_offset(rloc, 0);
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 32) {
+                for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
                     float h[32], g[32];
                     load_acc32(acc, quarter, c0, h);
                     load_acc32(acc, quarter, 128 + c0, g);

@@ -484,8 +484,10 @@ static int32_t ensure_logits(Model *m, int rows) {
 // The same decoder blocks for prefill-sized `rows`: every projection on the tcgen05 kernel, activations handed
 // from producer to consumer as operand images (RMSNorm writes one, the W1/W3 product's SwiGLU epilogue writes
 // one; only the attention output is packed by a kernel of its own).
+// attn(l, image): attention of layer l; writes the Wo operand image itself when image != nullptr (only asked
+// for when attn_writes_image), the row-major m->att otherwise.
 template <class AttnFn>
-static int32_t run_layers_umma(Model *m, int rows, AttnFn &&attn) {
+static int32_t run_layers_umma(Model *m, int rows, bool attn_writes_image, AttnFn &&attn) {
     const int D = m->d_model, F = m->d_ff;
     cudaStream_t st = m->ctx->stream;
     int *status = m->ctx->d_status;
@@ -507,8 +509,8 @@ static int32_t run_layers_umma(Model *m, int rows, AttnFn &&attn) {
         w2.C[0] = m->x, w2.R[0] = m->x;
         if ((rc = umma::rmsnorm_pack(m->x, y.norm1, rows, D, m->eps, m->aimg, st))) return rc;
         if ((rc = umma::launch(m->aimg, qkv, 3, rows, D, D, status, st))) return rc;
-        if ((rc = attn(l))) return rc;
-        if ((rc = umma::pack_activations(m->att, nullptr, rows, D, m->aimg, st))) return rc;
+        if ((rc = attn(l, attn_writes_image ? m->aimg : nullptr))) return rc;
+        if (!attn_writes_image && (rc = umma::pack_activations(m->att, nullptr, rows, D, m->aimg, st))) return rc;
         if ((rc = umma::launch(m->aimg, wo, 1, rows, D, D, status, st))) return rc;
         if ((rc = umma::rmsnorm_pack(m->x, y.norm2, rows, D, m->eps, m->aimg, st))) return rc;
         if (fused_ffn) {
@@ -531,11 +533,11 @@ static int32_t run_layers_umma(Model *m, int rows, AttnFn &&attn) {
 }
 
 template <class AttnFn>
-static int32_t run_layers(Model *m, int rows, AttnFn &&attn) {
+static int32_t run_layers(Model *m, int rows, bool attn_writes_image, AttnFn &&attn) {
     const int D = m->d_model, F = m->d_ff;
     if (!m->strict && m->umma_min_rows > 0 && rows >= m->umma_min_rows && umma::shape_ok(D, D) && umma::shape_ok(D, F) &&
         umma::shape_ok(F, D) && sizeof(float) * 8 * (size_t)(D + 4) <= 48 * 1024)
-        return run_layers_umma(m, rows, attn);
+        return run_layers_umma(m, rows, attn_writes_image, attn);
     cudaStream_t st = m->ctx->stream;
     for (int l = 0; l < m->layers; l++) {
         const LayerW &y = m->L[(size_t)l];
@@ -544,7 +546,7 @@ static int32_t run_layers(Model *m, int rows, AttnFn &&attn) {
         float *Cqkv[3] = {m->q, m->k, m->v};
         int32_t rc = gemm(m, m->xn, rows, D, D, 3, Wqkv, Cqkv, nullptr);
         if (rc) return rc;
-        rc = attn(l);
+        rc = attn(l, nullptr);
         if (rc) return rc;
         const float *Wo[1] = {y.wo};
         float *Co[1] = {m->x};
@@ -828,8 +830,10 @@ int32_t jgpt_forward_prefill_batch(jgpt_model h, jgpt_kvpool poolh, const int32_
     cudaStream_t st = m->ctx->stream;
     JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 2 * (size_t)rows, cudaMemcpyHostToDevice, st));
     embed_pos_kernel<<<rows, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + rows, m->x, m->d_model);
-    rc = run_layers(m, rows, [&](int l) {
-        return launch_attn_prefill(p, l, m->q, m->k, m->v, seq_ids_host, seq_starts_host, rope_offsets_host, n, m->att);
+    // d_head 16: one head is exactly one 16-wide k tile of the Wo operand image, which the attention kernel can
+    // then write itself
+    rc = run_layers(m, rows, p->dhead == 16, [&](int l, float *image) {
+        return launch_attn_prefill(p, l, m->q, m->k, m->v, seq_ids_host, seq_starts_host, rope_offsets_host, n, m->att, image);
     });
     if (rc) return rc;
     int n_sel = 0;
@@ -905,7 +909,7 @@ int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_
     cudaStream_t st = m->ctx->stream;
     JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
     embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model);
-    rc = run_layers(m, n, [&](int l) {
+    rc = run_layers(m, n, false, [&](int l, float *) {
         return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, max_len, m->att);
     });
     if (rc) return rc;
