@@ -248,7 +248,7 @@ __device__ __forceinline__ void load_acc32(uint32_t tmem_acc, int quarter, int c
 // epilogue warps drain tile j, the MMA thread is already accumulating tile j + 1, and the bulk copies run
 // ahead of both through the stage ring.
 //
-// MODE 0: C (+ R) row major.  MODE 1 (BN = 256 over a W1/W3 pair image): columns [0,128) of the tile are h1,
+// MODE 0: C row major.  MODE 2: C = R + product.  MODE 1 (BN = 256 over a W1/W3 pair image): columns [0,128) of the tile are h1,
 // columns [128,256) are g for the same 128 outputs; the epilogue writes h1 * g * sigmoid(g) (sigmoid clamped
 // to 1 / 0 at |g| >= 20: sigmoid_kernel, mul_kernel, src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:799-832)
 // as the activation image of the next product.
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
     constexpr int W_TILE_FLOATS = BN * BK * 2;
     constexpr uint32_t W_TILE_BYTES = W_TILE_FLOATS * 4, STAGE_BYTES = A_TILE_BYTES + W_TILE_BYTES;
     constexpr uint32_t IDESC = instr_desc<BN>();
-    static_assert(BN % 16 == 0 && BN <= 256 && (MODE == 0 || BN == 256), "bad tile width");
+    static_assert(BN % 64 == 0 && BN <= 256 && (MODE != 1 || BN == 256), "bad tile width");
     extern __shared__ uint8_t umma_smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t s_tmem_base;
@@ -354,30 +354,45 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
         uint32_t j = 0;
         for (int t = blockIdx.x; t < walk.total; t += gridDim.x, j++) {
             const uint32_t buf = j & 1u, round = j >> 1;
+            const uint32_t acc = tmem + buf * 256u;
+            const int n_idx = t % walk.n_tiles_n, z = (t / walk.n_tiles_n) % walk.nb, m_idx = t / (walk.n_tiles_n * walk.nb);
+            const int m = m_idx * BM + rloc, n0 = n_idx * BN;
+            constexpr int SLABS = BN / 2 / 32;  // 32-column slabs per warp
+            float4 res[MODE == 2 ? SLABS : 1][8];
+            if (MODE == 2) {
+                // The residual rows of this tile are requested before the accumulator is ready: their latency hides
+                // behind the MMAs.  (R may be C itself: every element is read, then written, by this one thread.)
+                const float *R = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
+#pragma unroll
+                for (int sl = 0; sl < SLABS; sl++)
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const int n = n0 + half * (BN / 2) + sl * 32 + q * 4;
+                        res[sl][q] = (m < M && n < N) ? *reinterpret_cast<const float4 *>(R + (size_t)m * N + n)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+            }
             int ok = 0;
             if (lane == 0) ok = mbar_wait_bounded(&acc_full[buf], round & 1u, status, s_abort) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t acc = tmem + buf * 256u;
-            const int n_idx = t % walk.n_tiles_n, z = (t / walk.n_tiles_n) % walk.nb, m_idx = t / (walk.n_tiles_n * walk.nb);
-            if (MODE == 0) {
-                const int m = m_idx * BM + rloc, n0 = n_idx * BN;
-                float *__restrict__ C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);  // selects, not an indexed copy of B
-                const float *__restrict__ R = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
-#pragma unroll 2
-                for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+            if (MODE != 1) {
+                float *C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);  // selects, not an indexed copy of B
+#pragma unroll
+                for (int sl = 0; sl < SLABS; sl++) {
+                    const int c0 = half * (BN / 2) + sl * 32;
                     if (n0 + c0 >= N) break;  // uniform across the warp
                     float v[32];
                     load_acc32(acc, quarter, c0, v);
                     if (m < M) {
 #pragma unroll
-                        for (int q = 0; q < 32; q += 4) {
-                            const int n = n0 + c0 + q;
+                        for (int q = 0; q < 8; q++) {
+                            const int n = n0 + c0 + q * 4;
                             if (n < N) {
-                                float4 o = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-                                if (R) {
-                                    const float4 r4 = *reinterpret_cast<const float4 *>(R + (size_t)m * N + n);
+                                float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                                if (MODE == 2) {
+                                    const float4 r4 = res[sl][q];
                                     o.x += r4.x, o.y += r4.y, o.z += r4.z, o.w += r4.w;
                                 }
                                 *reinterpret_cast<float4 *>(C + (size_t)m * N + n) = o;
@@ -454,8 +469,11 @@ int32_t launch(const float *Aimg, const Batch &b, int nb, int M, int K, int N, i
     const int bn = tile_cols(N);
     TileWalk walk{(N + bn - 1) / bn, nb, 0};
     walk.total = walk.n_tiles_n * nb * ((M + BM - 1) / BM);
-    if (bn == 256) return launch_t<256, 4, 0>(walk, Aimg, b, M, K, N, d_status, st);
-    return launch_t<192, 5, 0>(walk, Aimg, b, M, K, N, d_status, st);
+    bool residual = b.R[0] != nullptr;
+    for (int z = 0; z < nb; z++)
+        JGPT_REQUIRE((b.R[z] != nullptr) == residual, JGPT_ERR_INVALID_ARGUMENT, "gemm_umma: residuals for all products of a batch or for none");
+    if (bn == 256) return residual ? launch_t<256, 4, 2>(walk, Aimg, b, M, K, N, d_status, st) : launch_t<256, 4, 0>(walk, Aimg, b, M, K, N, d_status, st);
+    return residual ? launch_t<192, 5, 2>(walk, Aimg, b, M, K, N, d_status, st) : launch_t<192, 5, 0>(walk, Aimg, b, M, K, N, d_status, st);
 }
 
 int32_t launch_swiglu(const float *Aimg, const float *Wpair_img, int M, int K, int F, float *act_image, int *d_status,
