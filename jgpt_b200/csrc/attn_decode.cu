@@ -773,6 +773,18 @@ static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int t
     return JGPT_OK;
 }
 
+// Split-K chunk length of a launch with `base` (layer, sequence, head group) triples of up to max_blocks KV blocks.
+// Two CTAs fit on an SM.  When the triples alone fill those slots the launch runs in several waves anyway and
+// 32-block chunks keep the per-item set-up small.  Otherwise every sequence is cut into as many chunks as still
+// fit in ONE wave (a few CTAs spilling into a second wave would double the launch time), at least 4 blocks each.
+static int pick_chunk_blocks(const Pool *p, long long base, int max_blocks) {
+    const long long slots = 2ll * p->ctx->sm_count;
+    if (base >= slots) return 32;
+    const long long nsplit = std::max(1ll, std::min(slots / base, (long long)(max_blocks + 3) / 4));
+    const int cb = (int)((max_blocks + nsplit - 1) / nsplit);
+    return std::min(32, std::max(4, cb));
+}
+
 int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, const float *k_new, const float *v_new,
                            const int *seq_ids, const int *rope_pos, const int *lens, int n, int max_len, float *out) {
     DecodeParams P;
@@ -790,19 +802,10 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     // Work distribution.  Default (persistent <= 0): one CTA per work item, the hardware block scheduler hands
     // items to SMs as CTAs retire.  persistent = k > 0: k CTAs per SM claim items from a global counter (kept
     // for experiments: on B200 it measured 4-15 % slower than the plain grid at every chunk length).
-    const long long total_blocks = (long long)n_layers * n * (p->heads / P.HG) * max_blocks;
     const int per_sm = p->persistent > 0 ? p->persistent : 2;
     const long long slots = (long long)per_sm * p->ctx->sm_count;
     const bool dynamic = p->persistent > 0;
-    if (p->chunk_blocks > 0) {
-        P.chunk_blocks = p->chunk_blocks;
-    } else {
-        // Few items: one CTA per item; chunks as long as possible while the launch still offers ~1.5 CTAs per SM.
-        const long long want_items = 3ll * p->ctx->sm_count / 2;
-        int cb = 32;
-        while (cb > 4 && total_blocks / cb < want_items) cb >>= 1;
-        P.chunk_blocks = cb;
-    }
+    P.chunk_blocks = p->chunk_blocks > 0 ? p->chunk_blocks : pick_chunk_blocks(p, (long long)n_layers * n * P.n_hg, max_blocks);
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
     P.stages = p->stages;
@@ -1010,15 +1013,7 @@ static int32_t launch_attn_decode_static(Pool *p, int layer, const float *q, con
     P.HG = pick_head_group(p->heads, DH, p->head_group);
     P.n_hg = p->heads / P.HG;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
-    if (p->chunk_blocks > 0) {
-        P.chunk_blocks = p->chunk_blocks;
-    } else {
-        const long long total_blocks = (long long)n * P.n_hg * max_blocks;
-        const long long want_items = 3ll * p->ctx->sm_count / 2;
-        int cb = 32;
-        while (cb > 4 && total_blocks / cb < want_items) cb >>= 1;
-        P.chunk_blocks = cb;
-    }
+    P.chunk_blocks = p->chunk_blocks > 0 ? p->chunk_blocks : pick_chunk_blocks(p, (long long)n * P.n_hg, max_blocks);
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
     P.stages = p->stages;
