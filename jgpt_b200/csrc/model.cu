@@ -42,12 +42,16 @@ struct Model {
     std::unordered_map<const float *, float *> wpair;  // W1/W3 pair images by W1's pointer
     float *aimg = nullptr, *aimg2 = nullptr;  // activation images (grow-only): [rows, d_model]-sized and [rows, d_ff]-sized
     uint64_t aimg_floats = 0, aimg2_floats = 0;
+    // Decode-sized steps (rows <= 512): RMSNorm and SwiGLU live inside the projections.
+    float *ss_a = nullptr, *ss_b = nullptr;           // [max_rows][ceil(d_model / 32)] partial row sums of squares of x
+    std::unordered_map<const float *, float *> w13i;  // interleaved W1/W3 pairs by W1's pointer; dropped when weights change
 };
 
 static void drop_weight_images(Model *m) {
     for (auto &kv : m->wimg) cudaFree(kv.second);
     for (auto &kv : m->wpair) cudaFree(kv.second);
-    m->wimg.clear(), m->wpair.clear();
+    for (auto &kv : m->w13i) cudaFree(kv.second);
+    m->wimg.clear(), m->wpair.clear(), m->w13i.clear();
 }
 
 Registry<Model> &model_registry() {
@@ -63,15 +67,25 @@ Registry<Model> &model_registry() {
 // src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:937-955, 1020-1032)
 __global__ void __launch_bounds__(128) embed_pos_kernel(const float *__restrict__ tok, const float *__restrict__ pos,
                                                         const int *__restrict__ ids, const int *__restrict__ posrow,
-                                                        float *__restrict__ x, int D) {
+                                                        float *__restrict__ x, int D, float *__restrict__ ss_out) {
+    __shared__ float red[4];
     const int r = blockIdx.x;
     const float4 *t = reinterpret_cast<const float4 *>(tok + (size_t)ids[r] * D);
     const float4 *p = reinterpret_cast<const float4 *>(pos + (size_t)posrow[r] * D);
     float4 *o = reinterpret_cast<float4 *>(x + (size_t)r * D);
+    float ss = 0.f;
     for (int j = threadIdx.x; j < D / 4; j += blockDim.x) {
         const float4 a = t[j], b = p[j];
-        o[j] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+        const float4 v = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+        o[j] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
+    // sum of squares of the row (one partial): what the first fused RMSNorm of the decode-sized path consumes
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) ss_out[r] = red[0] + red[1] + red[2] + red[3];
 }
 
 // RMSNorm, one block per row (rms_norm_fwd_block_kernel, same file :694-713):
@@ -322,9 +336,24 @@ constexpr int kSmallBK = 64;
 template <int STAGES>
 __host__ __device__ constexpr size_t gemm_small_smem_bytes() { return sizeof(float) * (size_t)STAGES * (16 * (kSmallBK + 4) + kSmallBK * (32 + 8)); }
 
-template <int STAGES>
+//
+// Fusions of the decode step (template flags):
+//   NORM  A is RMS-normalised on the fly: y = x * inv * gamma with inv from the row's sum of squares, which the
+//         PRODUCER of x has left as `parts_in` partial sums per row (added in ascending order: deterministic).
+//   EPI 1 the epilogue also writes the sum of squares of its 32 output columns of every row (one partial per
+//         column tile) for the next NORM.
+//   EPI 2 W is a W1/W3 pair interleaved in groups of 16 columns; the epilogue writes h1 * g * sigmoid(g)
+//         (16 columns of [M, N / 2]), sigmoid clamped to 1 / 0 at |g| >= 20 like swiglu_kernel.
+struct SmallFuse {
+    const float *gamma, *ss_in;
+    float *ss_out;
+    int parts_in;
+    float eps;
+};
+
+template <int STAGES, bool NORM, int EPI>
 __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restrict__ A, const GemmBatch B, int M, int K, int N,
-                                                            const int *__restrict__ rowsel) {
+                                                            const int *__restrict__ rowsel, const SmallFuse F) {
     constexpr int BM = 16, BN = 32, BK = kSmallBK, AS = BK + 4, WS = BN + 8;
     static_assert(STAGES >= 2 && sizeof(float) * 8 * BM * (BN + 1) <= gemm_small_smem_bytes<STAGES>(), "reduction buffer must fit");
     extern __shared__ __align__(16) float gemm_smem[];
@@ -363,18 +392,38 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         if (s < nk) load_tiles(s, s * BK);
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    __shared__ float s_inv[BM];
+    if (NORM && tid < BM) {
+        const int m = m0 + tid;
+        float inv = 0.f;
+        if (m < M) {
+            const float *pp = F.ss_in + (size_t)(rowsel ? rowsel[m] : m) * F.parts_in;
+            float tot = 0.f;
+            for (int i = 0; i < F.parts_in; i++) tot += pp[i];
+            const float rms = sqrtf(tot / (float)K + F.eps);
+            inv = (rms > 0.f && isfinite(rms)) ? (1.f / rms) : 0.f;
+        }
+        s_inv[tid] = inv;
+    }
     const int ks = warp * 8;
     for (int kt = 0; kt < nk; kt++) {
         const int buf = kt % STAGES;
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
-        __syncthreads();  // tile kt visible to all; everyone is done with the buffer refilled below (read at kt-1)
+        __syncthreads();  // tile kt (and s_inv) visible to all; everyone is done with the buffer refilled below (read at kt-1)
         if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
         else asm volatile("cp.async.commit_group;" ::: "memory");
+        float a0 = As[buf][g][ks + t], a1 = As[buf][g + 8][ks + t], a2 = As[buf][g][ks + t + 4], a3 = As[buf][g + 8][ks + t + 4];
+        if (NORM) {
+            const int k = kt * BK + ks + t;
+            const float g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
+            const float ia = s_inv[g], ib = s_inv[g + 8];
+            a0 = a0 * ia * g0, a1 = a1 * ib * g0, a2 = a2 * ia * g1, a3 = a3 * ib * g1;
+        }
         uint32_t ah[4], al[4];
-        split_tf32(As[buf][g][ks + t], ah[0], al[0]);
-        split_tf32(As[buf][g + 8][ks + t], ah[1], al[1]);
-        split_tf32(As[buf][g][ks + t + 4], ah[2], al[2]);
-        split_tf32(As[buf][g + 8][ks + t + 4], ah[3], al[3]);
+        split_tf32(a0, ah[0], al[0]);
+        split_tf32(a1, ah[1], al[1]);
+        split_tf32(a2, ah[2], al[2]);
+        split_tf32(a3, ah[3], al[3]);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int c = j * 8 + g;
@@ -399,15 +448,49 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     __syncthreads();
     float *C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);
     const float *R = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
-    for (int e = tid; e < BM * BN; e += 256) {
-        const int r = e >> 5, c = e & 31, m = m0 + r, n = n0 + c;
-        if (m >= M || n >= N) continue;
-        float v = red[0][r][c];
+    if (EPI == 2) {
+        const int r = tid >> 4, c = tid & 15, m = m0 + r, n = blockIdx.x * 16 + c, Fo = N / 2;
+        if (m < M && n < Fo) {
+            float h = red[0][r][c], gv = red[0][r][16 + c];
 #pragma unroll
-        for (int w = 1; w < 8; w++) v += red[w][r][c];
-        if (R) v += R[(size_t)m * N + n];
-        C[(size_t)m * N + n] = v;
+            for (int w = 1; w < 8; w++) h += red[w][r][c], gv += red[w][r][16 + c];
+            float sg;
+            if (gv >= 20.f) sg = 1.f;
+            else if (gv <= -20.f) sg = 0.f;
+            else sg = 1.f / (1.f + expf(-gv));
+            C[(size_t)m * Fo + n] = h * (gv * sg);
+        }
+        return;
     }
+    for (int e = tid; e < BM * BN; e += 256) {  // one warp = one row of the tile per iteration
+        const int r = e >> 5, c = e & 31, m = m0 + r, n = n0 + c;
+        const bool ok = m < M && n < N;
+        float v = 0.f;
+        if (ok) {
+            v = red[0][r][c];
+#pragma unroll
+            for (int w = 1; w < 8; w++) v += red[w][r][c];
+            if (R) v += R[(size_t)m * N + n];
+            C[(size_t)m * N + n] = v;
+        }
+        if (EPI == 1) {
+            float sq = v * v;
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+            if (lane == 0 && m < M) F.ss_out[(size_t)m * gridDim.x + blockIdx.x] = sq;
+        }
+    }
+}
+
+// W1, W3 [K, Fo] -> [K, 2 Fo] with groups of 16 columns alternating (what EPI 2 expects).
+__global__ void __launch_bounds__(256) interleave_pair_kernel(const float *__restrict__ W1, const float *__restrict__ W3, int K, int Fo,
+                                                              float *__restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)K * 2 * Fo) return;
+    const int k = (int)(i / (2 * Fo)), c = (int)(i % (2 * Fo));
+    const int tile = c >> 5, within = c & 31;
+    const int col = tile * 16 + (within & 15);
+    out[i] = within < 16 ? W1[(size_t)k * Fo + col] : W3[(size_t)k * Fo + col];
 }
 
 // Greedy argmax per row, ties -> lowest index (argmaxLogitsGreedy,
@@ -441,6 +524,21 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
+// The larger tile configurations need more than 48 KiB of dynamic shared memory: once per device.
+static cudaError_t opt_in_shared_memory(const Ctx *ctx) {
+    static bool opted[64] = {};
+    if (opted[ctx->device & 63]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)gemm_tc_smem_bytes<64, 64, 3>());
+    const int sb = (int)gemm_small_smem_bytes<4>();
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) opted[ctx->device & 63] = true;
+    return e;
+}
+
 // The mma.sync / scalar kernels (any M; what decode-sized products use).
 static int32_t gemm_small(Ctx *ctx, int strict, const float *A, int M, int K, int N, int nb, const float *const *W,
                           float *const *C, const float *const *R, const int *rowsel) {
@@ -449,17 +547,10 @@ static int32_t gemm_small(Ctx *ctx, int strict, const float *A, int M, int K, in
     cudaStream_t st = ctx->stream;
     if (!strict && K % 4 == 0 && N % 4 == 0) {  // tensor cores, 3xTF32
         // Decode-sized M: 16x32 tiles, the k loop split over eight warps (latency); above that 64x64 tiles.
-        static bool opted[64] = {};  // per device: the 64x64 tile needs more than 48 KiB of dynamic shared memory
-        if (!opted[ctx->device & 63]) {
-            JGPT_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)gemm_tc_smem_bytes<64, 64, 3>()));
-            JGPT_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_small_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)gemm_small_smem_bytes<4>()));
-            opted[ctx->device & 63] = true;
-        }
+        JGPT_CUDA_TRY(opt_in_shared_memory(ctx));
         if (M <= 512) {  // measured: faster than 32x32 tiles of four warps up to here (batch 128: 1.34 -> 1.04 ms per decode step)
             dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
-            gemm_tc_small_kernel<4><<<grid, 256, gemm_small_smem_bytes<4>(), st>>>(A, B, M, K, N, rowsel);
+            gemm_tc_small_kernel<4, false, 0><<<grid, 256, gemm_small_smem_bytes<4>(), st>>>(A, B, M, K, N, rowsel, SmallFuse{});
         } else {
             dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
             gemm_tc_kernel<64, 64, 2, 2, 3><<<grid, 128, gemm_tc_smem_bytes<64, 64, 3>(), st>>>(A, B, M, K, N, rowsel);
@@ -628,9 +719,69 @@ static int32_t run_layers_umma(Model *m, int rows, bool attn_writes_image, AttnF
     return JGPT_OK;
 }
 
+// Decode-sized steps: every projection on gemm_tc_small_kernel with RMSNorm folded into the consumer (the producer
+// of x leaves partial row sums of squares) and SwiGLU into the W1/W3 product: 4 projection launches + attention per
+// layer instead of 7 launches + attention.
+static bool small_mode(const Model *m, int rows) {
+    return !m->strict && rows <= 512 && m->d_model % 4 == 0 && m->d_ff % 16 == 0 && m->vocab % 4 == 0 &&
+           !(m->umma_min_rows > 0 && rows >= m->umma_min_rows);
+}
+static int32_t pair_interleaved(Model *m, const float *W1, const float *W3, int K, int Fo, const float **out) {
+    auto it = m->w13i.find(W1);
+    if (it == m->w13i.end()) {
+        float *buf = nullptr;
+        JGPT_CUDA_TRY(cudaMalloc(&buf, sizeof(float) * (size_t)K * 2 * Fo));
+        it = m->w13i.emplace(W1, buf).first;
+        const long long n = (long long)K * 2 * Fo;
+        interleave_pair_kernel<<<(unsigned)((n + 255) / 256), 256, 0, m->ctx->stream>>>(W1, W3, K, Fo, buf);
+        JGPT_CUDA_TRY(cudaGetLastError());
+    }
+    *out = it->second;
+    return JGPT_OK;
+}
+template <bool NORM, int EPI>
+static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
+                            const float *const *R, const int *rowsel, const SmallFuse &fuse) {
+    JGPT_CUDA_TRY(opt_in_shared_memory(m->ctx));
+    GemmBatch B;
+    for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
+    dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
+    gemm_tc_small_kernel<4, NORM, EPI><<<grid, 256, gemm_small_smem_bytes<4>(), m->ctx->stream>>>(A, B, M, K, N, rowsel, fuse);
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
+template <class AttnFn>
+static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
+    const int D = m->d_model, F = m->d_ff, parts = (D + 31) / 32;
+    for (int l = 0; l < m->layers; l++) {
+        const LayerW &y = m->L[(size_t)l];
+        int32_t rc;
+        // x's sums of squares: one partial per row from the embedding, `parts` from a residual projection
+        const SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps};
+        const float *Wqkv[3] = {y.wq, y.wk, y.wv};
+        float *Cqkv[3] = {m->q, m->k, m->v};
+        if ((rc = small_launch<true, 0>(m, m->x, rows, D, D, 3, Wqkv, Cqkv, nullptr, nullptr, n1))) return rc;
+        if ((rc = attn(l, nullptr))) return rc;
+        const float *Wo[1] = {y.wo};
+        float *Cx[1] = {m->x};
+        const float *Rx[1] = {m->x};  // x1 = x + attn.Wo (each element read then written by the same thread)
+        if ((rc = small_launch<false, 1>(m, m->att, rows, D, D, 1, Wo, Cx, Rx, nullptr, SmallFuse{nullptr, nullptr, m->ss_b, 0, 0.f}))) return rc;
+        const float *pair = nullptr;
+        if ((rc = pair_interleaved(m, y.w1, y.w3, D, F, &pair))) return rc;
+        const float *Wp[1] = {pair};
+        float *Ch[1] = {m->h1};
+        if ((rc = small_launch<true, 2>(m, m->x, rows, D, 2 * F, 1, Wp, Ch, nullptr, nullptr, SmallFuse{y.norm2, m->ss_b, nullptr, parts, m->eps}))) return rc;
+        const float *W2[1] = {y.w2};
+        if ((rc = small_launch<false, 1>(m, m->h1, rows, F, D, 1, W2, Cx, Rx, nullptr, SmallFuse{nullptr, nullptr, m->ss_a, 0, 0.f}))) return rc;
+    }
+    return JGPT_OK;
+}
+
 template <class AttnFn>
 static int32_t run_layers(Model *m, int rows, bool attn_writes_image, AttnFn &&attn) {
     const int D = m->d_model, F = m->d_ff;
+    if (small_mode(m, rows)) return run_layers_small(m, rows, attn);
     if (!m->strict && m->umma_min_rows > 0 && rows >= m->umma_min_rows && umma::shape_ok(D, D) && umma::shape_ok(D, F) &&
         umma::shape_ok(F, D) && sizeof(float) * 8 * (size_t)(D + 4) <= 48 * 1024)
         return run_layers_umma(m, rows, attn_writes_image, attn);
@@ -668,13 +819,19 @@ static int32_t run_layers(Model *m, int rows, bool attn_writes_image, AttnFn &&a
 static int32_t lm_head(Model *m, int rows, int n_sel) {
     const int D = m->d_model;
     cudaStream_t st = m->ctx->stream;
-    rmsnorm_kernel<<<rows, 128, 0, st>>>(m->x, m->norm_final, m->xn, D, m->eps);
     const int out_rows = n_sel > 0 ? n_sel : rows;
     int32_t rc = ensure_logits(m, out_rows);
     if (rc) return rc;
     const float *W[1] = {m->lm_head};
     float *C[1] = {m->logits};
-    rc = gemm(m, m->xn, out_rows, D, m->vocab, 1, W, C, nullptr, n_sel > 0 ? m->d_rowsel : nullptr);
+    const int *rowsel = n_sel > 0 ? m->d_rowsel : nullptr;
+    if (small_mode(m, rows)) {  // the last W2 projection left the row sums of squares in ss_a
+        rc = small_launch<true, 0>(m, m->x, out_rows, D, m->vocab, 1, W, C, nullptr, rowsel,
+                                   SmallFuse{m->norm_final, m->ss_a, nullptr, (D + 31) / 32, m->eps});
+    } else {
+        rmsnorm_kernel<<<rows, 128, 0, st>>>(m->x, m->norm_final, m->xn, D, m->eps);
+        rc = gemm(m, m->xn, out_rows, D, m->vocab, 1, W, C, nullptr, rowsel);
+    }
     if (rc) return rc;
     argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
     JGPT_CUDA_TRY(cudaGetLastError());
@@ -781,6 +938,8 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     JGPT_CUDA_TRY(cudaMalloc(&m->d_next, sizeof(int) * R));
     JGPT_CUDA_TRY(cudaHostAlloc(&m->h_next, sizeof(int) * R, cudaHostAllocDefault));
     JGPT_CUDA_TRY(cudaMalloc(&m->d_rowsel, sizeof(int) * R));
+    JGPT_CUDA_TRY(A(&m->ss_a, R * ((D + 31) / 32)));
+    JGPT_CUDA_TRY(A(&m->ss_b, R * ((D + 31) / 32)));
     *out = model_registry().add(m);
     return JGPT_OK;
 }
@@ -798,7 +957,7 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     cudaFree(m->g), cudaFree(m->logits), cudaFree(m->d_idx), cudaFree(m->d_next), cudaFree(m->d_rowsel);
     cudaFreeHost(m->h_idx), cudaFreeHost(m->h_next);
     drop_weight_images(m);
-    cudaFree(m->aimg), cudaFree(m->aimg2);
+    cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b);
     delete m;
     return JGPT_OK;
 }
@@ -925,7 +1084,7 @@ int32_t jgpt_forward_prefill_batch(jgpt_model h, jgpt_kvpool poolh, const int32_
     }
     cudaStream_t st = m->ctx->stream;
     JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 2 * (size_t)rows, cudaMemcpyHostToDevice, st));
-    embed_pos_kernel<<<rows, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + rows, m->x, m->d_model);
+    embed_pos_kernel<<<rows, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + rows, m->x, m->d_model, m->ss_a);
     // d_head 16: one head is exactly one 16-wide k tile of the Wo operand image, which the attention kernel can
     // then write itself
     rc = run_layers(m, rows, p->dhead == 16, [&](int l, float *image) {
@@ -1004,7 +1163,7 @@ int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_
     }
     cudaStream_t st = m->ctx->stream;
     JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
-    embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model);
+    embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
     rc = run_layers(m, n, false, [&](int l, float *) {
         return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, max_len, m->att);
     });
