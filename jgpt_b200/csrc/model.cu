@@ -37,7 +37,7 @@ struct Model {
     int *d_rowsel = nullptr;  // [max_rows] rows whose logits are wanted
     int strict = 0;           // 0: tensor-core 3xTF32 projections; 1: k-ordered scalar fp32 (mul + add, two roundings)
     // Prefill-sized products (M >= umma_min_rows) run on the tcgen05 kernel over pre-tiled operand images.
-    int umma_min_rows = 1024;  // JGPT_B200_UMMA_MIN_ROWS; 0: never
+    int umma_min_rows = 513;  // JGPT_B200_UMMA_MIN_ROWS; 0: never
     std::unordered_map<const float *, float *> wimg;   // weight images by source pointer; dropped when weights change
     std::unordered_map<const float *, float *> wpair;  // W1/W3 pair images by W1's pointer
     float *aimg = nullptr, *aimg2 = nullptr;  // activation images (grow-only): [rows, d_model]-sized and [rows, d_ff]-sized
@@ -45,9 +45,29 @@ struct Model {
     // Decode-sized steps (rows <= 512): RMSNorm and SwiGLU live inside the projections.
     float *ss_a = nullptr, *ss_b = nullptr;           // [max_rows][ceil(d_model / 32)] partial row sums of squares of x
     std::unordered_map<const float *, float *> w13i;  // interleaved W1/W3 pairs by W1's pointer; dropped when weights change
+    // Decode steps replayed as CUDA graphs (JGPT_B200_DECODE_GRAPH=0 turns it off).  A step's launches depend on
+    // the batch size, on the attention's length bucket and on the addresses of every buffer involved; all of that
+    // is the key.  A key seen for the second time is captured, from then on replayed.
+    struct DecodeGraph {
+        const void *key[8] = {};
+        int n = 0, len_bucket = 0, geom[3] = {};
+        cudaGraphExec_t exec = nullptr;
+        bool failed = false;  // capture refused once (an allocation or a synchronisation inside): stay eager
+        uint64_t last_use = 0;
+    };
+    std::vector<DecodeGraph> decode_graphs;
+    uint64_t decode_graph_clock = 0;
+    int decode_graph_enabled = 1;
 };
 
+static void drop_decode_graphs(Model *m) {
+    for (auto &g : m->decode_graphs)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    m->decode_graphs.clear();
+}
+
 static void drop_weight_images(Model *m) {
+    drop_decode_graphs(m);  // they hold the addresses freed below
     for (auto &kv : m->wimg) cudaFree(kv.second);
     for (auto &kv : m->wpair) cudaFree(kv.second);
     for (auto &kv : m->w13i) cudaFree(kv.second);
@@ -460,9 +480,8 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             else sg = 1.f / (1.f + expf(-gv));
             C[(size_t)m * Fo + n] = h * (gv * sg);
         }
-        return;
     }
-    for (int e = tid; e < BM * BN; e += 256) {  // one warp = one row of the tile per iteration
+    for (int e = tid; EPI != 2 && e < BM * BN; e += 256) {  // one warp = one row of the tile per iteration
         const int r = e >> 5, c = e & 31, m = m0 + r, n = n0 + c;
         const bool ok = m < M && n < N;
         float v = 0.f;
@@ -860,7 +879,7 @@ extern "C" {
 
 // C[M,N] = A[M,K] . B[K,N], row-major fp32 device buffers, ordered on the context's stream
 // (TensorOpsGPU.matmulGpuDevice, src/main/java/com/veles/llm/jgpt/TensorOpsGPU.java:1393).  Products with at
-// least JGPT_B200_UMMA_MIN_ROWS rows (default 1024) and K % 16 == 0, N % 4 == 0 take the tcgen05 kernel; their
+// least JGPT_B200_UMMA_MIN_ROWS rows (default 513: above what the decode-sized kernel takes) and K % 16 == 0, N % 4 == 0 take the tcgen05 kernel; their
 // operand images live in stream-ordered scratch for the duration of the call.
 int32_t jgpt_matmul_device(jgpt_ctx ctxh, const float *a_dev, const float *b_dev, float *c_dev, int32_t M, int32_t K, int32_t N) {
     Ctx *c = ctx_registry().get(ctxh);
@@ -870,7 +889,7 @@ int32_t jgpt_matmul_device(jgpt_ctx ctxh, const float *a_dev, const float *b_dev
     JGPT_CUDA_TRY(make_current(c));
     const float *W[1] = {b_dev};
     float *C[1] = {c_dev};
-    const int min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 1024);
+    const int min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     const int strict = env_int("JGPT_B200_STRICT_GEMM", 0);
     if (strict || min_rows <= 0 || M < min_rows || !umma::shape_ok(K, N))
         return gemm_small(c, strict, a_dev, M, K, N, 1, W, C, nullptr, nullptr);
@@ -906,7 +925,8 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->ctx = c, m->vocab = vocab, m->max_seq = max_seq_len, m->d_model = d_model, m->heads = heads, m->layers = layers;
     m->d_ff = d_ff, m->eps = rms_eps, m->max_rows = max_rows;
     m->strict = env_int("JGPT_B200_STRICT_GEMM", 0);
-    m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 1024);
+    m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
+    m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -956,7 +976,7 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     cudaFree(m->x), cudaFree(m->xn), cudaFree(m->q), cudaFree(m->k), cudaFree(m->v), cudaFree(m->att), cudaFree(m->h1);
     cudaFree(m->g), cudaFree(m->logits), cudaFree(m->d_idx), cudaFree(m->d_next), cudaFree(m->d_rowsel);
     cudaFreeHost(m->h_idx), cudaFreeHost(m->h_next);
-    drop_weight_images(m);
+    drop_weight_images(m);  // and the decode graphs
     cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b);
     delete m;
     return JGPT_OK;
@@ -1162,17 +1182,72 @@ int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_
         if (rc) return rc;
     }
     cudaStream_t st = m->ctx->stream;
-    JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
-    embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
-    rc = run_layers(m, n, false, [&](int l, float *) {
-        return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, max_len, m->att);
-    });
-    if (rc) return rc;
-    rc = lm_head(m, n, 0);
+    // The attention sizes its split for an upper bound of the lengths; a bound in steps of 128 tokens keeps the
+    // launch shapes of consecutive steps identical (the exact lengths travel in d_idx).
+    const int cap = std::min(m->max_seq, p->max_blocks_per_seq * kBlockTokens);
+    const int len_bucket = std::min(cap, (max_len + 127) / 128 * 128);
+    auto enqueue = [&]() -> int32_t {
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+        embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
+        int32_t r2 = run_layers(m, n, false, [&](int l, float *) {
+            return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att);
+        });
+        if (r2) return r2;
+        r2 = lm_head(m, n, 0);
+        if (r2) return r2;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+        return JGPT_OK;
+    };
+    Model::DecodeGraph *slot = nullptr;
+    if (m->decode_graph_enabled && small_mode(m, n)) {
+        Model::DecodeGraph want;
+        const void *key[8] = {p, p->kv, p->d_table, p->d_partials, p->d_tickets, m->logits, m->d_idx, m->h_idx};
+        for (int i = 0; i < 8; i++) want.key[i] = key[i];
+        want.n = n, want.len_bucket = len_bucket, want.geom[0] = p->n_blocks, want.geom[1] = p->max_blocks_per_seq, want.geom[2] = p->heads;
+        for (auto &g : m->decode_graphs)
+            if (g.n == want.n && g.len_bucket == want.len_bucket && memcmp(g.key, want.key, sizeof(want.key)) == 0 &&
+                memcmp(g.geom, want.geom, sizeof(want.geom)) == 0)
+                slot = &g;
+        if (!slot) {  // first time: run eagerly (this also sizes every grow-only buffer the step needs)
+            if (m->decode_graphs.size() >= 32) {
+                size_t oldest = 0;
+                for (size_t i = 1; i < m->decode_graphs.size(); i++)
+                    if (m->decode_graphs[i].last_use < m->decode_graphs[oldest].last_use) oldest = i;
+                if (m->decode_graphs[oldest].exec) cudaGraphExecDestroy(m->decode_graphs[oldest].exec);
+                m->decode_graphs.erase(m->decode_graphs.begin() + (long)oldest);
+            }
+            want.last_use = ++m->decode_graph_clock;
+            m->decode_graphs.push_back(want);
+            rc = enqueue();
+        } else {
+            slot->last_use = ++m->decode_graph_clock;
+            if (!slot->exec && !slot->failed) {  // second time: capture
+                cudaGraph_t g = nullptr;
+                int32_t crc = JGPT_OK;
+                if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                    crc = enqueue();
+                    const cudaError_t e = cudaStreamEndCapture(st, &g);
+                    if (crc == JGPT_OK && e == cudaSuccess && g && cudaGraphInstantiate(&slot->exec, g, 0) != cudaSuccess) slot->exec = nullptr;
+                    if (g) cudaGraphDestroy(g);
+                }
+                if (!slot->exec) {
+                    slot->failed = true;
+                    cudaGetLastError();  // the refused capture leaves an error behind; the eager run below reports real ones
+                }
+            }
+            if (slot->exec) {
+                const cudaError_t e = cudaGraphLaunch(slot->exec, st);
+                rc = e == cudaSuccess ? JGPT_OK : fail(JGPT_ERR_CUDA, "cudaGraphLaunch: %s", cudaGetErrorString(e));
+            } else {
+                rc = enqueue();
+            }
+        }
+    } else {
+        rc = enqueue();
+    }
     if (rc) return rc;
     if (logits_host)
         JGPT_CUDA_TRY(cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * (size_t)n * m->vocab, cudaMemcpyDeviceToHost, st));
-    JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
     if (next_tokens_host)
         for (int i = 0; i < n; i++) next_tokens_host[i] = m->h_next[i];
