@@ -243,3 +243,54 @@ def test_jgpt_35m_greedy_decode_matches_oracle(ctx):
         assert np.abs(trace[0] - om.forward_prefill(prompt, om.new_cache(kv_fp16=True))[-1]).max() == 0.0
     finally:
         gm.close(), om.close()
+
+
+def test_graph_replayed_decode_steps_equal_eager_ones_and_follow_weight_updates(ctx):
+    """Decode steps are replayed as CUDA graphs from the second step of a (batch size, length bucket) on.  The
+    replayed steps must give the bits of eagerly launched ones (JGPT_B200_DECODE_GRAPH=0), across KV-block and
+    length-bucket boundaries and for two batch sizes; after a weight update the old graphs must be gone."""
+    V, MS, D, H, L, F = 96, 320, 64, 4, 2, 128
+    om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=11, std=0.15)
+    gm_graph = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=512)
+    os.environ["JGPT_B200_DECODE_GRAPH"] = "0"
+    try:
+        gm_eager = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=512)
+    finally:
+        os.environ.pop("JGPT_B200_DECODE_GRAPH")
+    gm_graph.setParameters(om.tensors()), gm_eager.setParameters(om.tensors())
+    pools = [g.newPool(n_blocks=3 * MS // 16, max_seqs=3) for g in (gm_graph, gm_eager)]
+    try:
+        prompts = [np.array([(i * 7 + s) % V for i in range(100 + 9 * s)], np.int32) for s in range(3)]
+        state = []
+        for g, pool in zip((gm_graph, gm_eager), pools):
+            seqs = [pool.seq_alloc() for _ in range(3)]
+            _, nxt = g.forwardPrefillBatch(pool, seqs, prompts)
+            state.append((seqs, nxt.copy(), [len(p) for p in prompts]))
+        assert np.array_equal(state[0][1], state[1][1])
+        for step in range(60):  # lengths 100..178: crosses 16-token blocks and the 128-token bucket
+            active = 3 if step < 40 else 2  # a second batch size: new graphs
+            outs = []
+            for (g, pool), (seqs, nxt, lens) in zip(zip((gm_graph, gm_eager), pools), state):
+                lg, nx = g.forwardDecodeBatch(pool, seqs[:active], nxt[:active], lens[:active], lens[:active])
+                outs.append((lg, nx))
+            assert np.array_equal(outs[0][0], outs[1][0]), step
+            assert np.array_equal(outs[0][1], outs[1][1]), step
+            for (seqs, nxt, lens), (lg, nx) in zip(state, outs):
+                nxt[:active] = nx
+                for i in range(active):
+                    lens[i] += 1
+        # new weights: replayed graphs would still read the old interleaved W1/W3 copies
+        om2 = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=12, std=0.15)
+        gm_graph.setParameters(om2.tensors()), gm_eager.setParameters(om2.tensors())
+        for _ in range(3):
+            outs = []
+            for (g, pool), (seqs, nxt, lens) in zip(zip((gm_graph, gm_eager), pools), state):
+                outs.append(g.forwardDecodeBatch(pool, seqs[:2], nxt[:2], lens[:2], lens[:2]))
+                for i in range(2):
+                    lens[i] += 1
+            assert np.array_equal(outs[0][0], outs[1][0])
+        om2.close()
+    finally:
+        for pool in pools:
+            pool.close()
+        gm_graph.close(), gm_eager.close(), om.close()
