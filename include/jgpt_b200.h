@@ -243,7 +243,10 @@ JGPT_API int32_t jgpt_forward_prefill_batch(jgpt_model model, jgpt_kvpool pool, 
  * cacheLenBefore[i] (must equal the stored length, else JGPT_ERR_ILLEGAL_STATE; full ->
  * JGPT_ERR_ILLEGAL_STATE) and ropePosition[i] (J/model/GptKvForward.java:131-141).
  * logits_host [n, vocab] may be NULL; next_tokens_host [n] (greedy argmax on the device, ties ->
- * lowest id, J/model/GptAutoregressiveGenerator.java:288-299) may be NULL.  Lengths become +1. */
+ * lowest id, J/model/GptAutoregressiveGenerator.java:288-299) may be NULL.  Lengths become +1.
+ * Up to 512 rows the step's launches are replayed as a CUDA graph from the second call with the
+ * same batch size and 128-token length bucket on (the reference replays its decoder layers the same
+ * way, cudaGraphExecLaunch0; JGPT_B200_DECODE_GRAPH=0 launches every kernel eagerly). */
 JGPT_API int32_t jgpt_forward_decode(jgpt_model model, jgpt_kvpool pool, const int32_t *seq_ids_host,
                                      const int32_t *ids_host, const int32_t *cache_len_before_host,
                                      const int32_t *rope_pos_host, int32_t n, float *logits_host,
