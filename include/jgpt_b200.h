@@ -183,8 +183,11 @@ JGPT_API int32_t jgpt_attn_decode_append(jgpt_kvpool pool, int32_t layer0, int32
                                          const int32_t *rope_pos_dev, const int32_t *lens_dev, int32_t n,
                                          int32_t max_len, float *out_dev);
 
-/* Host-buffer form of the fused step (what a JNI caller holding float[] uses): copies q,k,v and
- * the three index arrays to the device, runs jgpt_attn_decode_append, copies out back, synchronises. */
+/* Host-buffer form of the fused step (what a JNI caller holding float[] uses), synchronous.
+ * q, k, v and out in page-locked memory (jgpt_host_alloc_pinned, the reference's CudaPinnedHost):
+ * nothing is staged, the kernel reads the inputs and writes the result through the buffers' device
+ * mappings inside the one launch.  Pageable buffers: copied in and out around the kernel, pipelined
+ * over groups of layers on separate copy streams.  Same results either way. */
 JGPT_API int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n_layers,
                                               const float *q_host, const float *k_host, const float *v_host,
                                               const int32_t *seq_ids_host, const int32_t *rope_pos_host,

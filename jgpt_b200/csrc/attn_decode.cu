@@ -900,6 +900,35 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     cudaStream_t st = p->ctx->stream;
     float *dq = p->d_stage_f, *dk = dq + slab, *dv = dk + slab, *dout = dv + slab;
     int *dseq = p->d_stage_i, *drp = dseq + n, *dlen = drp + n;
+    // Pinned (page-locked, device-mapped) host buffers need no staging at all: the kernel reads q / k / v and
+    // writes the result through their device addresses, so the bytes cross PCIe inside the one launch instead
+    // of in copies before and after it.  Pageable buffers take the staged, pipelined path below.
+    if (env_int("JGPT_B200_HOST_ZEROCOPY", 1)) {
+        const void *hp[4] = {q_host, k_host, v_host, out_host};
+        void *dp[4] = {};
+        bool mapped = true;
+        for (int i = 0; i < 4 && mapped; i++) {
+            cudaPointerAttributes a;
+            if (cudaPointerGetAttributes(&a, hp[i]) != cudaSuccess) {
+                cudaGetLastError();
+                mapped = false;
+            } else if (a.type != cudaMemoryTypeHost || !a.devicePointer) {
+                mapped = false;
+            } else {
+                dp[i] = a.devicePointer;
+            }
+        }
+        if (mapped) {
+            JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+            JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+            JGPT_CUDA_TRY(cudaMemcpyAsync(dlen, lens_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+            rc = launch_attn_decode(p, layer0, n_layers, static_cast<const float *>(dp[0]), static_cast<const float *>(dp[1]),
+                                    static_cast<const float *>(dp[2]), dseq, drp, dlen, n, max_len, static_cast<float *>(dp[3]));
+            if (rc) return rc;
+            JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+            return JGPT_OK;
+        }
+    }
     JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
     JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
     JGPT_CUDA_TRY(cudaMemcpyAsync(dlen, lens_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
@@ -907,9 +936,26 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     // in the kernel, the inputs of group g+1 cross PCIe on the inbound copy engine and the outputs of group g-1
     // leave on the outbound one (three streams ordered by events).  One group = the plain path.
     constexpr int kMaxGroups = 4;  // events are allocated for up to four groups
-    // Three groups measured best for the 12-layer step (301 us against 333 us unpipelined, 337 us with four):
-    // every extra group adds a launch with its own ramp and tail.
-    const int groups = std::min(std::min(kMaxGroups, std::max(1, env_int("JGPT_B200_HOST_GROUPS", 3))), n_layers);
+    // Only the first group's inbound copy and the last group's outbound copy are exposed, every launch costs a
+    // fixed ~20 us: small first and last groups around one large one.  JGPT_B200_HOST_SPLIT = "a-b-c" (layers per
+    // group) overrides the default split, JGPT_B200_HOST_GROUPS = 1 selects the unpipelined path.
+    int sizes[kMaxGroups] = {n_layers, 0, 0, 0};
+    int groups = 1;
+    if (n_layers >= 4 && env_int("JGPT_B200_HOST_GROUPS", 3) > 1) groups = 3, sizes[0] = 1, sizes[1] = n_layers - 2, sizes[2] = 1;
+    if (const char *spec = getenv("JGPT_B200_HOST_SPLIT")) {
+        int tmp[kMaxGroups] = {}, cnt = 0, sum = 0;
+        for (const char *c = spec; *c && cnt < kMaxGroups;) {
+            const int v = atoi(c);
+            if (v <= 0) break;
+            tmp[cnt++] = v, sum += v;
+            while (*c && *c != '-') c++;
+            if (*c == '-') c++;
+        }
+        if (cnt >= 1 && sum == n_layers) {
+            groups = cnt;
+            for (int g = 0; g < kMaxGroups; g++) sizes[g] = tmp[g];
+        }
+    }
     if (groups == 1) {
         JGPT_CUDA_TRY(cudaMemcpyAsync(dq, q_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
         JGPT_CUDA_TRY(cudaMemcpyAsync(dk, k_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
@@ -933,10 +979,9 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     JGPT_CUDA_TRY(cudaEventRecord(p->ev_start, st));
     JGPT_CUDA_TRY(cudaStreamWaitEvent(p->s_in, p->ev_start, 0));
     const size_t per_layer = (size_t)n * p->heads * p->dhead;
-    const int base = n_layers / groups, extra = n_layers % groups;
     int l0 = 0;
     for (int g = 0; g < groups; g++) {
-        const int nl = base + (g < extra ? 1 : 0);
+        const int nl = sizes[g];
         const size_t off = (size_t)l0 * per_layer, cnt = (size_t)nl * per_layer;
         JGPT_CUDA_TRY(cudaMemcpyAsync(dq + off, q_host + off, sizeof(float) * cnt, cudaMemcpyHostToDevice, p->s_in));
         JGPT_CUDA_TRY(cudaMemcpyAsync(dk + off, k_host + off, sizeof(float) * cnt, cudaMemcpyHostToDevice, p->s_in));

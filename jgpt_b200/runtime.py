@@ -41,6 +41,15 @@ class Context:
         buf.copy_from(arr)
         return buf
 
+    def pinned_array(self, shape, dtype=np.float32) -> np.ndarray:
+        """A numpy view of page-locked host memory (``jgpt_host_alloc_pinned``): the host-buffer entry points read and
+        write such buffers in place, without staging copies.  Lives until the process ends."""
+        n = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        B.check(self._lib.jgpt_host_alloc_pinned(max(n, 1), C.byref(p)))
+        buf = (C.c_char * n).from_address(p.value)
+        return np.frombuffer(buf, dtype=dtype).reshape(shape)
+
     def matmul(self, a: "DeviceBuffer", b: "DeviceBuffer", c: "DeviceBuffer", M: int, K: int, N: int):
         """``TensorOpsGPU.matmulGpuDevice(a, b, c, M, K, N)``: C[M,N] = A[M,K] . B[K,N] on device buffers."""
         B.check(self._lib.jgpt_matmul_device(self.handle, a.ptr, b.ptr, c.ptr, M, K, N))

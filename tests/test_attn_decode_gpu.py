@@ -181,6 +181,25 @@ def test_host_buffer_entry_point_equals_device_entry_point(ctx):
         b.pool.attn_decode_append(0, 1, ctx.from_host(q), ctx.from_host(k), ctx.from_host(v), b.seq_ids_dev(),
                                   ctx.from_host(rope), ctx.from_host(lens1), n, int(lens1.max()), out_d)
         assert np.array_equal(out_h, out_d.to_host())
+        # page-locked buffers: the kernel reads and writes them in place (no staging copies); same bits
+        c = PagedCase(ctx, lens0, H=24, Dh=16, layers=1, seed=41, spare_tokens=2)
+        try:
+            qp, kp, vp, op = (ctx.pinned_array((n, D)) for _ in range(4))
+            qp[:], kp[:], vp[:] = q, k, v
+            op[:] = np.nan
+            got = c.pool.attn_decode_append_host(0, 1, qp, kp, vp, c.seqs, rope, lens1, out=op)
+            assert got is op or np.shares_memory(got, op)
+            assert np.array_equal(op, out_h)
+            # the token appended from the page-locked k / v is the one the device path appended: a second query
+            # over the grown caches (no append) sees the same keys and values
+            q2 = ctx.from_host(rng.standard_normal((n, D)).astype(np.float32))
+            o_b, o_c = ctx.alloc((n, D)), ctx.alloc((n, D))
+            for case, o in ((b, o_b), (c, o_c)):
+                case.pool.attn_decode(0, 1, q2, case.seq_ids_dev(), ctx.from_host(rope), ctx.from_host(lens1), n,
+                                      int(lens1.max()), o)
+            assert np.array_equal(o_b.to_host(), o_c.to_host())
+        finally:
+            c.close()
         with pytest.raises(RuntimeError):  # length beyond the reserved blocks -> IllegalState
             a.pool.attn_decode_append_host(0, 1, q, k, v, a.seqs, rope, lens1 + 64)
         with pytest.raises(IndexError):
