@@ -254,6 +254,16 @@ JGPT_API int32_t jgpt_forward_decode(jgpt_model model, jgpt_kvpool pool, const i
                                      const int32_t *ids_host, const int32_t *cache_len_before_host,
                                      const int32_t *rope_pos_host, int32_t n, float *logits_host,
                                      int32_t *next_tokens_host);
+/* forwardDecode followed by sampleNextToken(logits, temperature, topK)
+ * (J/model/GptAutoregressiveGenerator.java:208-286) with the sampler on the device: temperature
+ * divide, stable top-k by (logit desc, index asc), softmax, inverse CDF in index order — the steps
+ * and the summation order of the host routine, so the same draw gives the same token and no
+ * logits cross PCIe.  u01_host [n]: one uniform draw per row (the reference draws from an unseeded
+ * ThreadLocalRandom).  temperature <= 0: greedy. */
+JGPT_API int32_t jgpt_forward_decode_sample(jgpt_model model, jgpt_kvpool pool, const int32_t *seq_ids_host,
+                                            const int32_t *ids_host, const int32_t *cache_len_before_host,
+                                            const int32_t *rope_pos_host, int32_t n, float temperature,
+                                            int32_t top_k, const float *u01_host, int32_t *next_tokens_host);
 /* sampleNextToken on host logits (J/model/GptAutoregressiveGenerator.java:208-286): temperature, stable
  * top-k by (logit desc, index asc), softmax, inverse CDF with the caller's uniform draw u01 (the
  * reference draws from an unseeded ThreadLocalRandom); greedy with lowest-index ties when temperature <= 0. */

@@ -51,10 +51,15 @@ struct Model {
     struct DecodeGraph {
         const void *key[8] = {};
         int n = 0, len_bucket = 0, geom[3] = {};
+        float temperature = 0.f;  // 0: greedy argmax
+        int top_k = 0;
         cudaGraphExec_t exec = nullptr;
         bool failed = false;  // capture refused once (an allocation or a synchronisation inside): stay eager
         uint64_t last_use = 0;
     };
+    // on-device sampling: per-row uniform draws (pinned + device) and the [rows, vocab] work area of sample_kernel
+    float *h_u = nullptr, *d_u = nullptr, *d_samp = nullptr;
+    int samp_rows = 0;
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
@@ -540,6 +545,91 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     }
 }
 
+// sampleNextToken on the device (src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:208-286), one
+// CTA per row, every step of the reference in its own order so that the token is the one the host routine picks:
+// logits / temperature; keep the top_k by (logit descending, index ascending), the rest -inf; maximum;
+// e = (float)exp((double)(z - max)); sum and the running CDF accumulated in fp32 in INDEX order by one thread
+// (a float sum is not associative: a parallel reduction would move CDF boundaries); first index with u <= cdf,
+// else the last one.  The uniform draw u is supplied per row (the reference draws from an unseeded
+// ThreadLocalRandom).
+__global__ void __launch_bounds__(256) sample_kernel(const float *__restrict__ logits, float *__restrict__ work, int V, float temperature,
+                                                     int top_k, const float *__restrict__ u01, int *__restrict__ out) {
+    __shared__ float bv[8];
+    __shared__ int bi[8];
+    __shared__ float s_thr_v, s_mx, s_sum;
+    __shared__ int s_thr_i;
+    const float *row = logits + (size_t)blockIdx.x * V;
+    float *z = work + (size_t)blockIdx.x * V;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < V; i += 256) z[i] = temperature != 1.0f ? row[i] / temperature : row[i];
+    __syncthreads();
+    // block-wide "best" by (value descending, index ascending) among elements strictly after (pv, pi) in that order
+    auto next_best = [&](float pv, int pi, bool first) {
+        float best = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int i = tid; i < V; i += 256) {
+            const float v = z[i];
+            const bool eligible = first || v < pv || (v == pv && i > pi);
+            if (eligible && (v > best || (v == best && i < idx) || idx == 0x7fffffff)) best = v, idx = i;
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+            if (oi != 0x7fffffff && (idx == 0x7fffffff || ov > best || (ov == best && oi < idx))) best = ov, idx = oi;
+        }
+        if (lane == 0) bv[warp] = best, bi[warp] = idx;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < 8; w++)
+                if (bi[w] != 0x7fffffff && (idx == 0x7fffffff || bv[w] > best || (bv[w] == best && bi[w] < idx))) best = bv[w], idx = bi[w];
+            s_thr_v = best, s_thr_i = idx;
+        }
+        __syncthreads();
+    };
+    if (top_k > 0 && top_k < V) {
+        next_best(0.f, 0, true);
+        for (int r = 1; r < top_k; r++) next_best(s_thr_v, s_thr_i, false);
+        const float tv = s_thr_v;
+        const int ti = s_thr_i;  // the top_k-th element: everything after it in the order is dropped
+        for (int i = tid; i < V; i += 256) {
+            const float v = z[i];
+            if (v < tv || (v == tv && i > ti)) z[i] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += 256) mx = fmaxf(mx, z[i]);
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) bv[warp] = mx;
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 8; w++) mx = fmaxf(mx, bv[w]);
+        s_mx = mx;
+    }
+    __syncthreads();
+    mx = s_mx;
+    for (int i = tid; i < V; i += 256) z[i] = (float)exp((double)(z[i] - mx));
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.f;
+        for (int i = 0; i < V; i++) sum += z[i];
+        s_sum = sum;
+        const float u = u01[blockIdx.x];
+        float cum = 0.f;
+        int tok = V - 1;
+        for (int i = 0; i < V; i++) {
+            cum += z[i] / sum;
+            if (u <= cum) {
+                tok = i;
+                break;
+            }
+        }
+        out[blockIdx.x] = tok;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
@@ -683,6 +773,20 @@ static int32_t ensure_logits(Model *m, int rows) {
     m->logits = nullptr, m->logit_rows = 0;
     JGPT_CUDA_TRY(cudaMalloc(&m->logits, sizeof(float) * (size_t)rows * m->vocab));
     m->logit_rows = rows;
+    return JGPT_OK;
+}
+
+struct SampleSpec {
+    float temperature = 0.f;  // <= 0: greedy argmax on the device
+    int top_k = 0;
+};
+static int32_t ensure_sample_work(Model *m, int rows) {
+    if (rows <= m->samp_rows) return JGPT_OK;
+    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    if (m->d_samp) JGPT_CUDA_TRY(cudaFree(m->d_samp));
+    m->d_samp = nullptr, m->samp_rows = 0;
+    JGPT_CUDA_TRY(cudaMalloc(&m->d_samp, sizeof(float) * (size_t)rows * m->vocab));
+    m->samp_rows = rows;
     return JGPT_OK;
 }
 
@@ -835,7 +939,7 @@ static int32_t run_layers(Model *m, int rows, bool attn_writes_image, AttnFn &&a
 }
 
 // Final norm + LM head over the rows listed in d_rowsel[0..n_sel) (or all rows), then argmax.
-static int32_t lm_head(Model *m, int rows, int n_sel) {
+static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = SampleSpec()) {
     const int D = m->d_model;
     cudaStream_t st = m->ctx->stream;
     const int out_rows = n_sel > 0 ? n_sel : rows;
@@ -852,7 +956,13 @@ static int32_t lm_head(Model *m, int rows, int n_sel) {
         rc = gemm(m, m->xn, out_rows, D, m->vocab, 1, W, C, nullptr, rowsel);
     }
     if (rc) return rc;
-    argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
+    if (spec.temperature > 0.f) {  // the draws are in m->d_u (uploaded by the caller)
+        rc = ensure_sample_work(m, out_rows);
+        if (rc) return rc;
+        sample_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
+    } else {
+        argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
+    }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
@@ -958,6 +1068,8 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     JGPT_CUDA_TRY(cudaMalloc(&m->d_next, sizeof(int) * R));
     JGPT_CUDA_TRY(cudaHostAlloc(&m->h_next, sizeof(int) * R, cudaHostAllocDefault));
     JGPT_CUDA_TRY(cudaMalloc(&m->d_rowsel, sizeof(int) * R));
+    JGPT_CUDA_TRY(cudaHostAlloc(&m->h_u, sizeof(float) * R, cudaHostAllocDefault));
+    JGPT_CUDA_TRY(A(&m->d_u, R));
     JGPT_CUDA_TRY(A(&m->ss_a, R * ((D + 31) / 32)));
     JGPT_CUDA_TRY(A(&m->ss_b, R * ((D + 31) / 32)));
     *out = model_registry().add(m);
@@ -977,7 +1089,8 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     cudaFree(m->g), cudaFree(m->logits), cudaFree(m->d_idx), cudaFree(m->d_next), cudaFree(m->d_rowsel);
     cudaFreeHost(m->h_idx), cudaFreeHost(m->h_next);
     drop_weight_images(m);  // and the decode graphs
-    cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b);
+    cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b), cudaFree(m->d_u), cudaFree(m->d_samp);
+    cudaFreeHost(m->h_u);
     delete m;
     return JGPT_OK;
 }
@@ -1147,9 +1260,9 @@ int32_t jgpt_forward_prefill(jgpt_model h, jgpt_kvpool poolh, int32_t seq, const
                                       next_token_host);
 }
 
-int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_ids_host, const int32_t *ids_host,
-                            const int32_t *cache_len_before_host, const int32_t *rope_pos_host, int32_t n, float *logits_host,
-                            int32_t *next_tokens_host) {
+static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_ids_host, const int32_t *ids_host,
+                                   const int32_t *cache_len_before_host, const int32_t *rope_pos_host, int32_t n, float *logits_host,
+                                   int32_t *next_tokens_host, const SampleSpec &spec, const float *u01_host) {
     GET_MODEL(m, h);
     Pool *p = pool_registry().get(poolh);
     int32_t rc = check_pool(m, p);
@@ -1186,14 +1299,22 @@ int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_
     // launch shapes of consecutive steps identical (the exact lengths travel in d_idx).
     const int cap = std::min(m->max_seq, p->max_blocks_per_seq * kBlockTokens);
     const int len_bucket = std::min(cap, (max_len + 127) / 128 * 128);
+    const bool sampled = spec.temperature > 0.f;
+    if (sampled) {
+        JGPT_REQUIRE(u01_host, JGPT_ERR_INVALID_ARGUMENT, "sampling needs one uniform draw per row");
+        for (int i = 0; i < n; i++) m->h_u[i] = u01_host[i];
+        rc = ensure_sample_work(m, n);  // before any capture: it may allocate
+        if (rc) return rc;
+    }
     auto enqueue = [&]() -> int32_t {
         JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+        if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
         embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
         int32_t r2 = run_layers(m, n, false, [&](int l, float *) {
             return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att);
         });
         if (r2) return r2;
-        r2 = lm_head(m, n, 0);
+        r2 = lm_head(m, n, 0, spec);
         if (r2) return r2;
         JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
         return JGPT_OK;
@@ -1201,11 +1322,13 @@ int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_
     Model::DecodeGraph *slot = nullptr;
     if (m->decode_graph_enabled && small_mode(m, n)) {
         Model::DecodeGraph want;
-        const void *key[8] = {p, p->kv, p->d_table, p->d_partials, p->d_tickets, m->logits, m->d_idx, m->h_idx};
+        const void *key[8] = {p, p->kv, p->d_table, p->d_partials, p->d_tickets, m->logits, m->d_idx, m->d_samp};
         for (int i = 0; i < 8; i++) want.key[i] = key[i];
+        want.temperature = sampled ? spec.temperature : 0.f, want.top_k = sampled ? spec.top_k : 0;
         want.n = n, want.len_bucket = len_bucket, want.geom[0] = p->n_blocks, want.geom[1] = p->max_blocks_per_seq, want.geom[2] = p->heads;
         for (auto &g : m->decode_graphs)
-            if (g.n == want.n && g.len_bucket == want.len_bucket && memcmp(g.key, want.key, sizeof(want.key)) == 0 &&
+            if (g.n == want.n && g.len_bucket == want.len_bucket && g.temperature == want.temperature && g.top_k == want.top_k &&
+                memcmp(g.key, want.key, sizeof(want.key)) == 0 &&
                 memcmp(g.geom, want.geom, sizeof(want.geom)) == 0)
                 slot = &g;
         if (!slot) {  // first time: run eagerly (this also sizes every grow-only buffer the step needs)
@@ -1256,6 +1379,25 @@ int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_
         if (rc) return rc;
     }
     return JGPT_OK;
+}
+
+int32_t jgpt_forward_decode(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_ids_host, const int32_t *ids_host,
+                            const int32_t *cache_len_before_host, const int32_t *rope_pos_host, int32_t n, float *logits_host,
+                            int32_t *next_tokens_host) {
+    return forward_decode_impl(h, poolh, seq_ids_host, ids_host, cache_len_before_host, rope_pos_host, n, logits_host,
+                               next_tokens_host, SampleSpec(), nullptr);
+}
+
+// forwardDecode + sampleNextToken(logits, temperature, topK) in one call, the sampler on the device: no logits
+// cross PCIe.  u01_host[n]: the uniform draw of each row.  temperature <= 0: greedy (top_k does not change an argmax).
+int32_t jgpt_forward_decode_sample(jgpt_model h, jgpt_kvpool poolh, const int32_t *seq_ids_host, const int32_t *ids_host,
+                                   const int32_t *cache_len_before_host, const int32_t *rope_pos_host, int32_t n, float temperature,
+                                   int32_t top_k, const float *u01_host, int32_t *next_tokens_host) {
+    JGPT_REQUIRE(next_tokens_host, JGPT_ERR_INVALID_ARGUMENT, "null output");
+    SampleSpec spec;
+    spec.temperature = temperature, spec.top_k = top_k;
+    return forward_decode_impl(h, poolh, seq_ids_host, ids_host, cache_len_before_host, rope_pos_host, n, nullptr, next_tokens_host,
+                               spec, u01_host);
 }
 
 // sampleNextToken on host logits (src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:208-286):

@@ -106,6 +106,22 @@ class GPTModel:
                                               rp.ctypes.data, n, logits.ctypes.data if want_logits else None, nxt.ctypes.data))
         return logits, nxt
 
+    def forwardDecodeSampleBatch(self, pool: KvPool, seqs, tokens, cacheLenBefore, ropePositions, temperature, topK, u01):
+        """One decode step + ``sampleNextToken(logits, temperature, topK)`` per row, sampled on the device with the
+        uniform draws ``u01`` -> next tokens [n].  Same token as the host sampler picks from the same logits and draw."""
+        sq = np.ascontiguousarray(seqs, np.int32)
+        tk = np.ascontiguousarray(tokens, np.int32)
+        lb = np.ascontiguousarray(cacheLenBefore, np.int32)
+        rp = np.ascontiguousarray(ropePositions, np.int32)
+        u = np.ascontiguousarray(u01, np.float32)
+        n = sq.size
+        if u.size != n:
+            raise ValueError("one uniform draw per row")
+        nxt = np.empty(n, np.int32)
+        B.check(self._lib.jgpt_forward_decode_sample(self.handle, pool.handle, sq.ctypes.data, tk.ctypes.data, lb.ctypes.data,
+                                                     rp.ctypes.data, n, float(temperature), int(topK), u.ctypes.data, nxt.ctypes.data))
+        return nxt
+
     # ---- generation ----------------------------------------------------------------------------
     def generateGpuKv(self, inputTokens, maxNewTokens, temperature=0.0, topK=0, pool: KvPool | None = None, rng=None):
         """Returns ids [S + maxNewTokens]: prompt kept, zero tail after an early stop on sampled id 0
@@ -155,9 +171,10 @@ class GPTModel:
                         raise RuntimeError(f"sliding window: startIdx={start} maxSeqLen={self.maxSeqLen}")
                     pool.clear(cache.seq, zero_fill=False)
                     logits = self.forwardPrefill(out[start:start + ln], cache, start, all_rows=False)[0]
-                else:
-                    logits = self.forwardDecode(out[cur - 1:cur], cache, cache.length(), cur - 1)
-                tok = self.sampleNextToken(logits, temperature, top_k, float(rng.random()))
+                    tok = self.sampleNextToken(logits, temperature, top_k, float(rng.random()))
+                else:  # the decode step samples on the device: no logits come back
+                    tok = int(self.forwardDecodeSampleBatch(pool, [cache.seq], out[cur - 1:cur], [cache.length()], [cur - 1],
+                                                            temperature, top_k, [np.float32(rng.random())])[0])
                 out[cur] = tok
             return out
         finally:

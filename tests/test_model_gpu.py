@@ -294,3 +294,38 @@ def test_graph_replayed_decode_steps_equal_eager_ones_and_follow_weight_updates(
         for pool in pools:
             pool.close()
         gm_graph.close(), gm_eager.close(), om.close()
+
+
+def test_device_sampler_picks_the_oracles_token(ctx):
+    """forwardDecode + sampleNextToken with the sampler on the device: for the logits the same step produces
+    (read back through a twin cache) and the same uniform draw, the token is the one the oracle's sampleNextToken
+    picks - over temperatures, top-k sizes (none, 1, a few, more than the vocabulary), draws at both ends, three
+    rows per step, replayed graphs included (every combination runs several steps)."""
+    V, MS, D, H, L, F = 96, 64, 64, 4, 2, 128
+    om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=21, std=0.3)
+    gm = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=64)
+    gm.setParameters(om.tensors())
+    pool_s, pool_l = gm.newPool(3 * MS // 16, 3), gm.newPool(3 * MS // 16, 3)
+    try:
+        prompts = [np.array([(i * 3 + s) % V for i in range(5 + s)], np.int32) for s in range(3)]
+        seq_s = [pool_s.seq_alloc() for _ in range(3)]
+        seq_l = [pool_l.seq_alloc() for _ in range(3)]
+        _, nxt = gm.forwardPrefillBatch(pool_s, seq_s, prompts)
+        gm.forwardPrefillBatch(pool_l, seq_l, prompts)
+        lens = np.array([len(p) for p in prompts], np.int32)
+        rng = np.random.default_rng(5)
+        combos = [(1.0, 0), (0.7, 5), (1.3, 1), (1.0, 3), (0.5, 200), (2.0, 40)]
+        for step in range(36):
+            temp, k = combos[step // 6]
+            u = rng.random(3).astype(np.float32)
+            if step % 6 == 4:
+                u[:] = [0.0, 1.0, np.float32(1.0) - np.float32(2.0 ** -24)]
+            got = gm.forwardDecodeSampleBatch(pool_s, seq_s, nxt, lens, lens, temp, k, u)
+            logits, _ = gm.forwardDecodeBatch(pool_l, seq_l, nxt, lens, lens)
+            want = [O.sample_next_token(logits[i], temp, k, float(u[i])) for i in range(3)]
+            assert list(got) == want, (step, temp, k, u)
+            nxt, lens = got.astype(np.int32), lens + 1
+        with pytest.raises(ValueError):
+            gm.forwardDecodeSampleBatch(pool_s, seq_s, nxt, lens, lens, 1.0, 0, [0.5])
+    finally:
+        pool_s.close(), pool_l.close(), gm.close(), om.close()
