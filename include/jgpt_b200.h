@@ -226,6 +226,10 @@ JGPT_API int32_t jgpt_model_num_tensors(jgpt_model model, int32_t *n_out);
 JGPT_API int32_t jgpt_model_set_tensor(jgpt_model model, int32_t idx, const float *host, uint64_t n_floats);
 /* veles.weights.v1 file (J/model/GptModelWeightsLoader.java:58-81). */
 JGPT_API int32_t jgpt_model_load_weights(jgpt_model model, const char *path);
+/* The reverse: one tensor back to the host, and the whole set written as veles.weights.v1 (the writer
+ * of J/training/LlmTrainerCheckpointIo.java:129-140). */
+JGPT_API int32_t jgpt_model_get_tensor(jgpt_model model, int32_t idx, float *host, uint64_t n_floats);
+JGPT_API int32_t jgpt_model_save_weights(jgpt_model model, const char *path);
 
 /* forwardPrefill(ids [1,S], cache, ropeOffset) -> logits [S, vocab] (host).  Error contract of
  * J/model/GptKvForward.java:47-60.  logits_host [S, vocab], last_logits_host [vocab] and next_token_host

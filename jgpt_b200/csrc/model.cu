@@ -1179,6 +1179,69 @@ int32_t jgpt_model_load_weights(jgpt_model h, const char *path) {
     return JGPT_OK;
 }
 
+// Tensor idx back on the host (GPTModel.getParameters() order), and the whole set as a veles.weights.v1 file: the
+// writer of src/main/java/com/veles/llm/jgpt/training/LlmTrainerCheckpointIo.java:129-140 (writeUTF tag, int32 BE
+// count, per tensor int32 BE rank and dims, big-endian fp32 payload; matrices rank 2, norm gains rank 1).
+int32_t jgpt_model_get_tensor(jgpt_model h, int32_t idx, float *host, uint64_t n_floats) {
+    GET_MODEL(m, h);
+    JGPT_REQUIRE(idx >= 0 && idx < num_tensors(m), JGPT_ERR_OUT_OF_RANGE, "tensor %d outside [0,%d)", idx, num_tensors(m));
+    uint64_t count = 0;
+    const float *src = tensor_ptr(m, idx, &count);
+    JGPT_REQUIRE(host && n_floats == count, JGPT_ERR_INVALID_ARGUMENT, "tensor %d holds %llu floats, got %llu", idx,
+                 (unsigned long long)count, (unsigned long long)n_floats);
+    JGPT_CUDA_TRY(cudaMemcpyAsync(host, src, sizeof(float) * count, cudaMemcpyDeviceToHost, m->ctx->stream));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    return JGPT_OK;
+}
+
+int32_t jgpt_model_save_weights(jgpt_model h, const char *path) {
+    GET_MODEL(m, h);
+    JGPT_REQUIRE(path, JGPT_ERR_INVALID_ARGUMENT, "null path");
+    FILE *f = fopen(path, "wb");
+    if (!f) return fail(JGPT_ERR_IO, "cannot create %s", path);
+    auto wr32 = [&](uint32_t v) {
+        const unsigned char b[4] = {(unsigned char)(v >> 24), (unsigned char)(v >> 16), (unsigned char)(v >> 8), (unsigned char)v};
+        return fwrite(b, 1, 4, f) == 4;
+    };
+    const unsigned char len[2] = {0, 16};
+    bool ok = fwrite(len, 1, 2, f) == 2 && fwrite("veles.weights.v1", 1, 16, f) == 16 && wr32((uint32_t)num_tensors(m));
+    const uint32_t D = (uint32_t)m->d_model, F = (uint32_t)m->d_ff, V = (uint32_t)m->vocab;
+    std::vector<float> buf;
+    for (int i = 0; ok && i < num_tensors(m); i++) {
+        uint64_t count = 0;
+        const float *src = tensor_ptr(m, i, &count);
+        uint32_t d0 = 0, d1 = 0;  // d1 == 0: rank 1
+        const int n = num_tensors(m);
+        if (i == 0) d0 = V, d1 = D;
+        else if (i == 1) d0 = (uint32_t)m->max_seq, d1 = D;
+        else if (i == n - 2) d0 = D;
+        else if (i == n - 1) d0 = D, d1 = V;
+        else switch ((i - 2) % 9) {
+            case 0: case 1: case 2: case 3: d0 = D, d1 = D; break;
+            case 4: case 6: d0 = D, d1 = F; break;
+            case 5: d0 = F, d1 = D; break;
+            default: d0 = D; break;
+        }
+        buf.resize(count);
+        const cudaError_t e = cudaMemcpy(buf.data(), src, sizeof(float) * count, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) {
+            fclose(f);
+            return fail(JGPT_ERR_CUDA, "download of tensor %d: %s", i, cudaGetErrorString(e));
+        }
+        ok = wr32(d1 ? 2u : 1u) && wr32(d0) && (!d1 || wr32(d1));
+        for (uint64_t j = 0; j < count; j++) {
+            uint32_t u;
+            memcpy(&u, &buf[j], 4);
+            u = __builtin_bswap32(u);
+            memcpy(&buf[j], &u, 4);
+        }
+        ok = ok && fwrite(buf.data(), 4, count, f) == count;
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) return fail(JGPT_ERR_IO, "short write to %s", path);
+    return JGPT_OK;
+}
+
 // Batched prefill: n sequences, sequence i = rows [seq_starts[i], seq_starts[i+1]) of ids_host, RoPE /
 // position rows rope_offsets[i] + r, cache slots 0..S_i-1.  last_logits_host [n, vocab] and
 // next_tokens_host [n] (argmax of the last row) may be NULL.  Sets every sequence's length to S_i.

@@ -47,6 +47,10 @@ class GPTModel:
     def loadWeights(self, path):
         B.check(self._lib.jgpt_model_load_weights(self.handle, os.fsencode(path)))
 
+    def saveWeights(self, path):
+        """Writes the parameters as ``veles.weights.v1`` (what ``GptModelWeightsLoader`` reads)."""
+        B.check(self._lib.jgpt_model_save_weights(self.handle, os.fsencode(path)))
+
     def newPool(self, n_blocks, max_seqs, max_blocks_per_seq=None) -> KvPool:
         mbs = max_blocks_per_seq or -(-self.maxSeqLen // 16)
         return KvPool(self.ctx, self.numLayers, self.numHeads, self.dModel // self.numHeads, n_blocks, max_seqs, mbs,

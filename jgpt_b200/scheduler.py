@@ -99,3 +99,95 @@ def gather_step_tokens(local_pairs, world: int, rank: int, max_pairs: int, dist=
         a = recv[r].cpu().numpy()
         out.extend((int(a[1 + 2 * i]), int(a[2 + 2 * i])) for i in range(int(a[0])))
     return out
+
+
+class StepTokenGather:
+    """The same all-gather, issued asynchronously and read ``depth`` steps later: the collective of step t overlaps
+    the decode steps t+1 .. t+depth of every rank, and ranks may drift up to ``depth`` steps apart instead of meeting
+    after every step (one rank's prefill no longer stalls the others' decode steps).  Results come back in step
+    order, each the pairs of all ranks ordered by (rank, local order), exactly what ``gather_step_tokens`` returns.
+
+    Every rank must ``submit`` once per step and stop by the same rule on the gathered results (e.g. "all ranks
+    reported done"), then ``drain``; since results are read in the same order everywhere, all ranks then have issued
+    the same number of collectives."""
+
+    def __init__(self, world: int, rank: int, max_pairs: int, dist=None, device=None, depth: int = 4):
+        self.world, self.rank, self.max_pairs, self.dist, self.device = world, rank, max_pairs, dist, device
+        self.depth = max(0, int(depth))
+        self._inflight = []  # (work or None, slot or None, pairs or None)
+        self._slots, self._free = [], []
+        if world > 1 and dist is not None and device is not None:
+            # a ring of page-locked staging buffers and device tensors: a step's submit is one small copy and one launch
+            import torch
+
+            n = 1 + 2 * max_pairs
+            for _ in range(self.depth + 2):
+                self._slots.append({
+                    "send_host": torch.empty(n, dtype=torch.int32, pin_memory=True),
+                    "send_dev": torch.empty(n, dtype=torch.int32, device=device),
+                    "recv_dev": torch.empty(world * n, dtype=torch.int32, device=device),
+                    "recv_host": torch.empty(world * n, dtype=torch.int32, pin_memory=True),
+                })
+            self._free = list(range(len(self._slots)))
+
+    def submit(self, local_pairs):
+        local_pairs = np.asarray(local_pairs, np.int32).reshape(-1, 2)
+        if local_pairs.shape[0] > self.max_pairs:
+            raise ValueError(f"{local_pairs.shape[0]} pairs exceed the gather buffer of {self.max_pairs}")
+        if self.world == 1 or self.dist is None:
+            self._inflight.append((None, None, [tuple(int(x) for x in p) for p in local_pairs]))
+            return
+        import torch
+
+        if self._slots:
+            slot_id = self._free.pop(0)
+            slot = self._slots[slot_id]
+            buf = slot["send_host"].numpy()
+            buf[:] = -1
+            buf[0] = local_pairs.shape[0]
+            buf[1:1 + local_pairs.size] = local_pairs.reshape(-1)
+            slot["send_dev"].copy_(slot["send_host"], non_blocking=True)
+            work = self.dist.all_gather_into_tensor(slot["recv_dev"], slot["send_dev"], async_op=True)
+            self._inflight.append((work, slot_id, None))
+            return
+        buf = np.full(1 + 2 * self.max_pairs, -1, np.int32)
+        buf[0] = local_pairs.shape[0]
+        buf[1:1 + local_pairs.size] = local_pairs.reshape(-1)
+        send = torch.from_numpy(buf)
+        recv = [torch.empty_like(send) for _ in range(self.world)]
+        work = self.dist.all_gather(recv, send, async_op=True)
+        self._inflight.append((work, None, recv))
+
+    def ready(self) -> bool:
+        """True when a result must be read now to keep at most ``depth`` collectives in flight."""
+        return len(self._inflight) > self.depth
+
+    def pop(self):
+        """Waits for the oldest step's collective and returns its pairs."""
+        work, slot_id, payload = self._inflight.pop(0)
+        if work is None:
+            return payload
+        work.wait()
+        n = 1 + 2 * self.max_pairs
+        if slot_id is not None:
+            import torch
+
+            slot = self._slots[slot_id]
+            slot["recv_host"].copy_(slot["recv_dev"], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            flat = slot["recv_host"].numpy()
+            rows = [flat[r * n:(r + 1) * n] for r in range(self.world)]
+            self._free.append(slot_id)
+        else:
+            rows = [t.cpu().numpy() for t in payload]
+        out = []
+        for a in rows:
+            out.extend((int(a[1 + 2 * i]), int(a[2 + 2 * i])) for i in range(int(a[0])))
+        return out
+
+    def drain(self):
+        """Results of every step still in flight, oldest first."""
+        out = []
+        while self._inflight:
+            out.append(self.pop())
+        return out

@@ -11,7 +11,7 @@ import numpy as np
 from .kv_cache import KvPool
 from .model import GPTModel
 from .runtime import Event
-from .scheduler import ContinuousBatcher, gather_step_tokens, shard_requests
+from .scheduler import ContinuousBatcher, StepTokenGather, gather_step_tokens, shard_requests
 
 VOCAB, CTX, D_MODEL, HEADS, LAYERS, D_FF, EPS = 8000, 1024, 384, 24, 12, 768, 1e-5
 DHEAD = D_MODEL // HEADS
@@ -139,7 +139,7 @@ def run_prefill(ctx, batch=32, seq_len=1024, repeats=3):
         pool.close(), model.close()
 
 
-def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool_fraction=0.6, max_steps=100_000):
+def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool_fraction=0.6, max_steps=100_000, gather_depth=4):
     """256 requests (seed 2): prompt U[32,512], target U[64,1024] new tokens clipped to the 1024 context; pool sized
     at 60 % of the rank's total block demand; requests dealt round-robin to the ranks; sampled ids all-gathered."""
     rng = np.random.default_rng(2)
@@ -157,26 +157,44 @@ def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool
         for i in mine:
             sched.submit(prompts[i], int(t_len[i]))
         ctx.synchronize()
-        total_tokens, steps, done = 0, 0, False
+        total_tokens, steps, done, all_done = 0, 0, False, False
+        gather = StepTokenGather(world, rank, max_pairs=-(-n_requests // world) + 2, dist=dist, device=device, depth=gather_depth)
+
+        def account(allp):
+            nonlocal total_tokens, all_done
+            total_tokens += sum(1 for r, _ in allp if r >= 0)
+            all_done = all_done or sum(1 for r, _ in allp if r < 0) == world
+
         t0 = time.perf_counter()
-        while steps < max_steps:
+        t_step = t_submit = t_pop = 0.0
+        while steps < max_steps and not all_done:
+            ta = time.perf_counter()
             if not done:
                 pairs, nr, nw = sched.step()
                 done = nr == 0 and nw == 0
             else:
                 pairs = np.zeros((0, 2), np.int32)
-            local = [(mine[int(r)], int(t)) for r, t in pairs]
-            allp = gather_step_tokens(local + ([(-1, 1)] if done else []), world, rank, max_pairs=-(-n_requests // world) + 2, dist=dist, device=device)
-            total_tokens += sum(1 for r, _ in allp if r >= 0)
+            tb = time.perf_counter()
+            # the ids of step t are all-gathered while steps t+1 .. t+depth run; a finished rank keeps reporting (-1, 1)
+            gather.submit([(mine[int(r)], int(t)) for r, t in pairs] + ([(-1, 1)] if done else []))
+            tc = time.perf_counter()
             steps += 1
-            if sum(1 for r, _ in allp if r < 0) == world:
-                break
+            while gather.ready() and not all_done:
+                account(gather.pop())
+            td = time.perf_counter()
+            t_step += tb - ta
+            t_submit += tc - tb
+            t_pop += td - tc
+        for allp in gather.drain():
+            account(allp)
         el = time.perf_counter() - t0
         ev = sched.events()
         return {
             "workload": f"continuous batching: {n_requests} requests (seed 2), prompt U[32,512], target U[64,1024] clipped to the "
-                        f"1024 context, KV pool {pool_fraction:.0%} of demand, round-robin over {world} GPU(s), token ids all-gathered",
+                        f"1024 context, KV pool {pool_fraction:.0%} of demand, round-robin over {world} GPU(s), token ids all-gathered "
+                        f"(asynchronously, read {gather_depth} steps later)",
             "generated_tokens": total_tokens, "steps": steps, "seconds": el, "tokens_per_s": total_tokens / el,
+            "seconds_in": {"scheduler_steps": t_step, "gather_submit": t_submit, "gather_read": t_pop},
             "pool_blocks_rank0": n_blocks, "demand_blocks_rank0": demand, "evictions_rank0": sum(1 for e in ev if e[0] == 2),
             "timing": "host wall clock over the whole run (prefills included)",
         }

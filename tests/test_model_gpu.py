@@ -203,6 +203,12 @@ def test_weights_file_loader(ctx, tiny, tmp_path):
         from jgpt_b200 import JgptError
         with pytest.raises(JgptError):
             gm2.loadWeights(os.path.join(tmp_path, "missing.bin"))
+        # the writer: the file the library writes is, byte for byte, the file the oracle's writer produced
+        path2 = os.path.join(tmp_path, "model_out.bin")
+        gm2.saveWeights(path2)
+        assert open(path2, "rb").read() == open(path, "rb").read()
+        with pytest.raises(JgptError):
+            gm2.saveWeights(os.path.join(tmp_path, "no_such_dir", "x.bin"))
     finally:
         gm2.close()
 

@@ -53,6 +53,60 @@ def test_token_id_gather_two_ranks_gloo(tmp_path):
         assert o.strip().endswith("OK"), (o, e[-2000:])
 
 
+_WORKER_LAGGED = r"""
+import os, sys, time
+sys.path.insert(0, {root!r})
+import numpy as np, torch.distributed as dist
+from jgpt_b200.scheduler import StepTokenGather, shard_requests
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank=int(sys.argv[1]), world_size=2)
+rank, world, n_req = dist.get_rank(), 2, 11
+mine = shard_requests(n_req, world, rank)
+my_steps = 9 if rank == 0 else 5            # rank 1 finishes earlier and keeps reporting "done"
+g = StepTokenGather(world, rank, max_pairs=8, dist=dist, depth=3)
+seen, all_done, step = [], False, 0
+def account(pairs):
+    global all_done
+    seen.append([p for p in pairs if p[0] >= 0])
+    all_done = all_done or sum(1 for p in pairs if p[0] < 0) == world
+while not all_done:
+    done = step >= my_steps
+    local = [] if done else [(r, (r * 31 + step * 7) % 100) for r in mine if (r + step) % 3 != 0]
+    if rank == 1 and step % 2 == 0:
+        time.sleep(0.02)                    # uneven step times: the ranks drift within the window
+    g.submit(local + ([(-1, 1)] if done else []))
+    step += 1
+    while g.ready() and not all_done:
+        account(g.pop())
+for pairs in g.drain():
+    account(pairs)
+want = []
+for t in range(len(seen)):
+    want.append([(r, (r * 31 + t * 7) % 100) for rk in range(world) for r in shard_requests(n_req, world, rk)
+                 if t < (9 if rk == 0 else 5) and (r + t) % 3 != 0])
+ok = seen == want and len(seen) >= 10 and step == len(seen)
+dist.barrier()
+dist.destroy_process_group()
+print("OK" if ok else "MISMATCH %r %r" % (seen, want), flush=True)
+"""
+
+
+def test_lagged_token_id_gather_two_ranks_gloo(tmp_path):
+    """The asynchronous form: results arrive in step order, identical on both ranks, while the ranks run up to
+    `depth` steps apart; both stop on the same gathered step and have issued the same number of collectives."""
+    from jgpt_b200.scheduler import StepTokenGather
+    g = StepTokenGather(1, 0, 4)  # single rank: nothing is communicated, results still come `depth` steps later
+    g.submit([(3, 7)]), g.submit([(5, 0)])
+    assert not g.ready() and g.drain() == [[(3, 7)], [(5, 0)]]
+    port = 29900 + (os.getpid() % 90)
+    script = os.path.join(tmp_path, "worker_lagged.py")
+    open(script, "w").write(_WORKER_LAGGED.format(root=ROOT, port=port))
+    procs = [subprocess.Popen([sys.executable, script, str(r)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=180) for p in procs]
+    for p, (o, e) in zip(procs, outs):
+        assert p.returncode == 0, e[-2000:]
+        assert o.strip().endswith("OK"), (o, e[-2000:])
+
+
 def test_continuous_batching_policy_specification():
     """FIFO admission with up-front reservation, LRU eviction of finished sequences, no overtaking."""
     streams = [[5, 6, 7], [8, 0, 9], [1, 2, 3, 4], [9, 9]]
