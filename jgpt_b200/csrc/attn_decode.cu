@@ -16,6 +16,7 @@
 #include "ptx.cuh"
 
 #include <algorithm>
+#include <chrono>
 
 namespace jgpt {
 
@@ -900,13 +901,19 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     cudaStream_t st = p->ctx->stream;
     float *dq = p->d_stage_f, *dk = dq + slab, *dv = dk + slab, *dout = dv + slab;
     int *dseq = p->d_stage_i, *drp = dseq + n, *dlen = drp + n;
-    // Pinned (page-locked, device-mapped) host buffers need no staging at all: the kernel reads q / k / v and
-    // writes the result through their device addresses, so the bytes cross PCIe inside the one launch instead
-    // of in copies before and after it.  Pageable buffers take the staged, pipelined path below.
-    if (env_int("JGPT_B200_HOST_ZEROCOPY", 1)) {
+    // Three ways to move the bytes.  STAGED: copies in and out around the kernel, pipelined over groups of layers
+    // (works for any host memory).  ZEROCOPY (page-locked, device-mapped buffers): nothing is staged, the kernel
+    // reads q / k / v and writes the result through the buffers' device addresses inside the one launch; fastest
+    // when this process has the host fabric to itself (0.25 ms per 12-layer step against 0.30), slower when eight
+    // processes do it at once (0.46 against 0.33: many small PCIe reads).  HYBRID: inputs by one copy each, the
+    // result written in place.  Which one wins is a property of the machine at that moment, so the first calls
+    // on a pool take turns (three samples each, same results whatever the way) and the fastest is kept;
+    // JGPT_B200_HOST_ZEROCOPY = 0 / 1 / 2 pins STAGED / ZEROCOPY / HYBRID.
+    enum { STAGED = 0, ZEROCOPY = 1, HYBRID = 2 };
+    void *dp[4] = {};
+    bool mapped = true;
+    {
         const void *hp[4] = {q_host, k_host, v_host, out_host};
-        void *dp[4] = {};
-        bool mapped = true;
         for (int i = 0; i < 4 && mapped; i++) {
             cudaPointerAttributes a;
             if (cudaPointerGetAttributes(&a, hp[i]) != cudaSuccess) {
@@ -918,16 +925,55 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
                 dp[i] = a.devicePointer;
             }
         }
-        if (mapped) {
-            JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
-            JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
-            JGPT_CUDA_TRY(cudaMemcpyAsync(dlen, lens_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
-            rc = launch_attn_decode(p, layer0, n_layers, static_cast<const float *>(dp[0]), static_cast<const float *>(dp[1]),
-                                    static_cast<const float *>(dp[2]), dseq, drp, dlen, n, max_len, static_cast<float *>(dp[3]));
-            if (rc) return rc;
-            JGPT_CUDA_TRY(cudaStreamSynchronize(st));
-            return JGPT_OK;
+    }
+    int mode = STAGED;
+    bool tuning = false;
+    if (mapped) {
+        const int pinned_mode = env_int("JGPT_B200_HOST_ZEROCOPY", -1);
+        if (pinned_mode >= 0 && pinned_mode <= 2) {
+            mode = pinned_mode;
+        } else {
+            if (p->host_tune_n != n || p->host_tune_layers != n_layers) {  // another shape: measure again
+                p->host_tune_n = n, p->host_tune_layers = n_layers, p->host_tune_calls = 0, p->host_mode = -1;
+                for (double &b : p->host_tune_best) b = 1e30;
+            }
+            if (p->host_mode >= 0) {
+                mode = p->host_mode;
+            } else {
+                static const int order[3] = {ZEROCOPY, HYBRID, STAGED};
+                mode = order[p->host_tune_calls % 3];
+                tuning = true;
+            }
         }
+    }
+    const auto t_begin = std::chrono::steady_clock::now();
+    auto finish = [&]() {
+        if (!tuning) return;
+        const double us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_begin).count();
+        p->host_tune_best[mode] = std::min(p->host_tune_best[mode], us);
+        if (++p->host_tune_calls >= 9) {
+            int best = STAGED;
+            for (int mth = 0; mth < 3; mth++)
+                if (p->host_tune_best[mth] < p->host_tune_best[best]) best = mth;
+            p->host_mode = best;
+        }
+    };
+    if (mode == ZEROCOPY || mode == HYBRID) {
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(dlen, lens_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
+        const float *qi = static_cast<const float *>(dp[0]), *ki = static_cast<const float *>(dp[1]), *vi = static_cast<const float *>(dp[2]);
+        if (mode == HYBRID) {
+            JGPT_CUDA_TRY(cudaMemcpyAsync(dq, q_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+            JGPT_CUDA_TRY(cudaMemcpyAsync(dk, k_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+            JGPT_CUDA_TRY(cudaMemcpyAsync(dv, v_host, sizeof(float) * slab, cudaMemcpyHostToDevice, st));
+            qi = dq, ki = dk, vi = dv;
+        }
+        rc = launch_attn_decode(p, layer0, n_layers, qi, ki, vi, dseq, drp, dlen, n, max_len, static_cast<float *>(dp[3]));
+        if (rc) return rc;
+        JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+        finish();
+        return JGPT_OK;
     }
     JGPT_CUDA_TRY(cudaMemcpyAsync(dseq, seq_ids_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
     JGPT_CUDA_TRY(cudaMemcpyAsync(drp, rope_pos_host, sizeof(int) * (size_t)n, cudaMemcpyHostToDevice, st));
@@ -969,6 +1015,7 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
         if (rc) return rc;
         JGPT_CUDA_TRY(cudaMemcpyAsync(out_host, dout, sizeof(float) * slab, cudaMemcpyDeviceToHost, st));
         JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+        finish();
         return JGPT_OK;
     }
     if (!p->s_in) {
@@ -1002,6 +1049,7 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     }
     JGPT_CUDA_TRY(cudaStreamSynchronize(p->s_out));
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+    finish();
     return JGPT_OK;
 }
 

@@ -84,6 +84,9 @@ struct Pool {
     // copy streams + events of the pipelined host-buffer entry point (created on first use)
     cudaStream_t s_in = nullptr, s_out = nullptr;
     cudaEvent_t ev_in[4] = {}, ev_done[4] = {}, ev_start = nullptr;
+    // which way the host-buffer entry point moves its bytes (measured over the pool's first calls)
+    int host_mode = -1, host_tune_calls = 0, host_tune_n = -1, host_tune_layers = -1;
+    double host_tune_best[3] = {1e30, 1e30, 1e30};
     void *d_prefill_desc = nullptr;  // per-sequence descriptors of a prefill call
     int prefill_desc_cap = 0;
     // staging for the host-buffer entry points (grow-only)

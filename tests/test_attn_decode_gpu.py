@@ -187,9 +187,14 @@ def test_host_buffer_entry_point_equals_device_entry_point(ctx):
             qp, kp, vp, op = (ctx.pinned_array((n, D)) for _ in range(4))
             qp[:], kp[:], vp[:] = q, k, v
             op[:] = np.nan
-            got = c.pool.attn_decode_append_host(0, 1, qp, kp, vp, c.seqs, rope, lens1, out=op)
-            assert got is op or np.shares_memory(got, op)
-            assert np.array_equal(op, out_h)
+            # the first calls on a pool take turns between the transfer paths (kernel reading / writing the host
+            # buffers itself; inputs copied + result written in place; staged copies): same bits from each.  The
+            # same token is appended to the same slot every time, so the calls are idempotent.
+            for _ in range(4):
+                op[:] = np.nan
+                got = c.pool.attn_decode_append_host(0, 1, qp, kp, vp, c.seqs, rope, lens1, out=op)
+                assert got is op or np.shares_memory(got, op)
+                assert np.array_equal(op, out_h)
             # the token appended from the page-locked k / v is the one the device path appended: a second query
             # over the grown caches (no append) sees the same keys and values
             q2 = ctx.from_host(rng.standard_normal((n, D)).astype(np.float32))
