@@ -44,7 +44,16 @@ def small16(ctx):
     gm.close(), om.close()
 
 
-@pytest.mark.parametrize("which", ["tiny", "small16"])
+@pytest.fixture(scope="module")
+def odd_shapes(ctx):
+    """Shapes none of the fused paths take: d_ff 72 (not a multiple of 16: separate RMSNorm / SwiGLU launches, W2
+    with K % 16 != 0) and vocab 66 (N % 4 != 0: the LM head on the scalar kernel)."""
+    om, gm = _pair(ctx, 66, 40, 32, 4, 2, 72, 1e-6, seed=6, std=0.2)
+    yield om, gm
+    gm.close(), om.close()
+
+
+@pytest.mark.parametrize("which", ["tiny", "small16", "odd_shapes"])
 def test_prefill_and_decode_logits_match_oracle(request, ctx, which):
     om, gm = request.getfixturevalue(which)
     V, MS = om.vocab, om.max_seq
