@@ -1,11 +1,13 @@
 // Model weights on the device and the forward step around the attention kernels: embedding + learned
-// positions, RMSNorm, fp32 projections, SwiGLU, LM head, greedy argmax, and the generation loop.
+// positions, RMSNorm, fp32 projections, SwiGLU, LM head, greedy argmax / sampling, and the generation loop.
 //
 // Projections keep fp32 operands.  Default: tensor cores with split-TF32 operands (fp32-level accuracy; the
 // reference runs the same GEMMs through cuBLAS under plain TF32 math,
-// src/main/cpp/jgpt_cuda_jni_init_matmul.inl:67, 794, 892).  JGPT_B200_STRICT_GEMM=1 selects a scalar kernel
-// that accumulates every output element over k in ascending order in one thread (mul, then add), which is
-// bit-reproducible against a scalar CPU loop.
+// src/main/cpp/jgpt_cuda_jni_init_matmul.inl:67, 794, 892) - gemm_tc_small_kernel up to 512 rows (every decode
+// step; RMSNorm, SwiGLU and the residual fused, the step replayed as a CUDA graph), the tcgen05 kernel of
+// gemm_umma.cu above that (prefill).  JGPT_B200_STRICT_GEMM=1 selects a scalar kernel that accumulates every
+// output element over k in ascending order in one thread (mul, then add), which is bit-reproducible against a
+// scalar CPU loop.
 #include "common.cuh"
 #include "gemm_umma.cuh"
 
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_kernel(const float
 // (mma.sync m16n8k8).  The dropped Al.Bl term and the truncation of the low parts are ~2^-21 relative,
 // i.e. the result differs from a k-ordered fp32 loop by rounding noise only, where plain TF32 (what the
 // reference runs its cuBLAS GEMMs with) is ~2^-11.  A tile: BM x 32 (row major, stride 36 floats),
-// W tile: 32 x BN (stride BN + 8): both fragment loads are bank-conflict free.  cp.async double buffering.
+// W tile: 32 x BN (stride BN + 8): both fragment loads are bank-conflict free.  Multi-stage cp.async ring.
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
