@@ -18,10 +18,6 @@
 
 namespace jgpt {
 
-struct PrefillSeq {
-    int seq_id, row0, S, rope_off;
-};
-
 struct PrefillParams {
     __half *kv;
     const int *table;
@@ -365,9 +361,8 @@ __global__ void __launch_bounds__(128) attn_prefill_simt_kernel(const PrefillPar
 // ------------------------------------------------------------------------------------------------
 // Launcher
 // ------------------------------------------------------------------------------------------------
-int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v, const int *seq_ids_host,
-                            const int *seq_starts_host, const int *rope_offsets_host, int n_seqs, float *out, float *out_image) {
-    JGPT_REQUIRE(!out_image || p->dhead == 16, JGPT_ERR_INVALID_ARGUMENT, "image output needs d_head 16");
+int32_t prefill_upload_descriptors(Pool *p, const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
+                                   int n_seqs, int *max_S_out, int *n_rows_out) {
     std::vector<PrefillSeq> desc((size_t)n_seqs);
     int max_S = 0;
     for (int i = 0; i < n_seqs; i++) {
@@ -383,7 +378,6 @@ int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, 
         desc[(size_t)i] = PrefillSeq{s, seq_starts_host[i], S, ro};
         max_S = std::max(max_S, S);
     }
-    const int n_rows = seq_starts_host[n_seqs];
     if (n_seqs > p->prefill_desc_cap) {
         JGPT_CUDA_TRY(cudaStreamSynchronize(p->ctx->stream));
         if (p->d_prefill_desc) JGPT_CUDA_TRY(cudaFree(p->d_prefill_desc));
@@ -393,6 +387,17 @@ int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, 
     }
     JGPT_CUDA_TRY(cudaMemcpyAsync(p->d_prefill_desc, desc.data(), sizeof(PrefillSeq) * desc.size(), cudaMemcpyHostToDevice,
                                   p->ctx->stream));  // pageable source: staged before the call returns
+    *max_S_out = max_S, *n_rows_out = seq_starts_host[n_seqs];
+    return JGPT_OK;
+}
+
+int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v, const int *seq_ids_host,
+                            const int *seq_starts_host, const int *rope_offsets_host, int n_seqs, float *out, float *out_image,
+                            bool skip_append) {
+    JGPT_REQUIRE(!out_image || p->dhead == 16, JGPT_ERR_INVALID_ARGUMENT, "image output needs d_head 16");
+    int max_S = 0, n_rows = 0;
+    int32_t rc0 = prefill_upload_descriptors(p, seq_ids_host, seq_starts_host, rope_offsets_host, n_seqs, &max_S, &n_rows);
+    if (rc0) return rc0;
     PrefillParams P;
     memset(&P, 0, sizeof(P));
     P.kv = p->kv, P.table = p->d_table, P.rope = p->d_rope, P.q = q, P.k = k, P.v = v, P.out = out, P.out_image = out_image;
@@ -405,14 +410,16 @@ int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, 
     const long long total = (long long)n_rows * p->heads * cpr;
     const unsigned agrid = (unsigned)((total + 255) / 256);
     cudaStream_t st = p->ctx->stream;
-    switch (DH) {
-        case 4: kv_append_rows_kernel<4><<<agrid, 256, 0, st>>>(P); break;
-        case 8: kv_append_rows_kernel<8><<<agrid, 256, 0, st>>>(P); break;
-        case 16: kv_append_rows_kernel<16><<<agrid, 256, 0, st>>>(P); break;
-        case 32: kv_append_rows_kernel<32><<<agrid, 256, 0, st>>>(P); break;
-        default: return fail(JGPT_ERR_UNSUPPORTED, "dhead %d not supported", DH);
+    if (!skip_append) {  // skipped when the K / V projection's epilogue has already written the paged store
+        switch (DH) {
+            case 4: kv_append_rows_kernel<4><<<agrid, 256, 0, st>>>(P); break;
+            case 8: kv_append_rows_kernel<8><<<agrid, 256, 0, st>>>(P); break;
+            case 16: kv_append_rows_kernel<16><<<agrid, 256, 0, st>>>(P); break;
+            case 32: kv_append_rows_kernel<32><<<agrid, 256, 0, st>>>(P); break;
+            default: return fail(JGPT_ERR_UNSUPPORTED, "dhead %d not supported", DH);
+        }
+        JGPT_CUDA_TRY(cudaGetLastError());
     }
-    JGPT_CUDA_TRY(cudaGetLastError());
     if (DH == 16) {
         dim3 grid((unsigned)((max_S + kQTile - 1) / kQTile), (unsigned)p->heads, (unsigned)n_seqs);
         const size_t smem = sizeof(int) * (size_t)((max_S + kBlockTokens - 1) / kBlockTokens);

@@ -146,6 +146,24 @@ int32_t pool_ensure_split_scratch(Pool *p, uint64_t partial_floats, uint64_t tic
 // Push rows of the host block table to the device mirror.
 int32_t pool_upload_table_row(Pool *p, int seq);
 
+// One prompt of a prefill call: rows [row0, row0 + S) of the packed activations belong to sequence seq_id, row r
+// sits at cache slot r - row0 and RoPE position rope_off + (r - row0).
+struct PrefillSeq {
+    int seq_id, row0, S, rope_off;
+};
+// What a projection epilogue needs to write K / V rows straight into the paged fp16 store (d_head 16).
+struct PagedAppendArgs {
+    __half *kv;
+    const int *table;
+    const float2 *rope;
+    const PrefillSeq *seqs;
+    int *status;
+    int n_seqs, H, layer, n_blocks, mbs, max_positions;
+};
+// Validates the prompts of a prefill call against the pool and uploads their descriptors (p->d_prefill_desc).
+int32_t prefill_upload_descriptors(Pool *p, const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
+                                   int n_seqs, int *max_S_out, int *n_rows_out);
+
 // Kernel launchers (defined in the .cu files)
 int32_t launch_kv_append(Pool *p, int layer, const float *k, const float *v, const int *seq_ids,
                          const int *slot_pos, const int *rope_pos, int n);
@@ -156,6 +174,6 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
                            int max_len, float *out);
 int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v,
                             const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
-                            int n_seqs, float *out, float *out_image = nullptr);
+                            int n_seqs, float *out, float *out_image = nullptr, bool skip_append = false);
 
 }  // namespace jgpt

@@ -262,11 +262,12 @@ struct TileWalk {
 
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__restrict__ Aimg, const Batch B, const TileWalk walk,
-                                                               int M, int K, int N, int *__restrict__ status) {
+                                                               int M, int K, int N, int *__restrict__ status, const PagedAppendArgs pa) {
     constexpr int W_TILE_FLOATS = BN * BK * 2;
     constexpr uint32_t W_TILE_BYTES = W_TILE_FLOATS * 4, STAGE_BYTES = A_TILE_BYTES + W_TILE_BYTES;
     constexpr uint32_t IDESC = instr_desc<BN>();
     static_assert(BN % 64 == 0 && BN <= 256 && (MODE != 1 || BN == 256), "bad tile width");
+    static_assert(MODE >= 0 && MODE <= 3, "MODE 3: products 1 and 2 of the batch are K and V rows for the paged store");
     extern __shared__ uint8_t umma_smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t s_tmem_base;
@@ -377,7 +378,76 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_umma_kernel(const float *__re
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-            if (MODE != 1) {
+            if (MODE == 3 && z != 0) {
+                // K (z == 1) or V (z == 2) rows of a prefill: row m is slot m - row0 of its sequence.  Same arithmetic
+                // and store shape as kv_append_rows_kernel (RoPE from the table with separately rounded products, fp16
+                // round-to-nearest-even, 16-byte stores; the last prompt row zero-fills the rest of its block).
+                bool row_ok = m < M;
+                int slot = 0, tail = 0;
+                size_t blk = 0;
+                float2 cs[8];
+                if (row_ok) {
+                    int lo = 0, hi = pa.n_seqs - 1;
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (pa.seqs[mid].row0 <= m) lo = mid; else hi = mid - 1;
+                    }
+                    const PrefillSeq sd = pa.seqs[lo];
+                    slot = m - sd.row0;
+                    const int rp = sd.rope_off + slot;
+                    if (slot < 0 || slot >= sd.S || rp < 0 || rp >= pa.max_positions) {
+                        atomicOr(pa.status, DEV_STATUS_BAD_POSITION);
+                        row_ok = false;
+                    } else {
+                        const int phys = pa.table[(size_t)sd.seq_id * pa.mbs + slot / kBlockTokens];
+                        if (phys < 0 || phys >= pa.n_blocks) {
+                            atomicOr(pa.status, DEV_STATUS_BAD_BLOCK);
+                            row_ok = false;
+                        } else {
+                            blk = ((size_t)pa.layer * pa.n_blocks + phys) * pa.H;
+                            tail = slot == sd.S - 1 ? kBlockTokens - 1 - slot % kBlockTokens : 0;
+                            if (z == 1) {
+#pragma unroll
+                                for (int q = 0; q < 8; q++) cs[q] = pa.rope[(size_t)rp * 8 + q];
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int sl = 0; sl < SLABS; sl++) {
+                    const int c0 = half * (BN / 2) + sl * 32;
+                    if (n0 + c0 >= N) break;  // uniform across the warp
+                    float v[32];
+                    load_acc32(acc, quarter, c0, v);
+                    if (row_ok) {
+#pragma unroll
+                        for (int hh = 0; hh < 2; hh++) {
+                            const int head = (n0 + c0) / 16 + hh;
+                            if (head < pa.H) {
+                                __align__(16) __half hv[16];
+#pragma unroll
+                                for (int q = 0; q < 8; q++) {
+                                    const float x1 = v[hh * 16 + 2 * q], x2 = v[hh * 16 + 2 * q + 1];
+                                    if (z == 1) {
+                                        hv[2 * q] = __float2half_rn(__fsub_rn(__fmul_rn(x1, cs[q].x), __fmul_rn(x2, cs[q].y)));
+                                        hv[2 * q + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x1, cs[q].y), __fmul_rn(x2, cs[q].x)));
+                                    } else {
+                                        hv[2 * q] = __float2half_rn(x1), hv[2 * q + 1] = __float2half_rn(x2);
+                                    }
+                                }
+                                __half *dst = pa.kv + (blk + head) * (size_t)(2 * kBlockTokens * 16) + (size_t)(slot % kBlockTokens) * 16 +
+                                              (z == 2 ? kBlockTokens * 16 : 0);
+                                *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(hv);
+                                *reinterpret_cast<uint4 *>(dst + 8) = *reinterpret_cast<const uint4 *>(hv + 8);
+                                for (int t2 = 1; t2 <= tail; t2++) {
+                                    *reinterpret_cast<uint4 *>(dst + t2 * 16) = make_uint4(0, 0, 0, 0);
+                                    *reinterpret_cast<uint4 *>(dst + t2 * 16 + 8) = make_uint4(0, 0, 0, 0);
+                                }
+                            }
+                        }
+                    }
+                }
+            } else if (MODE != 1) {
                 float *C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);  // selects, not an indexed copy of B
 #pragma unroll
                 for (int sl = 0; sl < SLABS; sl++) {
@@ -455,11 +525,12 @@ static int sm_count_of_current_device() {
 }
 
 template <int BN, int STAGES, int MODE>
-static int32_t launch_t(const TileWalk &walk, const float *Aimg, const Batch &b, int M, int K, int N, int *d_status, cudaStream_t st) {
+static int32_t launch_t(const TileWalk &walk, const float *Aimg, const Batch &b, int M, int K, int N, int *d_status, cudaStream_t st,
+                        const PagedAppendArgs &pa = PagedAppendArgs()) {
     constexpr uint32_t smem = smem_bytes<BN, STAGES>();
     JGPT_CUDA_TRY(cudaFuncSetAttribute(gemm_umma_kernel<BN, STAGES, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = walk.total < sm_count_of_current_device() ? walk.total : sm_count_of_current_device();
-    gemm_umma_kernel<BN, STAGES, MODE><<<grid, THREADS, smem, st>>>(Aimg, b, walk, M, K, N, d_status);
+    gemm_umma_kernel<BN, STAGES, MODE><<<grid, THREADS, smem, st>>>(Aimg, b, walk, M, K, N, d_status, pa);
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
@@ -474,6 +545,17 @@ int32_t launch(const float *Aimg, const Batch &b, int nb, int M, int K, int N, i
         JGPT_REQUIRE((b.R[z] != nullptr) == residual, JGPT_ERR_INVALID_ARGUMENT, "gemm_umma: residuals for all products of a batch or for none");
     if (bn == 256) return residual ? launch_t<256, 4, 2>(walk, Aimg, b, M, K, N, d_status, st) : launch_t<256, 4, 0>(walk, Aimg, b, M, K, N, d_status, st);
     return residual ? launch_t<192, 5, 2>(walk, Aimg, b, M, K, N, d_status, st) : launch_t<192, 5, 0>(walk, Aimg, b, M, K, N, d_status, st);
+}
+
+int32_t launch_qkv_paged(const float *Aimg, const Batch &b, int M, int K, int N, const PagedAppendArgs &pa, int *d_status,
+                         cudaStream_t st) {
+    JGPT_REQUIRE(shape_ok(K, N) && M > 0 && N == pa.H * 16, JGPT_ERR_INVALID_ARGUMENT,
+                 "gemm_umma qkv: unsupported shape M=%d K=%d N=%d (heads %d, d_head 16)", M, K, N, pa.H);
+    const int bn = tile_cols(N);
+    TileWalk walk{(N + bn - 1) / bn, 3, 0};
+    walk.total = walk.n_tiles_n * 3 * ((M + BM - 1) / BM);
+    if (bn == 256) return launch_t<256, 4, 3>(walk, Aimg, b, M, K, N, d_status, st, pa);
+    return launch_t<192, 5, 3>(walk, Aimg, b, M, K, N, d_status, st, pa);
 }
 
 int32_t launch_swiglu(const float *Aimg, const float *Wpair_img, int M, int K, int F, float *act_image, int *d_status,

@@ -43,6 +43,12 @@ int32_t launch(const float *Aimg, const Batch &b, int nb, int M, int K, int N, i
 int32_t launch_swiglu(const float *Aimg, const float *Wpair_img, int M, int K, int F, float *act_image, int *d_status,
                       cudaStream_t st);
 
+// The Q, K, V products of a prefill (b.Wimg[0..2]; d_head 16, N = heads * 16): Q goes to b.C[0] row major, K gets its
+// RoPE and both K and V are written as fp16 straight into the paged store - the arithmetic and the stores of the
+// append kernel, without the fp32 round trip through memory.
+int32_t launch_qkv_paged(const float *Aimg, const Batch &b, int M, int K, int N, const PagedAppendArgs &pa, int *d_status,
+                         cudaStream_t st);
+
 inline bool shape_ok(int K, int N) { return K >= BK && K % BK == 0 && N % 4 == 0; }
 inline bool swiglu_shape_ok(int K, int F) { return K >= BK && K % BK == 0 && F % 128 == 0; }
 

@@ -796,10 +796,13 @@ static int32_t ensure_sample_work(Model *m, int rows) {
 // The same decoder blocks for prefill-sized `rows`: every projection on the tcgen05 kernel, activations handed
 // from producer to consumer as operand images (RMSNorm writes one, the W1/W3 product's SwiGLU epilogue writes
 // one; only the attention output is packed by a kernel of its own).
-// attn(l, image): attention of layer l; writes the Wo operand image itself when image != nullptr (only asked
-// for when attn_writes_image), the row-major m->att otherwise.
+// attn(l, image, kv_in_cache): attention of layer l; writes the Wo operand image itself when image != nullptr, the
+// row-major m->att otherwise; kv_in_cache: the K / V rows of the layer are already in the paged store.
+// `paged` != nullptr (a prefill at d_head 16): the attention can write that image, and the Q,K,V product writes
+// K / V straight into the paged store (paged->layer is set per layer here).
 template <class AttnFn>
-static int32_t run_layers_umma(Model *m, int rows, bool attn_writes_image, AttnFn &&attn) {
+static int32_t run_layers_umma(Model *m, int rows, const PagedAppendArgs *paged, AttnFn &&attn) {
+    const bool attn_writes_image = paged != nullptr;
     const int D = m->d_model, F = m->d_ff;
     cudaStream_t st = m->ctx->stream;
     int *status = m->ctx->d_status;
@@ -820,8 +823,14 @@ static int32_t run_layers_umma(Model *m, int rows, bool attn_writes_image, AttnF
         wo.C[0] = m->x, wo.R[0] = m->x;  // x1 = x + attn.Wo (each element read then written by the same thread)
         w2.C[0] = m->x, w2.R[0] = m->x;
         if ((rc = umma::rmsnorm_pack(m->x, y.norm1, rows, D, m->eps, m->aimg, st))) return rc;
-        if ((rc = umma::launch(m->aimg, qkv, 3, rows, D, D, status, st))) return rc;
-        if ((rc = attn(l, attn_writes_image ? m->aimg : nullptr))) return rc;
+        if (paged) {
+            PagedAppendArgs pa = *paged;
+            pa.layer = l;
+            if ((rc = umma::launch_qkv_paged(m->aimg, qkv, rows, D, D, pa, status, st))) return rc;
+        } else {
+            if ((rc = umma::launch(m->aimg, qkv, 3, rows, D, D, status, st))) return rc;
+        }
+        if ((rc = attn(l, attn_writes_image ? m->aimg : nullptr, paged != nullptr))) return rc;
         if (!attn_writes_image && (rc = umma::pack_activations(m->att, nullptr, rows, D, m->aimg, st))) return rc;
         if ((rc = umma::launch(m->aimg, wo, 1, rows, D, D, status, st))) return rc;
         if ((rc = umma::rmsnorm_pack(m->x, y.norm2, rows, D, m->eps, m->aimg, st))) return rc;
@@ -887,7 +896,7 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         const float *Wqkv[3] = {y.wq, y.wk, y.wv};
         float *Cqkv[3] = {m->q, m->k, m->v};
         if ((rc = small_launch<true, 0>(m, m->x, rows, D, D, 3, Wqkv, Cqkv, nullptr, nullptr, n1))) return rc;
-        if ((rc = attn(l, nullptr))) return rc;
+        if ((rc = attn(l, nullptr, false))) return rc;
         const float *Wo[1] = {y.wo};
         float *Cx[1] = {m->x};
         const float *Rx[1] = {m->x};  // x1 = x + attn.Wo (each element read then written by the same thread)
@@ -904,12 +913,12 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
 }
 
 template <class AttnFn>
-static int32_t run_layers(Model *m, int rows, bool attn_writes_image, AttnFn &&attn) {
+static int32_t run_layers(Model *m, int rows, const PagedAppendArgs *paged, AttnFn &&attn) {
     const int D = m->d_model, F = m->d_ff;
     if (small_mode(m, rows)) return run_layers_small(m, rows, attn);
     if (!m->strict && m->umma_min_rows > 0 && rows >= m->umma_min_rows && umma::shape_ok(D, D) && umma::shape_ok(D, F) &&
         umma::shape_ok(F, D) && sizeof(float) * 8 * (size_t)(D + 4) <= 48 * 1024)
-        return run_layers_umma(m, rows, attn_writes_image, attn);
+        return run_layers_umma(m, rows, paged, attn);
     cudaStream_t st = m->ctx->stream;
     for (int l = 0; l < m->layers; l++) {
         const LayerW &y = m->L[(size_t)l];
@@ -918,7 +927,7 @@ static int32_t run_layers(Model *m, int rows, bool attn_writes_image, AttnFn &&a
         float *Cqkv[3] = {m->q, m->k, m->v};
         int32_t rc = gemm(m, m->xn, rows, D, D, 3, Wqkv, Cqkv, nullptr);
         if (rc) return rc;
-        rc = attn(l, nullptr);
+        rc = attn(l, nullptr, false);
         if (rc) return rc;
         const float *Wo[1] = {y.wo};
         float *Co[1] = {m->x};
@@ -1284,9 +1293,22 @@ int32_t jgpt_forward_prefill_batch(jgpt_model h, jgpt_kvpool poolh, const int32_
     JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 2 * (size_t)rows, cudaMemcpyHostToDevice, st));
     embed_pos_kernel<<<rows, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + rows, m->x, m->d_model, m->ss_a);
     // d_head 16: one head is exactly one 16-wide k tile of the Wo operand image, which the attention kernel can
-    // then write itself
-    rc = run_layers(m, rows, p->dhead == 16, [&](int l, float *image) {
-        return launch_attn_prefill(p, l, m->q, m->k, m->v, seq_ids_host, seq_starts_host, rope_offsets_host, n, m->att, image);
+    // then write itself, and the Q,K,V product can append K / V to the paged store from its epilogue
+    PagedAppendArgs pa{};
+    const PagedAppendArgs *paged = nullptr;
+    if (p->dhead == 16 && m->d_model == p->heads * 16) {
+        int max_S = 0, n_rows = 0;
+        rc = prefill_upload_descriptors(p, seq_ids_host, seq_starts_host, rope_offsets_host, n, &max_S, &n_rows);
+        if (rc) return rc;
+        pa.kv = p->kv, pa.table = p->d_table, pa.rope = p->d_rope;
+        pa.seqs = reinterpret_cast<const PrefillSeq *>(p->d_prefill_desc), pa.status = p->ctx->d_status;
+        pa.n_seqs = n, pa.H = p->heads, pa.layer = 0, pa.n_blocks = p->n_blocks, pa.mbs = p->max_blocks_per_seq;
+        pa.max_positions = p->max_positions;
+        paged = &pa;
+    }
+    rc = run_layers(m, rows, paged, [&](int l, float *image, bool kv_in_cache) {
+        return launch_attn_prefill(p, l, m->q, m->k, m->v, seq_ids_host, seq_starts_host, rope_offsets_host, n, m->att, image,
+                                   kv_in_cache);
     });
     if (rc) return rc;
     int n_sel = 0;
@@ -1375,7 +1397,7 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
         if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
         embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
-        int32_t r2 = run_layers(m, n, false, [&](int l, float *) {
+        int32_t r2 = run_layers(m, n, nullptr, [&](int l, float *, bool) {
             return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att);
         });
         if (r2) return r2;
