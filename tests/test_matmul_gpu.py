@@ -178,5 +178,15 @@ def test_jgpt_35m_full_context_prefill_on_the_default_path_matches_oracle(ctx):
                 # 1e-4 the logits are allowed)
                 assert (np.abs(got_p - want_p) <= ulp + (2e-4 if layer == 0 else 1e-3)).all()
                 assert (got_p == want_p).mean() > (0.97 if layer == 0 else 0.6)
+        # the sliding-window form: a 600-token re-prefill at ropeOffset 100 (positions and RoPE shifted, slots from 0),
+        # K / V written by the projection's epilogue, 600 tokens = 37.5 blocks: the last block is zero-filled
+        cache.clear()
+        oc16b = om.new_cache(kv_fp16=True)
+        got2 = gm.forwardPrefill(prompt[:600], cache, 100)
+        want2 = om.forward_prefill(prompt[:600], oc16b, rope_offset=100)
+        assert cache.length() == 600 and np.abs(got2 - want2).max() < 5e-4
+        k0, v0 = cache.getK(0).to_host(), cache.getV(0).to_host()
+        assert (k0[:, :600] == oc16b.k(0)[:, :600]).mean() > 0.97 and (v0[:, :600] == oc16b.v(0)[:, :600]).mean() > 0.97
+        assert not k0[:, 600:].any() and not v0[:, 600:].any()
     finally:
         cache.close(), gm.close(), om.close()
