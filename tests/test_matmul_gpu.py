@@ -190,3 +190,32 @@ def test_jgpt_35m_full_context_prefill_on_the_default_path_matches_oracle(ctx):
         assert not k0[:, 600:].any() and not v0[:, 600:].any()
     finally:
         cache.close(), gm.close(), om.close()
+
+
+def test_ragged_batched_prefill_on_the_tcgen05_path(ctx):
+    """Three prompts of 37, 16 and 50 tokens in one call, every projection forced onto the tcgen05 kernel: the Q,K,V
+    epilogue finds each row's sequence, slot and block itself.  Last-row logits as the oracle's per-sequence prefill,
+    layer-0 payload on the oracle's fp16 values, slots past each prompt zero."""
+    V, MS, D, H, L, F = 96, 64, 64, 4, 2, 128
+    om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=31, std=0.15)
+    with _env(JGPT_B200_UMMA_MIN_ROWS=1):
+        gm = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=128)
+    gm.setParameters(om.tensors())
+    pool = gm.newPool(3 * MS // 16, 3)
+    try:
+        lens = [37, 16, 50]
+        prompts = [np.array([(i * 11 + 5 * s) % V for i in range(n)], np.int32) for s, n in enumerate(lens)]
+        seqs = [pool.seq_alloc() for _ in lens]
+        logits, nxt = gm.forwardPrefillBatch(pool, seqs, prompts)
+        for i, (s, pr) in enumerate(zip(seqs, prompts)):
+            oc = om.new_cache(kv_fp16=True)
+            want = om.forward_prefill(pr, oc)[-1]
+            assert np.abs(logits[i] - want).max() < 1e-3
+            assert int(nxt[i]) == int(np.argmax(logits[i]))
+            kd, vd = ctx.alloc((H, MS, D // H)), ctx.alloc((H, MS, D // H))
+            pool.gather(0, s, len(pr), MS, kd, vd)
+            k, v = kd.to_host(), vd.to_host()
+            assert (k[:, :len(pr)] == oc.k(0)[:, :len(pr)]).mean() > 0.97 and (v[:, :len(pr)] == oc.v(0)[:, :len(pr)]).mean() > 0.97
+            assert not k[:, len(pr):].any() and not v[:, len(pr):].any()
+    finally:
+        pool.close(), gm.close(), om.close()
