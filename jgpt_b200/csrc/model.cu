@@ -360,8 +360,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const float *__restrict__ 
 // eighth of the fragment loads, splits and MMAs of the k loop; the eight partial tiles are added in warp
 // order through shared memory (deterministic) in front of the residual epilogue.
 constexpr int kSmallBK = 64;
-template <int STAGES>
-__host__ __device__ constexpr size_t gemm_small_smem_bytes() { return sizeof(float) * (size_t)STAGES * (16 * (kSmallBK + 4) + kSmallBK * (32 + 8)); }
+template <int STAGES, int MT = 1>
+__host__ __device__ constexpr size_t gemm_small_smem_bytes() { return sizeof(float) * (size_t)STAGES * (16 * MT * (kSmallBK + 4) + kSmallBK * (32 + 8)); }
 
 //
 // Fusions of the decode step (template flags):
@@ -378,11 +378,12 @@ struct SmallFuse {
     float eps;
 };
 
-template <int STAGES, bool NORM, int EPI>
+// MT = 2: 32-row tiles (two MMA row blocks per warp share every weight fragment) for the larger decode batches.
+template <int STAGES, bool NORM, int EPI, int MT = 1>
 __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restrict__ A, const GemmBatch B, int M, int K, int N,
                                                             const int *__restrict__ rowsel, const SmallFuse F) {
-    constexpr int BM = 16, BN = 32, BK = kSmallBK, AS = BK + 4, WS = BN + 8;
-    static_assert(STAGES >= 2 && sizeof(float) * 8 * BM * (BN + 1) <= gemm_small_smem_bytes<STAGES>(), "reduction buffer must fit");
+    constexpr int BM = 16 * MT, BN = 32, BK = kSmallBK, AS = BK + 4, WS = BN + 8;
+    static_assert(STAGES >= 2 && sizeof(float) * 8 * BM * (BN + 1) <= gemm_small_smem_bytes<STAGES, MT>(), "reduction buffer must fit");
     extern __shared__ __align__(16) float gemm_smem[];
     float (*As)[BM][AS] = reinterpret_cast<float (*)[BM][AS]>(gemm_smem);
     float (*Ws)[BK][WS] = reinterpret_cast<float (*)[BK][WS]>(gemm_smem + (size_t)STAGES * BM * AS);
@@ -391,27 +392,37 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
 
-    // this thread's copy slots: one 16-byte chunk of A, two of W per k tile
+    // this thread's copy slots: MT 16-byte chunks of A (rows a_r, a_r + 16), two of W per k tile
     const int a_r = tid >> 4, a_c = (tid & 15) * 4;
-    const bool a_row_ok = m0 + a_r < M;
-    const float *a_src = A + (size_t)(a_row_ok ? (rowsel ? rowsel[m0 + a_r] : m0 + a_r) : 0) * K + a_c;
+    bool a_row_ok[MT];
+    const float *a_src[MT];
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+        a_row_ok[i] = m0 + a_r + 16 * i < M;
+        a_src[i] = A + (size_t)(a_row_ok[i] ? (rowsel ? rowsel[m0 + a_r + 16 * i] : m0 + a_r + 16 * i) : 0) * K + a_c;
+    }
     const int w_k = tid >> 3, w_c = (tid & 7) * 4;  // second chunk: k + 32
     const bool w_col_ok = n0 + w_c < N;
     const float *w_src = W + (size_t)w_k * N + (w_col_ok ? n0 + w_c : 0);
     auto load_tiles = [&](int buf, int k0) {
-        const bool ak = a_row_ok && k0 + a_c < K;
-        cp_async16(&As[buf][a_r][a_c], ak ? a_src + k0 : A, ak);
+#pragma unroll
+        for (int i = 0; i < MT; i++) {
+            const bool ak = a_row_ok[i] && k0 + a_c < K;
+            cp_async16(&As[buf][a_r + 16 * i][a_c], ak ? a_src[i] + k0 : A, ak);
+        }
         const bool k1 = w_col_ok && k0 + w_k < K, k2 = w_col_ok && k0 + w_k + 32 < K;
         cp_async16(&Ws[buf][w_k][w_c], k1 ? w_src + (size_t)k0 * N : W, k1);
         cp_async16(&Ws[buf][w_k + 32][w_c], k2 ? w_src + (size_t)(k0 + 32) * N : W, k2);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    float acc[4][4], cor[4][4];
+    float acc[MT][4][4], cor[MT][4][4];
 #pragma unroll
-    for (int j = 0; j < 4; j++)
+    for (int i = 0; i < MT; i++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) acc[j][e] = 0.f, cor[j][e] = 0.f;
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f, cor[i][j][e] = 0.f;
 
     const int nk = (K + BK - 1) / BK;
 #pragma unroll
@@ -439,44 +450,57 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         __syncthreads();  // tile kt (and s_inv) visible to all; everyone is done with the buffer refilled below (read at kt-1)
         if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
         else asm volatile("cp.async.commit_group;" ::: "memory");
-        float a0 = As[buf][g][ks + t], a1 = As[buf][g + 8][ks + t], a2 = As[buf][g][ks + t + 4], a3 = As[buf][g + 8][ks + t + 4];
+        uint32_t ah[MT][4], al[MT][4];
+        float g0 = 0.f, g1 = 0.f;
         if (NORM) {
             const int k = kt * BK + ks + t;
-            const float g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
-            const float ia = s_inv[g], ib = s_inv[g + 8];
-            a0 = a0 * ia * g0, a1 = a1 * ib * g0, a2 = a2 * ia * g1, a3 = a3 * ib * g1;
+            g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
         }
-        uint32_t ah[4], al[4];
-        split_tf32(a0, ah[0], al[0]);
-        split_tf32(a1, ah[1], al[1]);
-        split_tf32(a2, ah[2], al[2]);
-        split_tf32(a3, ah[3], al[3]);
+#pragma unroll
+        for (int i = 0; i < MT; i++) {
+            const int r = 16 * i + g;
+            float a0 = As[buf][r][ks + t], a1 = As[buf][r + 8][ks + t], a2 = As[buf][r][ks + t + 4], a3 = As[buf][r + 8][ks + t + 4];
+            if (NORM) {
+                const float ia = s_inv[r], ib = s_inv[r + 8];
+                a0 = a0 * ia * g0, a1 = a1 * ib * g0, a2 = a2 * ia * g1, a3 = a3 * ib * g1;
+            }
+            split_tf32(a0, ah[i][0], al[i][0]);
+            split_tf32(a1, ah[i][1], al[i][1]);
+            split_tf32(a2, ah[i][2], al[i][2]);
+            split_tf32(a3, ah[i][3], al[i][3]);
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int c = j * 8 + g;
             uint32_t bh0, bl0, bh1, bl1;
             split_tf32(Ws[buf][ks + t][c], bh0, bl0);
             split_tf32(Ws[buf][ks + t + 4][c], bh1, bl1);
-            mma_tf32(cor[j], al, bh0, bh1);
-            mma_tf32(acc[j], ah, bh0, bh1);
-            mma_tf32(cor[j], ah, bl0, bl1);
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+                mma_tf32(cor[i][j], al[i], bh0, bh1);
+                mma_tf32(acc[i][j], ah[i], bh0, bh1);
+                mma_tf32(cor[i][j], ah[i], bl0, bl1);
+            }
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();  // the stage buffers are dead: reuse them for the eight partial tiles
     float (*red)[BM][BN + 1] = reinterpret_cast<float (*)[BM][BN + 1]>(gemm_smem);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        red[warp][g][j * 8 + 2 * t] = acc[j][0] + cor[j][0];
-        red[warp][g][j * 8 + 2 * t + 1] = acc[j][1] + cor[j][1];
-        red[warp][g + 8][j * 8 + 2 * t] = acc[j][2] + cor[j][2];
-        red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3] + cor[j][3];
-    }
+    for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int r = 16 * i + g;
+            red[warp][r][j * 8 + 2 * t] = acc[i][j][0] + cor[i][j][0];
+            red[warp][r][j * 8 + 2 * t + 1] = acc[i][j][1] + cor[i][j][1];
+            red[warp][r + 8][j * 8 + 2 * t] = acc[i][j][2] + cor[i][j][2];
+            red[warp][r + 8][j * 8 + 2 * t + 1] = acc[i][j][3] + cor[i][j][3];
+        }
     __syncthreads();
     float *C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);
     const float *R = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
-    if (EPI == 2) {
-        const int r = tid >> 4, c = tid & 15, m = m0 + r, n = blockIdx.x * 16 + c, Fo = N / 2;
+    for (int e = tid; EPI == 2 && e < BM * 16; e += 256) {
+        const int r = e >> 4, c = e & 15, m = m0 + r, n = blockIdx.x * 16 + c, Fo = N / 2;
         if (m < M && n < Fo) {
             float h = red[0][r][c], gv = red[0][r][16 + c];
 #pragma unroll
@@ -635,17 +659,28 @@ __global__ void __launch_bounds__(256) sample_kernel(const float *__restrict__ l
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
+// From this many rows the decode-sized kernel uses 32-row tiles (JGPT_B200_SMALL_WIDE_ROWS).  Measured per decode
+// step, 16-row against 32-row tiles: batch 64 0.64 / 0.71 ms, batch 128 0.83 / 0.89 ms, batch 256 1.40 / 1.31 ms.
+static int small_rows_for_wide_tiles() {
+    static const int v = env_int("JGPT_B200_SMALL_WIDE_ROWS", 256);
+    return v;
+}
+
 // The larger tile configurations need more than 48 KiB of dynamic shared memory: once per device.
 static cudaError_t opt_in_shared_memory(const Ctx *ctx) {
     static bool opted[64] = {};
     if (opted[ctx->device & 63]) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)gemm_tc_smem_bytes<64, 64, 3>());
-    const int sb = (int)gemm_small_smem_bytes<4>();
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    const int sb = (int)gemm_small_smem_bytes<4, 1>(), sb2 = (int)gemm_small_smem_bytes<4, 2>();
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb2);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb2);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb2);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb2);
     if (e == cudaSuccess) opted[ctx->device & 63] = true;
     return e;
 }
@@ -660,8 +695,13 @@ static int32_t gemm_small(Ctx *ctx, int strict, const float *A, int M, int K, in
         // Decode-sized M: 16x32 tiles, the k loop split over eight warps (latency); above that 64x64 tiles.
         JGPT_CUDA_TRY(opt_in_shared_memory(ctx));
         if (M <= 512) {  // measured: faster than 32x32 tiles of four warps up to here (batch 128: 1.34 -> 1.04 ms per decode step)
-            dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
-            gemm_tc_small_kernel<4, false, 0><<<grid, 256, gemm_small_smem_bytes<4>(), st>>>(A, B, M, K, N, rowsel, SmallFuse{});
+            if (M >= small_rows_for_wide_tiles()) {
+                dim3 grid((N + 31) / 32, (M + 31) / 32, nb);
+                gemm_tc_small_kernel<4, false, 0, 2><<<grid, 256, gemm_small_smem_bytes<4, 2>(), st>>>(A, B, M, K, N, rowsel, SmallFuse{});
+            } else {
+                dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
+                gemm_tc_small_kernel<4, false, 0, 1><<<grid, 256, gemm_small_smem_bytes<4, 1>(), st>>>(A, B, M, K, N, rowsel, SmallFuse{});
+            }
         } else {
             dim3 grid((N + 63) / 64, (M + 63) / 64, nb);
             gemm_tc_kernel<64, 64, 2, 2, 3><<<grid, 128, gemm_tc_smem_bytes<64, 64, 3>(), st>>>(A, B, M, K, N, rowsel);
@@ -879,8 +919,13 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     JGPT_CUDA_TRY(opt_in_shared_memory(m->ctx));
     GemmBatch B;
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
-    dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
-    gemm_tc_small_kernel<4, NORM, EPI><<<grid, 256, gemm_small_smem_bytes<4>(), m->ctx->stream>>>(A, B, M, K, N, rowsel, fuse);
+    if (M >= small_rows_for_wide_tiles()) {
+        dim3 grid((N + 31) / 32, (M + 31) / 32, nb);
+        gemm_tc_small_kernel<4, NORM, EPI, 2><<<grid, 256, gemm_small_smem_bytes<4, 2>(), m->ctx->stream>>>(A, B, M, K, N, rowsel, fuse);
+    } else {
+        dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
+        gemm_tc_small_kernel<4, NORM, EPI, 1><<<grid, 256, gemm_small_smem_bytes<4, 1>(), m->ctx->stream>>>(A, B, M, K, N, rowsel, fuse);
+    }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
