@@ -740,12 +740,18 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
 }
 
 // Largest divisor of H whose slab (HG * 64 * DH bytes) stays within 24 KiB and 480 consumer threads.
-static int pick_head_group(int H, int DH, int forced) {
+// A launch with few (layer, sequence) pairs - the model's per-layer decode step at small batch - takes the smallest
+// group of at least 6 heads that still gives no more CTAs than fit at once (two per SM): more, lighter CTAs
+// (measured on the decode step at batch 64: 0.638 ms with 24 heads per CTA, 0.613 ms with 6 or 8).
+static int pick_head_group(int H, int DH, int forced, long long pairs = 0, long long slots = 0) {
     const int cap = std::min(30, std::max(1, 384 / DH));  // == max_head_group<DH>()
     if (forced > 0 && forced <= cap && H % forced == 0) return forced;
     int best = 1;
     for (int g = 1; g <= std::min(H, cap); g++)
         if (H % g == 0) best = g;
+    if (pairs > 0 && slots > 0 && pairs * (H / best) < slots)
+        for (int g = 6; g < best; g++)
+            if (H % g == 0 && pairs * (H / g) <= slots) return g;
     return best;
 }
 
@@ -797,7 +803,7 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.status = p->ctx->d_status;
     P.n = n, P.H = p->heads, P.layer0 = layer0, P.n_layers = n_layers, P.mbs = p->max_blocks_per_seq;
     P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
-    P.HG = pick_head_group(p->heads, DH, p->head_group);
+    P.HG = pick_head_group(p->heads, DH, p->head_group, (long long)n_layers * n, 2ll * p->ctx->sm_count);
     P.n_hg = p->heads / P.HG;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
     // Work distribution.  Default (persistent <= 0): one CTA per work item, the hardware block scheduler hands
