@@ -49,7 +49,9 @@ enum {
     JGPT_ERR_CUDA = 7,
     JGPT_ERR_UNSUPPORTED = 8,      /* the reference returns null / throws ISE for unsupported shapes */
     JGPT_ERR_DEVICE_CHECK = 9,     /* a kernel reported a failed self-check or a timed-out wait */
-    JGPT_ERR_IO = 10
+    JGPT_ERR_IO = 10,
+    JGPT_ERR_NCCL = 11,            /* the collective library reported an error (or is missing) */
+    JGPT_ERR_TIMEOUT = 12          /* a bounded host-side wait ran out; nothing blocks for ever */
 };
 
 /* ---------------------------------------------------------------------------------------------
@@ -76,6 +78,9 @@ JGPT_API int32_t jgpt_dev_free(jgpt_ctx ctx, void *dev);
 JGPT_API int32_t jgpt_h2d(jgpt_ctx ctx, void *dev_dst, const void *host_src, uint64_t bytes);
 JGPT_API int32_t jgpt_d2h(jgpt_ctx ctx, void *host_dst, const void *dev_src, uint64_t bytes);
 JGPT_API int32_t jgpt_dev_memset(jgpt_ctx ctx, void *dev, int32_t byte_value, uint64_t bytes);
+/* TensorOpsGPU.getGpuMemoryAllocated0 / getGpuMemoryReserved0 (C/jgpt_cuda_jni_ops_graph.inl:471-491):
+ * free and total bytes of the context's device (cudaMemGetInfo); allocated = total - free. */
+JGPT_API int32_t jgpt_mem_info(jgpt_ctx ctx, uint64_t *free_bytes_out, uint64_t *total_bytes_out);
 /* cuda.CudaPinnedHost (C/jgpt_cuda_jni_ops_graph.inl:494-519). */
 JGPT_API int32_t jgpt_host_alloc_pinned(uint64_t bytes, void **host_out);
 JGPT_API int32_t jgpt_host_free_pinned(void *host);
@@ -118,6 +123,9 @@ JGPT_API int32_t jgpt_kvpool_destroy(jgpt_kvpool pool); /* KvCacheGpu.close() */
 JGPT_API int32_t jgpt_kvpool_free_blocks(jgpt_kvpool pool, int32_t *n_free_out);
 /* Device address and byte size of the K/V storage (tests poison / inspect it). */
 JGPT_API int32_t jgpt_kvpool_storage(jgpt_kvpool pool, void **dev_out, uint64_t *bytes_out);
+/* Device mirror of the block tables, int32 [max_seqs][row_stride], -1 = unmapped (read-only for
+ * callers' own kernels; tests corrupt an entry to exercise the kernels' self-checks). */
+JGPT_API int32_t jgpt_kvpool_table_device(jgpt_kvpool pool, int32_t **dev_out, int32_t *row_stride_out);
 
 /* Sequence lifecycle: `new KvCacheGpu(..)` / close(); length(), setLength(), clear()
  * (J/model/KvCacheGpu.java:60-101).  seq ids are small ints (lowest free slot first). */
@@ -306,6 +314,43 @@ JGPT_API int32_t jgpt_sched_result(uint64_t sched, int32_t req_id, int32_t *toke
  * request), 3 finish(request, tokens sampled). */
 JGPT_API int32_t jgpt_sched_events(uint64_t sched, int32_t *out, int32_t cap_ints, int32_t *n_ints_out);
 
+/* ---------------------------------------------------------------------------------------------
+ * Multi-GPU: gather of the sampled token ids (one process + one context per GPU of one box).
+ * Sequences are sharded over the GPUs and never interact; the only exchange is what each rank
+ * sampled in a step.  The reference has no counterpart: it drives device 0 only
+ * (C/jgpt_cuda_jni_ops_graph.inl:112,119).  NCCL (libnccl.so.2, or the path in JGPT_B200_NCCL_LIB)
+ * is opened at run time, so single-GPU hosts do not need it.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Rank 0 makes the 128-byte rendezvous id (ncclGetUniqueId) and gives it to the other ranks by
+ * whatever channel the host has (a file, a socket, the launcher's store). */
+JGPT_API int32_t jgpt_comm_unique_id(void *id_out, int32_t cap_bytes);
+/* Joins `world` ranks.  Each step a rank contributes up to max_words int32 words; up to `depth`
+ * steps may be in flight before a result has to be read (the ring holds depth + 2 slots).
+ * timeout_ms bounds every wait on the other ranks inside later calls (the rendezvous itself is given
+ * at least 60 s); a wait that runs out returns JGPT_ERR_TIMEOUT.  world = 1 needs no id and no NCCL.
+ * Allocates its buffers here, nothing later. */
+JGPT_API int32_t jgpt_comm_create(jgpt_ctx ctx, const void *unique_id, int32_t world, int32_t rank,
+                                  int32_t max_words, int32_t depth, int32_t timeout_ms, uint64_t *comm_out);
+/* Orderly when nothing is in flight; otherwise aborts the communicator (ncclCommAbort), which also
+ * ends a collective that is still waiting for a rank that never came. */
+JGPT_API int32_t jgpt_comm_destroy(uint64_t comm);
+/* One step's words from host memory, e.g. the (request id, token) pairs of jgpt_sched_step.
+ * Enqueues upload, ncclAllGather and download on the communicator's own stream and returns. */
+JGPT_API int32_t jgpt_comm_submit(uint64_t comm, const int32_t *words_host, int32_t n_words);
+/* The same from device memory, ordered after the work already enqueued on the context's stream:
+ * e.g. the token ids the sampler of jgpt_forward_decode left on the device
+ * (jgpt_model_next_tokens_device), without a round trip through the host. */
+JGPT_API int32_t jgpt_comm_submit_device(uint64_t comm, const int32_t *words_dev, int32_t n_words);
+/* Steps in flight; *must_pop_out = 1 when more than `depth` are, i.e. read one before submitting. */
+JGPT_API int32_t jgpt_comm_in_flight(uint64_t comm, int32_t *n_out, int32_t *must_pop_out);
+/* Result of the oldest step in flight: words_out [world][max_words] (unused tail = -1) and
+ * counts_out [world], rank by rank, identical on every rank.  Waits at most timeout_ms; on
+ * JGPT_ERR_TIMEOUT the step stays in flight and the call may be repeated. */
+JGPT_API int32_t jgpt_comm_pop(uint64_t comm, int32_t *words_out, int32_t *counts_out, int32_t timeout_ms);
+/* Device address of the token ids sampled by the model's last forward step ([rows] int32). */
+JGPT_API int32_t jgpt_model_next_tokens_device(jgpt_model model, const int32_t **dev_out);
+
 /* Decode attention that allocates nothing.  No counterpart in the reference.
  *
  * Same computation as jgpt_attn_decode for ONE layer, but the split-K scratch (partial softmax
@@ -315,12 +360,18 @@ JGPT_API int32_t jgpt_sched_events(uint64_t sched, int32_t *out, int32_t cap_int
  * own buffers (a late cudaMalloc may fail there, and every cudaMalloc/cudaFree stalls the device).
  * The call makes no cudaMalloc / cudaFree and uses no allocating library routine.
  *
- *   - Limits: n * ceil(ceil(max_len/16)/chunk) * heads * (dhead+2) <= 1,048,576 partial words (4 MiB)
- *     and n * head_groups <= 4,096 counters.  Larger requests return JGPT_ERR_INVALID_ARGUMENT with a
- *     message that states both numbers.  Every GPU that loads the library holds the 4 MiB + 16 KiB
- *     array until the process exits.
- *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress); make
- *     that first call before any stream capture.
+ *   - Set-up and when the memory is taken.  The first call on a device resolves the array's device
+ *     address (cudaGetSymbolAddress) and raises the kernel's shared-memory limit.  CUDA loads code
+ *     lazily, so it is this first use -- not opening the library -- that reserves the array's
+ *     4 MiB + 16 KiB on that GPU and loads the kernel; from then on the GPU holds them until the
+ *     process exits and later calls take no device memory at all.  A call with n = 0 performs only
+ *     the set-up (pointers may be NULL): make it once per device BEFORE the host commits the rest of
+ *     the GPU and before any stream capture.
+ *   - Limits apply only when a sequence is split into chunks (one chunk needs no scratch):
+ *     n * chunks * heads * (dhead+2) <= 1,048,576 partial words and n * head_groups <= 4,096
+ *     counters, where chunks <= ceil(ceil(max_len/16) / 4) (a chunk is never shorter than 4 blocks)
+ *     and head_groups <= heads; a request within those caller-computable bounds always fits.
+ *     Larger requests return JGPT_ERR_INVALID_ARGUMENT with a message that states the numbers.
  *   - All calls on a device share the one array and it keeps the previous call's contents: the call
  *     clears the counters it uses on the stream before launching.  Two calls that overlap on the
  *     GPU (different contexts or streams on the same device) race on it; keep them stream ordered. */

@@ -9,4 +9,4 @@ from .binding import JgptError, PoolExhausted, load  # noqa: F401
 from .runtime import Context, DeviceBuffer  # noqa: F401
 from .kv_cache import KvPool, KvCacheGpu  # noqa: F401
 from .model import GPTModel  # noqa: F401
-from .scheduler import ContinuousBatcher, StepTokenGather, gather_step_tokens, shard_requests  # noqa: F401
+from .scheduler import ContinuousBatcher, TokenGather, pack_pairs, shard_requests, unpack_pairs  # noqa: F401

@@ -16,6 +16,7 @@ LIB_PATH = os.environ.get("JGPT_B200_LIB", os.path.join(_HERE, "lib", "libjgpt_b
 OK = 0
 ERR_INVALID_ARGUMENT, ERR_ILLEGAL_STATE, ERR_OUT_OF_RANGE, ERR_OUT_OF_MEMORY = 1, 2, 3, 4
 ERR_POOL_EXHAUSTED, ERR_BAD_HANDLE, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_CHECK, ERR_IO = 5, 6, 7, 8, 9, 10
+ERR_NCCL, ERR_TIMEOUT = 11, 12
 
 
 class JgptError(RuntimeError):
@@ -40,6 +41,8 @@ def raise_for(code: int, msg: str):
         raise MemoryError(msg)  # OutOfMemoryError
     if code == ERR_POOL_EXHAUSTED:
         raise PoolExhausted(code, msg)
+    if code == ERR_TIMEOUT:
+        raise TimeoutError(msg)
     raise JgptError(code, msg)
 
 

@@ -739,6 +739,19 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     }
 }
 
+// Raises a decode kernel's dynamic shared-memory limit to the largest request any launch makes, once per
+// (kernel variant, device).  Guarded: contexts of different devices may launch from different host threads.
+static cudaError_t decode_opt_in_smem(void (*kern)(const DecodeParams), int variant, int device) {
+    static std::mutex mu;
+    static bool done[16][64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    const bool tracked = variant >= 0 && variant < 16 && device >= 0 && device < 64;
+    if (tracked && done[variant][device]) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxStages * 24 * 1024);
+    if (e == cudaSuccess && tracked) done[variant][device] = true;
+    return e;
+}
+
 // Largest divisor of H whose slab (HG * 64 * DH bytes) stays within 24 KiB and 480 consumer threads.
 // A launch with few (layer, sequence) pairs - the model's per-layer decode step at small batch - takes the smallest
 // group of at least 6 heads that still gives no more CTAs than fit at once (two per SM): more, lighter CTAs
@@ -768,13 +781,10 @@ static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int t
     if constexpr (kCanMma) {
         if (mma) kern = fused ? attn_decode_kernel<DH, true, true> : attn_decode_kernel<DH, false, true>;
     }
-    // Opt in to > 48 KiB of dynamic shared memory once per kernel, device and size.
-    static int opted[4][16] = {};
-    int &have = opted[(fused ? 1 : 0) + (mma ? 2 : 0)][p->ctx->device & 15];
-    if ((int)smem > have) {
-        JGPT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        have = (int)smem;
-    }
+    // Opt in to > 48 KiB of dynamic shared memory once per kernel and device: the most a launch can ask for
+    // (kMaxStages stages of a 24 KiB slab), so that no later, smaller request ever lowers the limit again.
+    JGPT_CUDA_TRY(decode_opt_in_smem(kern, (fused ? 1 : 0) + (mma ? 2 : 0) + 4 * (DH == 4 ? 0 : DH == 8 ? 1 : DH == 16 ? 2 : 3),
+                                     p->ctx->device));
     kern<<<grid, threads, smem, p->ctx->stream>>>(P);
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
@@ -983,9 +993,10 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
         }
         rc = launch_attn_decode(p, layer0, n_layers, qi, ki, vi, dseq, drp, dlen, n, max_len, static_cast<float *>(dp[3]));
         if (rc) return rc;
+        JGPT_CUDA_TRY(status_enqueue_read(p->ctx));
         JGPT_CUDA_TRY(cudaStreamSynchronize(st));
         finish();
-        return JGPT_OK;
+        return status_check_after_sync(p->ctx, p, "jgpt_attn_decode_append_host");
     }
     JGPT_CUDA_TRY(upload_indices());
     // The layers of one call are independent, so the call is pipelined in groups of layers: while group g is
@@ -1024,9 +1035,10 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
         rc = launch_attn_decode(p, layer0, n_layers, dq, dk, dv, dseq, drp, dlen, n, max_len, dout);
         if (rc) return rc;
         JGPT_CUDA_TRY(cudaMemcpyAsync(out_host, dout, sizeof(float) * slab, cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(status_enqueue_read(p->ctx));
         JGPT_CUDA_TRY(cudaStreamSynchronize(st));
         finish();
-        return JGPT_OK;
+        return status_check_after_sync(p->ctx, p, "jgpt_attn_decode_append_host");
     }
     if (!p->s_in) {
         JGPT_CUDA_TRY(cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking));
@@ -1057,10 +1069,11 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
         JGPT_CUDA_TRY(cudaMemcpyAsync(out_host + off, dout + off, sizeof(float) * cnt, cudaMemcpyDeviceToHost, p->s_out));
         l0 += nl;
     }
+    JGPT_CUDA_TRY(status_enqueue_read(p->ctx));
     JGPT_CUDA_TRY(cudaStreamSynchronize(p->s_out));
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
     finish();
-    return JGPT_OK;
+    return status_check_after_sync(p->ctx, p, "jgpt_attn_decode_append_host");
 }
 
 }  // extern "C"
@@ -1073,8 +1086,13 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
 // generation path: a process that has already handed the whole GPU to its own buffers (a trainer
 // that samples text between optimizer steps with the device full, a server that sizes its KV pool to
 // whatever memory is left) can see that late cudaMalloc fail, and any cudaMalloc/cudaFree stalls the
-// device while it runs.  This variant never allocates: its scratch is the array below, which every
-// GPU that loads the library holds from load until the process exits.
+// device while it runs.  This variant never calls an allocator: its scratch is the array below.
+//
+// When the memory is taken: CUDA loads a module lazily, so the device memory of the array is
+// reserved (and the kernel's code loaded) the first time this translation unit is used on a device --
+// the set-up below -- not when the shared library is opened.  A call with n == 0 runs only that
+// set-up, so a host can do it before it commits the rest of the GPU.  From then on every GPU that ran
+// the set-up holds the array until the process exits.
 //
 // Limits, stated: kStaticPartialFloats fp32 partial words (4 MiB) and kStaticTickets counters
 // (16 KiB) per device.  One layer per call.  Requests that need more are rejected.
@@ -1088,19 +1106,32 @@ constexpr size_t kStaticTickets = 4096;                   // arrival counters, o
 static __device__ __align__(256) float g_decode_static_scratch[kStaticPartialFloats + kStaticTickets];
 
 constexpr int kStaticMaxDevices = 64;
-static float *g_static_scratch_addr[kStaticMaxDevices] = {};  // per device, resolved on first use
+static float *g_static_scratch_addr[kStaticMaxDevices] = {};  // per device, resolved by the set-up
+static std::mutex g_static_scratch_mu;                        // the table above and the opt-in below
 
-// Resolves the array's device address for the context's device (which must be current).
-static int32_t static_scratch_for(const Ctx *c, float **partials, int **tickets) {
+// Once per device, with that device current: resolves the array's device address and loads the kernel
+// (both trigger the lazy module load that reserves the array's memory).
+static int32_t static_scratch_setup(const Pool *p, float **partials, int **tickets) {
+    const Ctx *c = p->ctx;
     JGPT_REQUIRE(c->device >= 0 && c->device < kStaticMaxDevices, JGPT_ERR_UNSUPPORTED,
                  "device index %d is beyond the %d devices the static scratch table covers", c->device, kStaticMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
     if (!g_static_scratch_addr[c->device]) {
-        void *p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
-        if (e != cudaSuccess || !p)
-            return fail(JGPT_ERR_CUDA, "cudaGetSymbolAddress(static decode scratch) on device %d: %s", c->device,
-                        cudaGetErrorString(e));
-        g_static_scratch_addr[c->device] = static_cast<float *>(p);
+        void *addr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&addr, g_decode_static_scratch);
+        if (e != cudaSuccess || !addr)
+            return fail(e == cudaErrorMemoryAllocation ? JGPT_ERR_OUT_OF_MEMORY : JGPT_ERR_CUDA,
+                        "cudaGetSymbolAddress(static decode scratch) on device %d: %s", c->device, cudaGetErrorString(e));
+        cudaError_t a = cudaSuccess;
+        switch (p->dhead) {
+            case 4: a = decode_opt_in_smem(attn_decode_kernel<4, false, false>, 0, c->device); break;
+            case 8: a = decode_opt_in_smem(attn_decode_kernel<8, false, false>, 4, c->device); break;
+            case 16: a = decode_opt_in_smem(attn_decode_kernel<16, false, false>, 8, c->device); break;
+            case 32: a = decode_opt_in_smem(attn_decode_kernel<32, false, false>, 12, c->device); break;
+            default: break;
+        }
+        if (a != cudaSuccess) return fail(JGPT_ERR_CUDA, "static decode scratch set-up on device %d: %s", c->device, cudaGetErrorString(a));
+        g_static_scratch_addr[c->device] = static_cast<float *>(addr);
     }
     *partials = g_static_scratch_addr[c->device];
     *tickets = reinterpret_cast<int *>(g_static_scratch_addr[c->device] + kStaticPartialFloats);
@@ -1118,7 +1149,8 @@ static int32_t launch_attn_decode_static(Pool *p, int layer, const float *q, con
     P.status = p->ctx->d_status;
     P.n = n, P.H = p->heads, P.layer0 = layer, P.n_layers = 1, P.mbs = p->max_blocks_per_seq;
     P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
-    P.HG = pick_head_group(p->heads, DH, p->head_group);
+    // same launch shape as jgpt_attn_decode gives a one-layer call (small batches get lighter CTAs)
+    P.HG = pick_head_group(p->heads, DH, p->head_group, (long long)n, 2ll * p->ctx->sm_count);
     P.n_hg = p->heads / P.HG;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
     P.chunk_blocks = p->chunk_blocks > 0 ? p->chunk_blocks : pick_chunk_blocks(p, (long long)n * P.n_hg, max_blocks);
@@ -1129,27 +1161,35 @@ static int32_t launch_attn_decode_static(Pool *p, int layer, const float *q, con
     const long long items = (long long)n * P.n_hg * P.max_chunks;
     JGPT_REQUIRE(items < (1ll << 31), JGPT_ERR_INVALID_ARGUMENT, "too many work items (%lld)", items);
     P.n_items = (int)items;
-    const unsigned long long need_partials = (unsigned long long)n * P.max_chunks * p->heads * (DH + 2);
-    const unsigned long long need_tickets = (unsigned long long)n * P.n_hg;
-    JGPT_REQUIRE(need_partials <= kStaticPartialFloats && need_tickets <= kStaticTickets, JGPT_ERR_INVALID_ARGUMENT,
-                 "request needs %llu partial words and %llu counters; the static scratch holds %llu and %llu "
-                 "(lower n or max_len, or use jgpt_attn_decode)",
-                 need_partials, need_tickets, (unsigned long long)kStaticPartialFloats, (unsigned long long)kStaticTickets);
-    int32_t rc = static_scratch_for(p->ctx, &P.partials, &P.tickets);
+    int32_t rc = static_scratch_setup(p, &P.partials, &P.tickets);
     if (rc) return rc;
-    // The array keeps whatever the previous call left.  Partials are always written before they are read;
-    // the counters must start at zero (they reset themselves, but not if an earlier launch gave up half way).
-    JGPT_CUDA_TRY(cudaMemsetAsync(P.tickets, 0, sizeof(int) * need_tickets, p->ctx->stream));
+    if (P.max_chunks > 1) {
+        // Only a split sequence touches the scratch; an unsplit launch needs none of it and has no size limit.
+        const unsigned long long need_partials = (unsigned long long)n * P.max_chunks * p->heads * (DH + 2);
+        const unsigned long long need_tickets = (unsigned long long)n * P.n_hg;
+        JGPT_REQUIRE(need_partials <= kStaticPartialFloats && need_tickets <= kStaticTickets, JGPT_ERR_INVALID_ARGUMENT,
+                     "request needs %llu partial words and %llu counters; the static scratch holds %llu and %llu "
+                     "(lower n or max_len, or use jgpt_attn_decode)",
+                     need_partials, need_tickets, (unsigned long long)kStaticPartialFloats,
+                     (unsigned long long)kStaticTickets);
+        // The array keeps whatever the previous call left.  Partials are always written before they are read;
+        // the counters must start at zero (they reset themselves, but not if an earlier launch gave up half way).
+        JGPT_CUDA_TRY(cudaMemsetAsync(P.tickets, 0, sizeof(int) * need_tickets, p->ctx->stream));
+    }
     const int n_cons = ((kBlockTokens * P.HG + 31) / 32) * 32;
     const int threads = n_cons + 32;
     const size_t smem = (size_t)P.HG * 2 * kBlockTokens * DH * 2 * P.stages;
+    void (*kern)(const DecodeParams) = nullptr;
     switch (DH) {
-        case 4: return launch_decode_t<4>(p, P, false, threads, smem, P.n_items);
-        case 8: return launch_decode_t<8>(p, P, false, threads, smem, P.n_items);
-        case 16: return launch_decode_t<16>(p, P, false, threads, smem, P.n_items);
-        case 32: return launch_decode_t<32>(p, P, false, threads, smem, P.n_items);
+        case 4: kern = attn_decode_kernel<4, false, false>; break;
+        case 8: kern = attn_decode_kernel<8, false, false>; break;
+        case 16: kern = attn_decode_kernel<16, false, false>; break;
+        case 32: kern = attn_decode_kernel<32, false, false>; break;
         default: return fail(JGPT_ERR_UNSUPPORTED, "dhead %d not supported", DH);
     }
+    kern<<<P.n_items, threads, smem, p->ctx->stream>>>(P);
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
 }
 
 }  // namespace jgpt
@@ -1161,7 +1201,13 @@ extern "C" int32_t jgpt_attn_decode_static_scratch(jgpt_kvpool pool, int32_t lay
     JGPT_REQUIRE(p, JGPT_ERR_BAD_HANDLE, "bad kvpool handle");
     JGPT_CUDA_TRY(make_current(p->ctx));
     JGPT_REQUIRE(layer >= 0 && layer < p->layers, JGPT_ERR_OUT_OF_RANGE, "layer %d outside [0,%d)", layer, p->layers);
-    if (n == 0) return JGPT_OK;
+    JGPT_REQUIRE(p->dhead == 4 || p->dhead == 8 || p->dhead == 16 || p->dhead == 32, JGPT_ERR_UNSUPPORTED,
+                 "dhead %d not supported", p->dhead);
+    if (n == 0) {  // set-up only: take the array's memory and load the kernel now, launch nothing
+        float *partials;
+        int *tickets;
+        return static_scratch_setup(p, &partials, &tickets);
+    }
     JGPT_REQUIRE(n > 0 && q_dev && seq_ids_dev && rope_pos_dev && lens_dev && out_dev, JGPT_ERR_INVALID_ARGUMENT,
                  "null pointer or negative count");
     JGPT_REQUIRE(max_len >= 1, JGPT_ERR_INVALID_ARGUMENT, "max_len must be >= 1");

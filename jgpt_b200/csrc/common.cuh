@@ -108,6 +108,9 @@ struct Pool {
     int persistent = -1;  // < 0: automatic
     int head_group = 0;  // 0 = automatic
     int decode_mma = 0;  // 1: tensor-core consumer in the decode kernel (dhead 16)
+    // Unique per pool object (low half) and bumped when a device buffer that kernels are handed is reallocated (high
+    // half): captured CUDA graphs are keyed on it, so a pool re-created at the same address never replays an old graph.
+    uint64_t generation = 0;
 };
 
 struct Model;
@@ -139,6 +142,11 @@ Registry<Pool> &pool_registry();
 inline cudaError_t make_current(const Ctx *c) { return cudaSetDevice(c->device); }
 
 int env_int(const char *name, int dflt);
+
+// Device status word at the end of a self-synchronising entry point: enqueue the read with the step's other
+// device-to-host copies, and after the stream sync turn a non-zero word into JGPT_ERR_DEVICE_CHECK (pool may be null).
+cudaError_t status_enqueue_read(Ctx *c);
+int32_t status_check_after_sync(Ctx *c, Pool *p, const char *what);
 
 // Grow-only staging helpers (never called on the steady-state decode path once sized).
 int32_t pool_ensure_staging(Pool *p, uint64_t n_floats, uint64_t n_ints);

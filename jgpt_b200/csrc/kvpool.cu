@@ -6,6 +6,8 @@
 // contiguous memory: the decode kernel fetches such a slab with a single bulk copy.
 #include "common.cuh"
 
+#include <atomic>
+
 #include <algorithm>
 #include <cmath>
 
@@ -236,6 +238,7 @@ int32_t pool_ensure_split_scratch(Pool *p, uint64_t partial_floats, uint64_t tic
         p->d_partials = nullptr, p->partials_floats = 0;
         JGPT_CUDA_TRY(cudaMalloc(&p->d_partials, sizeof(float) * partial_floats));
         p->partials_floats = partial_floats;
+        p->generation += (uint64_t)1 << 32;  // captured graphs hold the old address
     }
     if (tickets > p->n_tickets) {
         JGPT_CUDA_TRY(cudaStreamSynchronize(p->ctx->stream));
@@ -244,6 +247,7 @@ int32_t pool_ensure_split_scratch(Pool *p, uint64_t partial_floats, uint64_t tic
         JGPT_CUDA_TRY(cudaMalloc(&p->d_tickets, sizeof(int) * tickets));
         JGPT_CUDA_TRY(cudaMemsetAsync(p->d_tickets, 0, sizeof(int) * tickets, p->ctx->stream));
         p->n_tickets = tickets;
+        p->generation += (uint64_t)1 << 32;
     }
     return JGPT_OK;
 }
@@ -255,6 +259,20 @@ static void free_seq_blocks(Pool *p, SeqState &s, std::vector<int> *freed) {
     }
     s.blocks.clear();
     s.len = 0;
+}
+
+// Frees everything a pool owns (also a partly built one: null pointers are skipped by the runtime).
+static void release_pool(Pool *p) {
+    cudaFree(p->kv), cudaFree(p->d_table), cudaFree(p->d_rope), cudaFree(p->d_partials), cudaFree(p->d_tickets);
+    cudaFree(p->d_evict_list), cudaFree(p->d_stage_f), cudaFree(p->d_stage_i);
+    cudaFree(p->d_prefill_desc);
+    cudaFree(p->d_item_counters);
+    if (p->s_in) {
+        cudaStreamDestroy(p->s_in), cudaStreamDestroy(p->s_out), cudaEventDestroy(p->ev_start);
+        for (int g = 0; g < 4; g++) cudaEventDestroy(p->ev_in[g]), cudaEventDestroy(p->ev_done[g]);
+    }
+    cudaFreeHost(p->h_stage_f), cudaFreeHost(p->h_stage_i);
+    delete p;
 }
 
 }  // namespace jgpt
@@ -306,26 +324,38 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
         return fail(JGPT_ERR_OUT_OF_MEMORY, "KV pool of %llu bytes does not fit: %s", (unsigned long long)bytes,
                     cudaGetErrorString(e));
     }
-    JGPT_CUDA_TRY(cudaMemsetAsync(p->kv, 0, p->kv_bytes, c->stream));
-    const size_t tn = (size_t)max_seqs * max_blocks_per_seq;
-    JGPT_CUDA_TRY(cudaMalloc(&p->d_table, sizeof(int) * tn));
-    JGPT_CUDA_TRY(cudaMemsetAsync(p->d_table, 0xFF, sizeof(int) * tn, c->stream));
-    JGPT_CUDA_TRY(cudaMalloc(&p->d_item_counters, sizeof(int) * 2));
-    JGPT_CUDA_TRY(cudaMemsetAsync(p->d_item_counters, 0, sizeof(int) * 2, c->stream));
-    // RoPE table on the host with the reference's formula (rope_4d_kernel,
-    // src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:1151-1154): theta = (float)p / powf(base, 2j/dhead).
-    {
-        const int half = dhead / 2;
-        std::vector<float2> tab((size_t)max_positions * half);
-        for (int pos = 0; pos < max_positions; pos++)
-            for (int j = 0; j < half; j++) {
-                const float theta = (float)pos / powf(rope_base, (2.f * (float)j) / (float)dhead);
-                tab[(size_t)pos * half + j] = make_float2(cosf(theta), sinf(theta));
-            }
-        JGPT_CUDA_TRY(cudaMalloc(&p->d_rope, sizeof(float2) * tab.size()));
-        JGPT_CUDA_TRY(cudaMemcpyAsync(p->d_rope, tab.data(), sizeof(float2) * tab.size(), cudaMemcpyHostToDevice, c->stream));
-        JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    // from here on a failure must give back what was already taken
+    const int32_t rc_build = [&]() -> int32_t {
+        JGPT_CUDA_TRY(cudaMemsetAsync(p->kv, 0, p->kv_bytes, c->stream));
+        const size_t tn = (size_t)max_seqs * max_blocks_per_seq;
+        JGPT_CUDA_TRY(cudaMalloc(&p->d_table, sizeof(int) * tn));
+        JGPT_CUDA_TRY(cudaMemsetAsync(p->d_table, 0xFF, sizeof(int) * tn, c->stream));
+        JGPT_CUDA_TRY(cudaMalloc(&p->d_item_counters, sizeof(int) * 2));
+        JGPT_CUDA_TRY(cudaMemsetAsync(p->d_item_counters, 0, sizeof(int) * 2, c->stream));
+        // RoPE table on the host with the reference's formula (rope_4d_kernel,
+        // src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:1151-1154): theta = (float)p / powf(base, 2j/dhead).
+        {
+            const int half = dhead / 2;
+            std::vector<float2> tab((size_t)max_positions * half);
+            for (int pos = 0; pos < max_positions; pos++)
+                for (int j = 0; j < half; j++) {
+                    const float theta = (float)pos / powf(rope_base, (2.f * (float)j) / (float)dhead);
+                    tab[(size_t)pos * half + j] = make_float2(cosf(theta), sinf(theta));
+                }
+            JGPT_CUDA_TRY(cudaMalloc(&p->d_rope, sizeof(float2) * tab.size()));
+            JGPT_CUDA_TRY(cudaMemcpyAsync(p->d_rope, tab.data(), sizeof(float2) * tab.size(), cudaMemcpyHostToDevice, c->stream));
+            JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
+        }
+        return JGPT_OK;
+    }();
+    if (rc_build) {
+        const std::string keep = last_error_ref();
+        release_pool(p);
+        last_error_ref() = keep;
+        return rc_build;
     }
+    static std::atomic<uint64_t> next_generation{1};
+    p->generation = next_generation.fetch_add(1);
     p->free_list.resize((size_t)n_blocks);
     for (int i = 0; i < n_blocks; i++) p->free_list[(size_t)i] = n_blocks - 1 - i;  // block 0 is handed out first
     p->seqs.resize((size_t)max_seqs);
@@ -337,16 +367,7 @@ int32_t jgpt_kvpool_destroy(jgpt_kvpool h) {
     GET_POOL(p, h);
     cudaStreamSynchronize(p->ctx->stream);
     pool_registry().remove(p);
-    cudaFree(p->kv), cudaFree(p->d_table), cudaFree(p->d_rope), cudaFree(p->d_partials), cudaFree(p->d_tickets);
-    cudaFree(p->d_evict_list), cudaFree(p->d_stage_f), cudaFree(p->d_stage_i);
-    cudaFree(p->d_prefill_desc);
-    cudaFree(p->d_item_counters);
-    if (p->s_in) {
-        cudaStreamDestroy(p->s_in), cudaStreamDestroy(p->s_out), cudaEventDestroy(p->ev_start);
-        for (int g = 0; g < 4; g++) cudaEventDestroy(p->ev_in[g]), cudaEventDestroy(p->ev_done[g]);
-    }
-    cudaFreeHost(p->h_stage_f), cudaFreeHost(p->h_stage_i);
-    delete p;
+    release_pool(p);
     return JGPT_OK;
 }
 
@@ -361,6 +382,13 @@ int32_t jgpt_kvpool_storage(jgpt_kvpool h, void **dev_out, uint64_t *bytes_out) 
     GET_POOL(p, h);
     if (dev_out) *dev_out = p->kv;
     if (bytes_out) *bytes_out = p->kv_bytes;
+    return JGPT_OK;
+}
+
+int32_t jgpt_kvpool_table_device(jgpt_kvpool h, int32_t **dev_out, int32_t *row_stride_out) {
+    GET_POOL(p, h);
+    if (dev_out) *dev_out = p->d_table;
+    if (row_stride_out) *row_stride_out = p->max_blocks_per_seq;
     return JGPT_OK;
 }
 

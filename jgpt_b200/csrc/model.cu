@@ -52,7 +52,7 @@ struct Model {
     // is the key.  A key seen for the second time is captured, from then on replayed.
     struct DecodeGraph {
         const void *key[8] = {};
-        int n = 0, len_bucket = 0, geom[3] = {};
+        int n = 0, len_bucket = 0, geom[5] = {};
         float temperature = 0.f;  // 0: greedy argmax
         int top_k = 0;
         cudaGraphExec_t exec = nullptr;
@@ -1374,7 +1374,11 @@ int32_t jgpt_forward_prefill_batch(jgpt_model h, jgpt_kvpool poolh, const int32_
         JGPT_CUDA_TRY(cudaMemcpyAsync(last_logits_host, src, sizeof(float) * (size_t)nrow * m->vocab, cudaMemcpyDeviceToHost, st));
     }
     JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)out_rows, cudaMemcpyDeviceToHost, st));
+    JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+    // a kernel of the step recorded a failed self-check: no tokens, no length change
+    rc = status_check_after_sync(m->ctx, p, "jgpt_forward_prefill");
+    if (rc) return rc;
     if (next_tokens_host)
         for (int i = 0; i < n; i++) next_tokens_host[i] = all_logits_host ? m->h_next[rows - 1] : m->h_next[i];
     for (int i = 0; i < n; i++) {  // cache.setLength(seqLen)
@@ -1449,15 +1453,23 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         r2 = lm_head(m, n, 0, spec);
         if (r2) return r2;
         JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));  // part of the replayed graph too
         return JGPT_OK;
     };
     Model::DecodeGraph *slot = nullptr;
     if (m->decode_graph_enabled && small_mode(m, n)) {
-        Model::DecodeGraph want;
-        const void *key[8] = {p, p->kv, p->d_table, p->d_partials, p->d_tickets, m->logits, m->d_idx, m->d_samp};
-        for (int i = 0; i < 8; i++) want.key[i] = key[i];
-        want.temperature = sampled ? spec.temperature : 0.f, want.top_k = sampled ? spec.top_k : 0;
-        want.n = n, want.len_bucket = len_bucket, want.geom[0] = p->n_blocks, want.geom[1] = p->max_blocks_per_seq, want.geom[2] = p->heads;
+        // Key: the pool object and its generation (unique per pool, bumped whenever a device buffer the kernels are
+        // handed is reallocated), every other buffer address baked into the captured launches, and the pool geometry.
+        auto make_key = [&]() {
+            Model::DecodeGraph k;
+            const void *key[8] = {p, reinterpret_cast<const void *>(p->generation), p->kv, p->d_table, p->d_rope, m->logits, m->d_idx, m->d_samp};
+            for (int i = 0; i < 8; i++) k.key[i] = key[i];
+            k.temperature = sampled ? spec.temperature : 0.f, k.top_k = sampled ? spec.top_k : 0;
+            k.n = n, k.len_bucket = len_bucket, k.geom[0] = p->n_blocks, k.geom[1] = p->max_blocks_per_seq, k.geom[2] = p->heads;
+            k.geom[3] = p->max_seqs, k.geom[4] = p->max_positions;
+            return k;
+        };
+        Model::DecodeGraph want = make_key();
         for (auto &g : m->decode_graphs)
             if (g.n == want.n && g.len_bucket == want.len_bucket && g.temperature == want.temperature && g.top_k == want.top_k &&
                 memcmp(g.key, want.key, sizeof(want.key)) == 0 &&
@@ -1471,9 +1483,10 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
                 if (m->decode_graphs[oldest].exec) cudaGraphExecDestroy(m->decode_graphs[oldest].exec);
                 m->decode_graphs.erase(m->decode_graphs.begin() + (long)oldest);
             }
+            rc = enqueue();
+            want = make_key();  // after the eager run: it may have grown the pool's split scratch (new generation)
             want.last_use = ++m->decode_graph_clock;
             m->decode_graphs.push_back(want);
-            rc = enqueue();
         } else {
             slot->last_use = ++m->decode_graph_clock;
             if (!slot->exec && !slot->failed) {  // second time: capture
@@ -1504,6 +1517,9 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
     if (logits_host)
         JGPT_CUDA_TRY(cudaMemcpyAsync(logits_host, m->logits, sizeof(float) * (size_t)n * m->vocab, cudaMemcpyDeviceToHost, st));
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+    // a kernel of the step recorded a failed self-check: no tokens, no length change
+    rc = status_check_after_sync(m->ctx, p, "jgpt_forward_decode");
+    if (rc) return rc;
     if (next_tokens_host)
         for (int i = 0; i < n; i++) next_tokens_host[i] = m->h_next[i];
     for (int i = 0; i < n; i++) {  // cache.setLength(cacheLenBefore + 1)
@@ -1530,6 +1546,13 @@ int32_t jgpt_forward_decode_sample(jgpt_model h, jgpt_kvpool poolh, const int32_
     spec.temperature = temperature, spec.top_k = top_k;
     return forward_decode_impl(h, poolh, seq_ids_host, ids_host, cache_len_before_host, rope_pos_host, n, nullptr, next_tokens_host,
                                spec, u01_host);
+}
+
+int32_t jgpt_model_next_tokens_device(jgpt_model h, const int32_t **dev_out) {
+    GET_MODEL(m, h);
+    JGPT_REQUIRE(dev_out, JGPT_ERR_INVALID_ARGUMENT, "null output");
+    *dev_out = m->d_next;
+    return JGPT_OK;
 }
 
 // sampleNextToken on host logits (src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:208-286):

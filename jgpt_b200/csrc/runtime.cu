@@ -29,6 +29,29 @@ Registry<Pool> &pool_registry() {
     return r;
 }
 
+cudaError_t status_enqueue_read(Ctx *c) {
+    return cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
+}
+
+// To be called after the stream has been synchronised behind status_enqueue_read.  A non-zero word means a kernel of
+// the step recorded a self-check failure (its results are not to be trusted): the word is cleared, the pool's split-K
+// arrival counters and work-queue counters are put back to zero (an aborted launch can leave them half counted, which
+// would make every later launch on the pool merge too early or never), and the call fails.
+int32_t status_check_after_sync(Ctx *c, Pool *p, const char *what) {
+    const int st = *c->h_status;
+    if (st == 0) return JGPT_OK;
+    *c->h_status = 0;
+    cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
+    if (p) {
+        if (p->d_tickets && p->n_tickets) cudaMemsetAsync(p->d_tickets, 0, sizeof(int) * p->n_tickets, c->stream);
+        if (p->d_item_counters) cudaMemsetAsync(p->d_item_counters, 0, sizeof(int) * 2, c->stream);
+    }
+    return fail(JGPT_ERR_DEVICE_CHECK, "%s: device self-check failed: status=0x%x%s%s%s%s%s", what, st,
+                (st & DEV_STATUS_BAD_BLOCK) ? " bad-block-id" : "", (st & DEV_STATUS_BAD_POSITION) ? " bad-position" : "",
+                (st & DEV_STATUS_BAD_SEQ) ? " bad-seq-id" : "", (st & DEV_STATUS_WAIT_TIMEOUT) ? " wait-timeout" : "",
+                (st & DEV_STATUS_LEN_OVER_BOUND) ? " len-over-bound" : "");
+}
+
 int env_int(const char *name, int dflt) {
     const char *v = getenv(name);
     if (!v || !*v) return dflt;
@@ -103,17 +126,21 @@ int32_t jgpt_sync(jgpt_ctx h) {
     Ctx *c = ctx_registry().get(h);
     JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
     JGPT_CUDA_TRY(make_current(c));
-    JGPT_CUDA_TRY(cudaMemcpyAsync(c->h_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    JGPT_CUDA_TRY(status_enqueue_read(c));
     JGPT_CUDA_TRY(cudaStreamSynchronize(c->stream));
-    if (*c->h_status != 0) {
-        const int st = *c->h_status;
-        cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream);
-        return fail(JGPT_ERR_DEVICE_CHECK,
-                    "device self-check failed: status=0x%x%s%s%s%s%s", st, (st & DEV_STATUS_BAD_BLOCK) ? " bad-block-id" : "",
-                    (st & DEV_STATUS_BAD_POSITION) ? " bad-position" : "", (st & DEV_STATUS_BAD_SEQ) ? " bad-seq-id" : "",
-                    (st & DEV_STATUS_WAIT_TIMEOUT) ? " wait-timeout" : "",
-                    (st & DEV_STATUS_LEN_OVER_BOUND) ? " len-over-bound" : "");
-    }
+    return status_check_after_sync(c, nullptr, "jgpt_sync");
+}
+
+// TensorOpsGPU.getGpuMemoryAllocated0 / getGpuMemoryReserved0 (src/main/cpp/jgpt_cuda_jni_ops_graph.inl:471-491):
+// both are cudaMemGetInfo of the current device.
+int32_t jgpt_mem_info(jgpt_ctx h, uint64_t *free_bytes_out, uint64_t *total_bytes_out) {
+    Ctx *c = ctx_registry().get(h);
+    JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");
+    JGPT_CUDA_TRY(make_current(c));
+    size_t f = 0, t = 0;
+    JGPT_CUDA_TRY(cudaMemGetInfo(&f, &t));
+    if (free_bytes_out) *free_bytes_out = f;
+    if (total_bytes_out) *total_bytes_out = t;
     return JGPT_OK;
 }
 

@@ -123,6 +123,10 @@ int32_t jgpt_sched_submit(uint64_t h, const int32_t *prompt_host, int32_t S, int
     JGPT_REQUIRE(S + max_new - 1 <= s->max_seq && S + max_new <= s->p->max_blocks_per_seq * kBlockTokens + 1,
                  JGPT_ERR_INVALID_ARGUMENT, "prompt %d + %d new tokens exceed the context of %d", S, max_new, s->max_seq);
     JGPT_REQUIRE(S <= s->max_rows, JGPT_ERR_INVALID_ARGUMENT, "prompt of %d rows exceeds the per-call workspace of %d", S, s->max_rows);
+    // a reservation larger than the whole pool could never be admitted and would block the queue for ever
+    const int need_blocks = (S + max_new - 1 + kBlockTokens - 1) / kBlockTokens;
+    JGPT_REQUIRE(need_blocks <= s->p->n_blocks, JGPT_ERR_INVALID_ARGUMENT,
+                 "prompt %d + %d new tokens need %d blocks; the pool has %d", S, max_new, need_blocks, s->p->n_blocks);
     Request r;
     r.prompt.assign(prompt_host, prompt_host + S);
     r.max_new = max_new;
@@ -137,6 +141,10 @@ int32_t jgpt_sched_step(uint64_t h, int32_t *pairs_out, int32_t cap_pairs, int32
                         int32_t *n_waiting_out) {
     GET_SCHED(s, h);
     Pool *p = s->p;
+    // a step samples at most one token per running request; check the buffer before any state changes
+    JGPT_REQUIRE(!pairs_out || cap_pairs >= std::min(s->max_running, (int)(s->running.size() + s->waiting.size())),
+                 JGPT_ERR_INVALID_ARGUMENT, "pairs buffer holds %d; a step can produce up to %d", cap_pairs,
+                 std::min(s->max_running, (int)(s->running.size() + s->waiting.size())));
     std::vector<int> produced;  // flat pairs
     // the requests that were running before this step decode in phase 3
     const std::vector<int> decoding = s->running;
@@ -150,7 +158,15 @@ int32_t jgpt_sched_step(uint64_t h, int32_t *pairs_out, int32_t cap_pairs, int32
         // blocks for every position the request can ever occupy: prompt + (max_new - 1) appended tokens
         const int need = (S + r.max_new - 1 + kBlockTokens - 1) / kBlockTokens;
         int32_t rc = make_room(s, need, true);
-        if (rc == JGPT_ERR_POOL_EXHAUSTED) break;  // head of line waits; nobody overtakes
+        if (rc == JGPT_ERR_POOL_EXHAUSTED) {
+            // head of line waits for running requests to finish; nobody overtakes.  With nothing running there is
+            // nothing to wait for (the blocks are held by sequences the scheduler does not own): report it instead
+            // of returning OK for ever.
+            if (s->running.empty())
+                return fail(JGPT_ERR_POOL_EXHAUSTED, "request %d needs %d blocks: %d free, nothing running and nothing evictable", rid,
+                            need, (int)p->free_list.size());
+            break;
+        }
         if (rc) return rc;
         int32_t seq = -1;
         rc = jgpt_seq_alloc(s->pool, &seq);

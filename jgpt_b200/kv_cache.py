@@ -49,6 +49,12 @@ class KvPool:
         B.check(self._lib.jgpt_kvpool_storage(self.handle, C.byref(p), C.byref(n)))
         return p.value, n.value
 
+    def table_device(self):
+        """(device address, row stride) of the block-table mirror, int32 [max_seqs][row stride]."""
+        p, n = C.c_void_p(), C.c_int32()
+        B.check(self._lib.jgpt_kvpool_table_device(self.handle, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
     def seq_alloc(self) -> int:
         s = C.c_int32()
         B.check(self._lib.jgpt_seq_alloc(self.handle, C.byref(s)))

@@ -26,6 +26,12 @@ class Context:
         """``TensorOpsGPU.synchronizeStream``; raises if a kernel recorded a failed self-check."""
         B.check(self._lib.jgpt_sync(self.handle))
 
+    def mem_info(self):
+        """(free bytes, total bytes) of the context's device."""
+        f, t = C.c_uint64(), C.c_uint64()
+        B.check(self._lib.jgpt_mem_info(self.handle, C.byref(f), C.byref(t)))
+        return f.value, t.value
+
     @property
     def stream(self) -> int:
         p = C.c_void_p()

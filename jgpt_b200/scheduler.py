@@ -1,6 +1,7 @@
 """Continuous-batching scheduler (host mirror of the ``jgpt_sched_*`` entry points) and the multi-GPU
 sharding helpers: requests are dealt round-robin to the ranks (``request % world``), every rank runs its own
-scheduler on its own GPU and pool, and only the sampled token ids are gathered."""
+scheduler on its own GPU and pool, and only the sampled token ids are gathered (``TokenGather``: NCCL inside the
+library, no PyTorch)."""
 from __future__ import annotations
 
 import ctypes as C
@@ -74,120 +75,129 @@ def shard_requests(n_requests: int, world: int, rank: int):
     return list(range(rank, n_requests, world))
 
 
-def gather_step_tokens(local_pairs, world: int, rank: int, max_pairs: int, dist=None, device=None):
-    """All-gathers one step's (global request id, token) pairs.  Every rank contributes a fixed-size int32
-    buffer (count, then pairs, padded with -1) so that the collective has the same shape on every rank.
-    Returns the pairs of all ranks ordered by (rank, local order).  ``dist`` is ``torch.distributed`` (NCCL on
-    GPUs, gloo in CPU tests); with world == 1 nothing is communicated."""
-    local_pairs = np.asarray(local_pairs, np.int32).reshape(-1, 2)
-    if local_pairs.shape[0] > max_pairs:
-        raise ValueError(f"{local_pairs.shape[0]} pairs exceed the gather buffer of {max_pairs}")
-    if world == 1 or dist is None:
-        return [tuple(int(x) for x in p) for p in local_pairs]
-    import torch
+def rendezvous_unique_id(rank: int, world: int, key: str, directory: str | None = None, timeout_s: float = 120.0) -> bytes | None:
+    """Hands rank 0's NCCL unique id to the other ranks of one box through a file: a launcher that has no store of
+    its own needs nothing else.  ``key`` must be the same on all ranks of a job and differ between jobs (e.g. the
+    launcher's port or run id).  Returns None for a single rank."""
+    import os
+    import time
 
-    buf = np.full(1 + 2 * max_pairs, -1, np.int32)
-    buf[0] = local_pairs.shape[0]
-    buf[1:1 + local_pairs.size] = local_pairs.reshape(-1)
-    send = torch.from_numpy(buf)
-    if device is not None:
-        send = send.to(device)
-    recv = [torch.empty_like(send) for _ in range(world)]
-    dist.all_gather(recv, send)
+    if world <= 1:
+        return None
+    directory = directory or os.environ.get("JGPT_B200_RDZV_DIR", "/tmp")
+    path = os.path.join(directory, f"jgpt_b200_rdzv_{key}")
+    if rank == 0:
+        uid = TokenGather.unique_id()
+        tmp = f"{path}.{os.getpid()}.tmp"
+        with open(tmp, "wb") as f:
+            f.write(uid)
+        os.replace(tmp, path)  # appears atomically
+        return uid
+    deadline = time.time() + timeout_s
+    while time.time() < deadline:
+        try:
+            with open(path, "rb") as f:
+                uid = f.read()
+            if len(uid) == 128:
+                return uid
+        except FileNotFoundError:
+            pass
+        time.sleep(0.01)
+    raise TimeoutError(f"rank {rank}: no unique id at {path} after {timeout_s} s")
+
+
+def rendezvous_cleanup(key: str, directory: str | None = None):
+    """Removes the rendezvous file of ``key`` (rank 0, once every rank has joined the communicator)."""
+    import os
+
+    try:
+        os.remove(os.path.join(directory or os.environ.get("JGPT_B200_RDZV_DIR", "/tmp"), f"jgpt_b200_rdzv_{key}"))
+    except OSError:
+        pass
+
+
+def pack_pairs(pairs, done: bool = False):
+    """(request id, token) pairs of one step as the flat int32 words a rank contributes to the gather.  A rank
+    that has nothing left to do appends the sentinel pair (-1, 1): when every rank has sent it the job is over."""
+    a = np.asarray(pairs, np.int32).reshape(-1, 2)
+    if done:
+        a = np.concatenate([a, np.array([[-1, 1]], np.int32)])
+    return np.ascontiguousarray(a.reshape(-1))
+
+
+def unpack_pairs(words, counts):
+    """Inverse of ``pack_pairs`` over the gathered rows: the pairs of all ranks ordered by (rank, local order)."""
     out = []
-    for r in range(world):
-        a = recv[r].cpu().numpy()
-        out.extend((int(a[1 + 2 * i]), int(a[2 + 2 * i])) for i in range(int(a[0])))
+    for r, c in enumerate(counts):
+        w = words[r]
+        out.extend((int(w[2 * i]), int(w[2 * i + 1])) for i in range(int(c) // 2))
     return out
 
 
-class StepTokenGather:
-    """The same all-gather, issued asynchronously and read ``depth`` steps later: the collective of step t overlaps
-    the decode steps t+1 .. t+depth of every rank, and ranks may drift up to ``depth`` steps apart instead of meeting
-    after every step (one rank's prefill no longer stalls the others' decode steps).  Results come back in step
-    order, each the pairs of all ranks ordered by (rank, local order), exactly what ``gather_step_tokens`` returns.
+class TokenGather:
+    """All-gather of every rank's sampled token ids over NCCL, inside the library (``jgpt_comm_*``).
 
-    Every rank must ``submit`` once per step and stop by the same rule on the gathered results (e.g. "all ranks
-    reported done"), then ``drain``; since results are read in the same order everywhere, all ranks then have issued
-    the same number of collectives."""
+    One per rank.  ``submit`` hands in this step's pairs and returns at once; the collective runs on a stream of
+    its own and its result is read up to ``depth`` steps later (``ready`` says when one has to be read), so the
+    ranks never meet after every step.  Results come back in step order, identical on every rank.  Every rank
+    must submit once per step and stop by the same rule on the gathered results, then ``drain``.
 
-    def __init__(self, world: int, rank: int, max_pairs: int, dist=None, device=None, depth: int = 4):
-        self.world, self.rank, self.max_pairs, self.dist, self.device = world, rank, max_pairs, dist, device
-        self.depth = max(0, int(depth))
-        self._inflight = []  # (work or None, slot or None, pairs or None)
-        self._slots, self._free = [], []
-        if world > 1 and dist is not None and device is not None:
-            # a ring of page-locked staging buffers and device tensors: a step's submit is one small copy and one launch
-            import torch
+    ``unique_id`` is the 128-byte rendezvous id made by rank 0 (``TokenGather.unique_id()``) and handed to the
+    other ranks by the launcher; with ``world == 1`` nothing is communicated and no NCCL is needed."""
 
-            n = 1 + 2 * max_pairs
-            for _ in range(self.depth + 2):
-                self._slots.append({
-                    "send_host": torch.empty(n, dtype=torch.int32, pin_memory=True),
-                    "send_dev": torch.empty(n, dtype=torch.int32, device=device),
-                    "recv_dev": torch.empty(world * n, dtype=torch.int32, device=device),
-                    "recv_host": torch.empty(world * n, dtype=torch.int32, pin_memory=True),
-                })
-            self._free = list(range(len(self._slots)))
+    def __init__(self, ctx, world: int, rank: int, max_pairs: int, unique_id: bytes | None = None, depth: int = 4,
+                 timeout_ms: int = 30000):
+        self._lib, self.ctx = ctx._lib, ctx
+        self.world, self.rank, self.max_words, self.depth, self.timeout_ms = world, rank, 2 * (max_pairs + 1), depth, timeout_ms
+        h = C.c_uint64()
+        B.check(self._lib.jgpt_comm_create(ctx.handle, unique_id, world, rank, self.max_words, depth, timeout_ms, C.byref(h)))
+        self.handle = h.value
 
-    def submit(self, local_pairs):
-        local_pairs = np.asarray(local_pairs, np.int32).reshape(-1, 2)
-        if local_pairs.shape[0] > self.max_pairs:
-            raise ValueError(f"{local_pairs.shape[0]} pairs exceed the gather buffer of {self.max_pairs}")
-        if self.world == 1 or self.dist is None:
-            self._inflight.append((None, None, [tuple(int(x) for x in p) for p in local_pairs]))
-            return
-        import torch
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        B.check(B.load().jgpt_comm_unique_id(buf, 128))
+        return buf.raw
 
-        if self._slots:
-            slot_id = self._free.pop(0)
-            slot = self._slots[slot_id]
-            buf = slot["send_host"].numpy()
-            buf[:] = -1
-            buf[0] = local_pairs.shape[0]
-            buf[1:1 + local_pairs.size] = local_pairs.reshape(-1)
-            slot["send_dev"].copy_(slot["send_host"], non_blocking=True)
-            work = self.dist.all_gather_into_tensor(slot["recv_dev"], slot["send_dev"], async_op=True)
-            self._inflight.append((work, slot_id, None))
-            return
-        buf = np.full(1 + 2 * self.max_pairs, -1, np.int32)
-        buf[0] = local_pairs.shape[0]
-        buf[1:1 + local_pairs.size] = local_pairs.reshape(-1)
-        send = torch.from_numpy(buf)
-        recv = [torch.empty_like(send) for _ in range(self.world)]
-        work = self.dist.all_gather(recv, send, async_op=True)
-        self._inflight.append((work, None, recv))
+    def submit(self, pairs, done: bool = False):
+        self.submit_words(pack_pairs(pairs, done))
+
+    def submit_words(self, words):
+        w = np.ascontiguousarray(words, np.int32).reshape(-1)
+        B.check(self._lib.jgpt_comm_submit(self.handle, w.ctypes.data, w.size))
+
+    def submit_device(self, words_dev, n_words: int):
+        """Gathers n_words int32 words that work already enqueued on the context's stream leaves at ``words_dev``."""
+        B.check(self._lib.jgpt_comm_submit_device(self.handle, words_dev, n_words))
+
+    def in_flight(self) -> int:
+        n, m = C.c_int32(), C.c_int32()
+        B.check(self._lib.jgpt_comm_in_flight(self.handle, C.byref(n), C.byref(m)))
+        return n.value
 
     def ready(self) -> bool:
-        """True when a result must be read now to keep at most ``depth`` collectives in flight."""
-        return len(self._inflight) > self.depth
+        n, m = C.c_int32(), C.c_int32()
+        B.check(self._lib.jgpt_comm_in_flight(self.handle, C.byref(n), C.byref(m)))
+        return bool(m.value)
 
-    def pop(self):
-        """Waits for the oldest step's collective and returns its pairs."""
-        work, slot_id, payload = self._inflight.pop(0)
-        if work is None:
-            return payload
-        work.wait()
-        n = 1 + 2 * self.max_pairs
-        if slot_id is not None:
-            import torch
+    def pop_words(self, timeout_ms: int | None = None):
+        """(words [world, max_words], counts [world]) of the oldest step; TimeoutError leaves it in flight."""
+        words = np.empty((self.world, self.max_words), np.int32)
+        counts = np.empty(self.world, np.int32)
+        B.check(self._lib.jgpt_comm_pop(self.handle, words.ctypes.data, counts.ctypes.data,
+                                        self.timeout_ms if timeout_ms is None else timeout_ms))
+        return words, counts
 
-            slot = self._slots[slot_id]
-            slot["recv_host"].copy_(slot["recv_dev"], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            flat = slot["recv_host"].numpy()
-            rows = [flat[r * n:(r + 1) * n] for r in range(self.world)]
-            self._free.append(slot_id)
-        else:
-            rows = [t.cpu().numpy() for t in payload]
-        out = []
-        for a in rows:
-            out.extend((int(a[1 + 2 * i]), int(a[2 + 2 * i])) for i in range(int(a[0])))
-        return out
+    def pop(self, timeout_ms: int | None = None):
+        return unpack_pairs(*self.pop_words(timeout_ms))
 
     def drain(self):
-        """Results of every step still in flight, oldest first."""
         out = []
-        while self._inflight:
+        while self.in_flight():
             out.append(self.pop())
         return out
+
+    def close(self):
+        if self.handle:
+            self._lib.jgpt_comm_destroy(self.handle)
+            self.handle = 0

@@ -11,7 +11,7 @@ import numpy as np
 from .kv_cache import KvPool
 from .model import GPTModel
 from .runtime import Event
-from .scheduler import ContinuousBatcher, StepTokenGather, gather_step_tokens, shard_requests
+from .scheduler import ContinuousBatcher, TokenGather, shard_requests
 
 VOCAB, CTX, D_MODEL, HEADS, LAYERS, D_FF, EPS = 8000, 1024, 384, 24, 12, 768, 1e-5
 DHEAD = D_MODEL // HEADS
@@ -139,7 +139,7 @@ def run_prefill(ctx, batch=32, seq_len=1024, repeats=3):
         pool.close(), model.close()
 
 
-def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool_fraction=0.6, max_steps=100_000, gather_depth=4):
+def run_contbatch(ctx, rank, world, unique_id=None, n_requests=256, pool_fraction=0.6, max_steps=100_000, gather_depth=4):
     """256 requests (seed 2): prompt U[32,512], target U[64,1024] new tokens clipped to the 1024 context; pool sized
     at 60 % of the rank's total block demand; requests dealt round-robin to the ranks; sampled ids all-gathered."""
     rng = np.random.default_rng(2)
@@ -158,7 +158,7 @@ def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool
             sched.submit(prompts[i], int(t_len[i]))
         ctx.synchronize()
         total_tokens, steps, done, all_done = 0, 0, False, False
-        gather = StepTokenGather(world, rank, max_pairs=-(-n_requests // world) + 2, dist=dist, device=device, depth=gather_depth)
+        gather = TokenGather(ctx, world, rank, max_pairs=-(-n_requests // world) + 2, unique_id=unique_id, depth=gather_depth)
 
         def account(allp):
             nonlocal total_tokens, all_done
@@ -176,7 +176,7 @@ def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool
                 pairs = np.zeros((0, 2), np.int32)
             tb = time.perf_counter()
             # the ids of step t are all-gathered while steps t+1 .. t+depth run; a finished rank keeps reporting (-1, 1)
-            gather.submit([(mine[int(r)], int(t)) for r, t in pairs] + ([(-1, 1)] if done else []))
+            gather.submit([(mine[int(r)], int(t)) for r, t in pairs], done=done)
             tc = time.perf_counter()
             steps += 1
             while gather.ready() and not all_done:
@@ -188,11 +188,12 @@ def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool
         for allp in gather.drain():
             account(allp)
         el = time.perf_counter() - t0
+        gather.close()
         ev = sched.events()
         return {
             "workload": f"continuous batching: {n_requests} requests (seed 2), prompt U[32,512], target U[64,1024] clipped to the "
-                        f"1024 context, KV pool {pool_fraction:.0%} of demand, round-robin over {world} GPU(s), token ids all-gathered "
-                        f"(asynchronously, read {gather_depth} steps later)",
+                        f"1024 context, KV pool {pool_fraction:.0%} of demand, round-robin over {world} GPU(s), token ids all-gathered by the library's "
+                        f"NCCL communicator (asynchronously, read {gather_depth} steps later)",
             "generated_tokens": total_tokens, "steps": steps, "seconds": el, "tokens_per_s": total_tokens / el,
             "seconds_in": {"scheduler_steps": t_step, "gather_submit": t_submit, "gather_read": t_pop},
             "pool_blocks_rank0": n_blocks, "demand_blocks_rank0": demand, "evictions_rank0": sum(1 for e in ev if e[0] == 2),
@@ -200,6 +201,103 @@ def run_contbatch(ctx, rank, world, dist=None, device=None, n_requests=256, pool
         }
     finally:
         sched.close(), pool.close(), model.close()
+
+
+def run_kvstore(ctx, batch=64, ctx_len=1024, n_blocks=4096, repeats=7):
+    """The three K/V store kernels on their own at the microbenchmark's size (12 layers x 24 heads x d_head 16, 64
+    sequences x 1024 tokens, 4096-block pool, seeded random block table): append of all 65,536 tokens of one layer
+    (RoPE + fp16 conversion), gather of the 64 sequences of one layer into contiguous fp32 planes, and the eviction
+    scrub of the whole pool.  CUDA events on the library's stream, median of `repeats`; algorithmic bytes per unit:
+    append = per token H*DH*(4*2 read + 2*2 written) + 12 index bytes; gather = per (head, position) DH*(2*2 read +
+    4*2 written); scrub = per freed block layers*H*64*DH bytes written."""
+    import json
+    import os
+    import statistics
+
+    try:
+        peak = float(json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")))["hbm_gbs"])
+        kind = "of measured"
+    except Exception:
+        peak, kind = 6650.0, "of fallback"
+    pool = KvPool(ctx, LAYERS, HEADS, DHEAD, n_blocks, batch, ctx_len // 16, max_positions=ctx_len)
+    rng = np.random.default_rng(1234)
+    perm = rng.permutation(n_blocks).astype(np.int32).reshape(batch, ctx_len // 16)
+    try:
+        seqs = []
+        for i in range(batch):
+            s = pool.seq_alloc()
+            pool.set_block_table(s, perm[i])
+            pool.set_length(s, ctx_len)
+            seqs.append(s)
+        tot = batch * ctx_len
+        k = ctx.from_host(rng.standard_normal((tot, D_MODEL), dtype=np.float32))
+        v = ctx.from_host(rng.standard_normal((tot, D_MODEL), dtype=np.float32))
+        sid = ctx.from_host(np.repeat(np.asarray(seqs, np.int32), ctx_len))
+        pos = ctx.from_host(np.tile(np.arange(ctx_len, dtype=np.int32), batch))
+        e0, e1 = Event(ctx), Event(ctx)
+
+        def timed(fn, reps=repeats):
+            fn()
+            ctx.synchronize()
+            ts = []
+            for _ in range(reps):
+                e0.record()
+                fn()
+                e1.record()
+                ts.append(e0.elapsed_ms(e1))
+            return statistics.median(ts)
+
+        out = {}
+        # append: a different layer each repeat, so the written lines are not the ones just written (1.2 GB pool > L2)
+        layer_it = iter(range(10 ** 9))
+        ms = timed(lambda: pool.append(next(layer_it) % LAYERS, k, v, sid, pos, pos, tot))
+        alg = tot * (HEADS * DHEAD * (4 * 2 + 2 * 2) + 12)
+        out["kv_append_kernel"] = {"ms": ms, "algorithmic_bytes": alg, "GBps": alg / ms / 1e6, "frac": alg / ms / 1e6 / peak,
+                                   "unit": f"{tot} tokens of one layer per launch"}
+        # gather: 64 launches (one per sequence, the reference's getK/getV granularity), timed as one region
+        kd = [ctx.alloc((HEADS, ctx_len, DHEAD)) for _ in range(2)]
+        gl = iter(range(10 ** 9))
+
+        def gather_all():
+            layer = next(gl) % LAYERS
+            for s in seqs:
+                pool.gather(layer, s, ctx_len, ctx_len, kd[0], kd[1])
+
+        ms = timed(gather_all)
+        alg = batch * HEADS * ctx_len * DHEAD * (2 * 2 + 4 * 2)
+        out["kv_gather_kernel"] = {"ms": ms, "algorithmic_bytes": alg, "GBps": alg / ms / 1e6, "frac": alg / ms / 1e6 / peak,
+                                   "launches": batch, "unit": "64 sequences x 1024 positions of one layer, one launch per sequence "
+                                   "(4.7 MB each: launch-bound)"}
+        # scrub: free every sequence with zero fill (all 4096 blocks x 12 layers), then map them again
+        def scrub_all():
+            for s in seqs:
+                pool.mark_evictable(s, True)
+            pool.evict_lru(n_blocks, zero_fill=True)
+
+        def remap():
+            seqs.clear()
+            for i in range(batch):
+                s = pool.seq_alloc()
+                pool.set_block_table(s, perm[i])
+                pool.set_length(s, ctx_len)
+                seqs.append(s)
+
+        ts = []
+        for _ in range(max(3, repeats // 2)):
+            ctx.synchronize()
+            e0.record()
+            scrub_all()
+            e1.record()
+            ts.append(e0.elapsed_ms(e1))
+            remap()
+        ms = statistics.median(ts)
+        alg = n_blocks * LAYERS * HEADS * 64 * DHEAD
+        out["kv_scrub_kernel"] = {"ms": ms, "algorithmic_bytes": alg, "GBps": alg / ms / 1e6, "frac": alg / ms / 1e6 / peak,
+                                  "unit": "all 4096 blocks x 12 layers zero-filled by one eviction call (host allocator work included)"}
+        return {"workload": "K/V store kernels standalone: 12 layers x 24 heads x d_head 16, 64 x 1024 tokens, 4096-block pool",
+                "peak_GBps": peak, "peak_kind": kind, "kernels": out, "timing": f"CUDA events on the library's stream, median of {repeats}"}
+    finally:
+        pool.close()
 
 
 def run_longctx(ctx, rank, world, n_seqs_total=512, steps=20, warmup=3):

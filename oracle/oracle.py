@@ -29,14 +29,28 @@ def build(force: bool = False) -> str:
 
 
 _lib = None
+_FAST_PATH = os.path.join(_HERE, "libjgpt_oracle_fast.so")
+_use_fast = False
+
+
+def use_timing_build(on: bool = True):
+    """Switches this module to ``libjgpt_oracle_fast.so``: the same C file compiled ``-O3 -march=native`` on THIS
+    machine (always rebuilt: a copy built on another CPU may use instructions this one lacks).  For timing the CPU
+    baseline only; parity checks use the strict build (``-ffp-contract=off``), which stays the default."""
+    global _lib, _use_fast
+    if on:
+        subprocess.run(["make", "-B", "-C", _HERE, "timing"], check=True, capture_output=True)
+    if on != _use_fast:
+        _use_fast, _lib = on, None
 
 
 def lib():
     global _lib
     if _lib is not None:
         return _lib
-    build()
-    L = C.CDLL(_LIB_PATH)
+    if not _use_fast:
+        build()
+    L = C.CDLL(_FAST_PATH if _use_fast else _LIB_PATH)
     vp, ci, cf = C.c_void_p, C.c_int, C.c_float
     sig = {
         "og_rmsnorm": (None, [_f32p, _f32p, _f32p, ci, ci, cf]),

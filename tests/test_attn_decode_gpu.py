@@ -8,26 +8,10 @@ import numpy as np
 import pytest
 
 import oracle as O
-from helpers import PagedCase
+from helpers import PagedCase, oracle_decode as _oracle_decode
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-5
-
-
-def _oracle_decode(case, layer, q, lens, rope_pos):
-    """Attention only (no append): run the oracle's append+attend on a copy with the cached last token as 'new'."""
-    n, H, Dh = case.n, case.H, case.Dh
-    out = np.zeros((n, H * Dh), np.float32)
-    scale = 1.0 / np.sqrt(Dh)
-    qh = O.split_heads(q.reshape(n, 1, H * Dh), H)  # [n,H,1,Dh]
-    for i in range(n):
-        L = int(lens[i])
-        if L == 0:
-            continue
-        qr = O.rope_4d(qh[i:i + 1], positions=np.array([rope_pos[i]], np.int32))[0, :, 0]
-        for h in range(H):
-            out[i, h * Dh:(h + 1) * Dh] = O.attn_query_one(qr[h], case.kc[layer, i, h, :L], case.vc[layer, i, h, :L], scale)
-    return out
 
 
 @pytest.mark.parametrize("Dh,H", [(16, 24), (16, 5), (8, 4), (4, 2), (32, 6)])

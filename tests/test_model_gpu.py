@@ -344,3 +344,46 @@ def test_device_sampler_picks_the_oracles_token(ctx):
             gm.forwardDecodeSampleBatch(pool_s, seq_s, nxt, lens, lens, 1.0, 0, [0.5])
     finally:
         pool_s.close(), pool_l.close(), gm.close(), om.close()
+
+
+def test_forward_step_reports_a_failed_device_self_check_itself(ctx, small16):
+    """A corrupted block-table entry (-1 where the step reads or appends) must come back as an error from the
+    forward call itself -- no jgpt_sync needed, no tokens, no length change -- and the pool must stay usable:
+    the split-K arrival counters an aborted step may leave half counted are cleared with the status word."""
+    from jgpt_b200 import JgptError
+
+    om, gm = small16
+    V = om.vocab
+    pool = gm.newPool(n_blocks=16, max_seqs=2)
+    try:
+        seqs = [pool.seq_alloc(), pool.seq_alloc()]
+        prompts = [np.array([(i * 5 + 1) % V for i in range(40)], np.int32), np.array([3, 4, 5], np.int32)]
+        _, nxt = gm.forwardPrefillBatch(pool, seqs, prompts)
+        lens = [40, 3]
+        tab, stride = pool.table_device()
+        good = pool.block_table(seqs[0])
+        entry = tab + 4 * (seqs[0] * stride + 1)  # second block of the first sequence: tokens 16..31
+        bad = np.array([-1], np.int32)
+        J_lib = ctx._lib
+        from jgpt_b200 import binding as B
+        B.check(J_lib.jgpt_h2d(ctx.handle, entry, bad.ctypes.data, 4))
+        with pytest.raises(JgptError, match="bad-block-id"):
+            gm.forwardDecodeBatch(pool, seqs, nxt, lens, lens)
+        assert [pool.length(s) for s in seqs] == lens  # nothing advanced
+        ctx.synchronize()  # the status word was consumed by the failing call
+        fix = np.array([good[1]], np.int32)
+        B.check(J_lib.jgpt_h2d(ctx.handle, entry, fix.ctypes.data, 4))
+        logits, nxt2 = gm.forwardDecodeBatch(pool, seqs, nxt, lens, lens)
+        assert [pool.length(s) for s in seqs] == [41, 4]
+        # same answer as a pool that never saw the corruption
+        pool2 = gm.newPool(n_blocks=16, max_seqs=2)
+        try:
+            s2 = [pool2.seq_alloc(), pool2.seq_alloc()]
+            _, n0 = gm.forwardPrefillBatch(pool2, s2, prompts)
+            want, want_next = gm.forwardDecodeBatch(pool2, s2, n0, lens, lens)
+            assert np.array_equal(n0, nxt) and np.array_equal(want_next, nxt2)
+            assert np.abs(want - logits).max() < 1e-5
+        finally:
+            pool2.close()
+    finally:
+        pool.close()
