@@ -108,3 +108,18 @@ def test_algorithmic_bytes_figure():
     import bench
 
     assert bench.ALG_BYTES_LAYER == 100_876_288 and bench.ALG_BYTES_STEP == 1_210_515_456
+
+
+def test_java_ffm_bindings_cover_every_declared_symbol_with_matching_arity():
+    """java/.../JgptB200.java is what a Java host binds (no JDK here to compile it): it must name every entry point
+    the header declares, with one layout per C argument plus the return value."""
+    import re
+
+    from jgpt_b200 import binding
+
+    src = open(os.path.join(ROOT, "java", "com", "veles", "llm", "jgpt", "b200", "JgptB200.java")).read()
+    bound = {m.group(1): m.group(2) for m in re.finditer(r'bind\("(jgpt_\w+)", FunctionDescriptor\.of\(([^)]*)\)\)', src)}
+    for name, _res, args in binding.declared_functions():
+        assert name in bound, f"{name} has no FFM handle"
+        assert len([x for x in bound[name].split(",") if x.strip()]) == 1 + len(args), name
+    assert len(bound) == len(binding.declared_functions())
