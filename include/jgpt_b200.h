@@ -123,6 +123,12 @@ JGPT_API int32_t jgpt_kvpool_destroy(jgpt_kvpool pool); /* KvCacheGpu.close() */
 JGPT_API int32_t jgpt_kvpool_free_blocks(jgpt_kvpool pool, int32_t *n_free_out);
 /* Device address and byte size of the K/V storage (tests poison / inspect it). */
 JGPT_API int32_t jgpt_kvpool_storage(jgpt_kvpool pool, void **dev_out, uint64_t *bytes_out);
+/* Launch tuning of the decode-attention kernel for this pool (the values JGPT_B200_CHUNK_BLOCKS / _STAGES /
+ * _HEAD_GROUP / _PERSISTENT give at creation): KV blocks per split-K chunk (0 = automatic, <= 32), copy-ring
+ * stages (2..8), heads per CTA (0 = automatic, else a divisor of heads), persistent (<= 0: one CTA per work
+ * item; k > 0: k CTAs per SM claiming items from a queue).  Results do not depend on them. */
+JGPT_API int32_t jgpt_kvpool_set_tuning(jgpt_kvpool pool, int32_t chunk_blocks, int32_t stages, int32_t head_group,
+                                        int32_t persistent);
 /* Device mirror of the block tables, int32 [max_seqs][row_stride], -1 = unmapped (read-only for
  * callers' own kernels; tests corrupt an entry to exercise the kernels' self-checks). */
 JGPT_API int32_t jgpt_kvpool_table_device(jgpt_kvpool pool, int32_t **dev_out, int32_t *row_stride_out);

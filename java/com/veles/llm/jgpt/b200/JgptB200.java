@@ -58,6 +58,7 @@ public final class JgptB200 {
     private static final MethodHandle H_KVPOOL_DESTROY = bind("jgpt_kvpool_destroy", FunctionDescriptor.of(JAVA_INT, JAVA_LONG));
     private static final MethodHandle H_KVPOOL_FREE_BLOCKS = bind("jgpt_kvpool_free_blocks", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_KVPOOL_STORAGE = bind("jgpt_kvpool_storage", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS));
+    private static final MethodHandle H_KVPOOL_SET_TUNING = bind("jgpt_kvpool_set_tuning", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT));
     private static final MethodHandle H_KVPOOL_TABLE_DEVICE = bind("jgpt_kvpool_table_device", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS));
     private static final MethodHandle H_SEQ_ALLOC = bind("jgpt_seq_alloc", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_SEQ_FREE = bind("jgpt_seq_free", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT));
@@ -234,6 +235,11 @@ public final class JgptB200 {
     /** jgpt_kvpool_storage */
     public static int kvpoolStorage(long pool, MemorySegment dev_out, MemorySegment bytes_out) {
         try { return (int) H_KVPOOL_STORAGE.invokeExact(pool, devOut, bytesOut); } catch (Throwable t) { throw rethrow(t); }
+    }
+
+    /** jgpt_kvpool_set_tuning */
+    public static int kvpoolSetTuning(long pool, int chunk_blocks, int stages, int head_group, int persistent) {
+        try { return (int) H_KVPOOL_SET_TUNING.invokeExact(pool, chunkBlocks, stages, headGroup, persistent); } catch (Throwable t) { throw rethrow(t); }
     }
 
     /** jgpt_kvpool_table_device */

@@ -385,6 +385,17 @@ int32_t jgpt_kvpool_storage(jgpt_kvpool h, void **dev_out, uint64_t *bytes_out) 
     return JGPT_OK;
 }
 
+int32_t jgpt_kvpool_set_tuning(jgpt_kvpool h, int32_t chunk_blocks, int32_t stages, int32_t head_group, int32_t persistent) {
+    GET_POOL(p, h);
+    JGPT_REQUIRE(chunk_blocks >= 0 && chunk_blocks <= 32, JGPT_ERR_INVALID_ARGUMENT, "chunk_blocks must be in [0, 32] (0 = automatic)");
+    JGPT_REQUIRE(stages >= 2 && stages <= 8, JGPT_ERR_INVALID_ARGUMENT, "stages must be in [2, 8]");
+    JGPT_REQUIRE(head_group >= 0 && head_group <= p->heads && (head_group == 0 || p->heads % head_group == 0),
+                 JGPT_ERR_INVALID_ARGUMENT, "head_group must be 0 (automatic) or a divisor of %d", p->heads);
+    p->chunk_blocks = chunk_blocks, p->stages = stages, p->head_group = head_group, p->persistent = persistent;
+    p->generation += (uint64_t)1 << 32;  // graphs captured with the old launch shapes must not be replayed
+    return JGPT_OK;
+}
+
 int32_t jgpt_kvpool_table_device(jgpt_kvpool h, int32_t **dev_out, int32_t *row_stride_out) {
     GET_POOL(p, h);
     if (dev_out) *dev_out = p->d_table;
