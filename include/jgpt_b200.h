@@ -70,6 +70,14 @@ JGPT_API const char *jgpt_last_error(void);
 /* cudaStream_t of the context, for callers that enqueue their own work or time with events. */
 JGPT_API int32_t jgpt_ctx_stream(jgpt_ctx ctx, void **stream_out);
 JGPT_API int32_t jgpt_device_count(int32_t *out);
+/* The JGPT_* environment settings that reach this path, parsed with the reference's rules
+ * (J/TensorOpsGpuInit.java:30-101: JGPT_RMSNORM_EPS in (0, 1e-2], default 1e-5 with JGPT_FP16_MATMUL else
+ * 1e-6; J/training/LLMConfig.java:190-199: JGPT_MAX_SEQ_LEN positive, 0 here = not set) plus this
+ * library's own: JGPT_KV_BLOCK_TOKENS (16), JGPT_KV_POOL_BLOCKS (0 = not set), JGPT_KV_BACKEND
+ * (unset or "b200" -> 1; anything else -> 0: the host keeps the reference's own KV path).
+ * Needs no GPU.  Any output pointer may be NULL. */
+JGPT_API int32_t jgpt_env_config(int32_t *kv_block_tokens_out, int32_t *kv_pool_blocks_out,
+                                 int32_t *max_seq_len_out, float *rmsnorm_eps_out, int32_t *backend_b200_out);
 
 /* GpuFloatBuffer.allocate / close / copyFrom / copyTo / clear (J/GpuFloatBuffer.java:46-130,
  * natives C/jgpt_cuda_jni_buffers.inl:185-487).  jgpt_d2h synchronises before returning. */
@@ -146,6 +154,12 @@ JGPT_API int32_t jgpt_seq_length(jgpt_kvpool pool, int32_t seq, int32_t *len_out
 JGPT_API int32_t jgpt_seq_set_length(jgpt_kvpool pool, int32_t seq, int32_t len);
 /* clear(): length 0, blocks returned to the pool and (zero_fill != 0) scrubbed by the eviction kernel. */
 JGPT_API int32_t jgpt_seq_clear(jgpt_kvpool pool, int32_t seq, int32_t zero_fill);
+/* Block-granular rolling window.  No counterpart in the reference, which clears the cache and re-prefills the
+ * window when the context is full (J/model/GptAutoregressiveGenerator.java:51-88, O(window^2) per overflow).
+ * Forgets the oldest n_blocks KV blocks of the sequence: they return to the free list, the block table shifts
+ * left and the length drops by 16 * n_blocks; no K/V byte moves.  Cached keys keep the RoPE of their absolute
+ * positions.  JGPT_ERR_INVALID_ARGUMENT unless the sequence holds at least that many full blocks. */
+JGPT_API int32_t jgpt_seq_drop_front(jgpt_kvpool pool, int32_t seq, int32_t n_blocks, int32_t zero_fill);
 /* Install an explicit block table (benchmark: seeded permutation of the pool).  The blocks must be free. */
 JGPT_API int32_t jgpt_seq_set_block_table(jgpt_kvpool pool, int32_t seq, const int32_t *blocks_host, int32_t n);
 /* Copy the sequence's block table out (bit-exact checks against the allocator specification). */
@@ -292,6 +306,14 @@ JGPT_API int32_t jgpt_sample_next_token(const float *logits_host, int32_t vocab,
  * re-prefill when the context overflows.  n_sampled_out = number of sampled tokens. */
 JGPT_API int32_t jgpt_generate_greedy(jgpt_model model, jgpt_kvpool pool, const int32_t *prompt_host, int32_t S,
                                       int32_t max_new, int32_t *out_host, int32_t *n_sampled_out);
+/* The same loop with the rolling window instead of the re-prefill: when the sequence has filled its context the
+ * oldest block is dropped (jgpt_seq_drop_front) and decoding continues, RoPE at the absolute position and the
+ * position-table row = position mod max_seq_len (each token keeps the row it was embedded with while it stays
+ * in the window).  Needs a pool whose RoPE table (max_positions) covers S + max_new - 1 positions; jgpt_forward_decode
+ * accepts positions beyond max_seq_len only on such a pool, otherwise it rejects them as the reference does.
+ * Identical to jgpt_generate_greedy until the context first fills; not an exact-parity mode after that. */
+JGPT_API int32_t jgpt_generate_greedy_rolling(jgpt_model model, jgpt_kvpool pool, const int32_t *prompt_host, int32_t S,
+                                              int32_t max_new, int32_t *out_host, int32_t *n_sampled_out);
 
 
 /* ---------------------------------------------------------------------------------------------

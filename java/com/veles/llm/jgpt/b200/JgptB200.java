@@ -38,6 +38,7 @@ public final class JgptB200 {
     private static final MethodHandle H_LAST_ERROR = bind("jgpt_last_error", FunctionDescriptor.of(ADDRESS));
     private static final MethodHandle H_CTX_STREAM = bind("jgpt_ctx_stream", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_DEVICE_COUNT = bind("jgpt_device_count", FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    private static final MethodHandle H_ENV_CONFIG = bind("jgpt_env_config", FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
     private static final MethodHandle H_DEV_ALLOC = bind("jgpt_dev_alloc", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_DEV_FREE = bind("jgpt_dev_free", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_H2D = bind("jgpt_h2d", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, JAVA_LONG));
@@ -66,6 +67,7 @@ public final class JgptB200 {
     private static final MethodHandle H_SEQ_LENGTH = bind("jgpt_seq_length", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, ADDRESS));
     private static final MethodHandle H_SEQ_SET_LENGTH = bind("jgpt_seq_set_length", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT));
     private static final MethodHandle H_SEQ_CLEAR = bind("jgpt_seq_clear", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT));
+    private static final MethodHandle H_SEQ_DROP_FRONT = bind("jgpt_seq_drop_front", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_INT));
     private static final MethodHandle H_SEQ_SET_BLOCK_TABLE = bind("jgpt_seq_set_block_table", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, ADDRESS, JAVA_INT));
     private static final MethodHandle H_BLOCK_TABLE_COPY_OUT = bind("jgpt_block_table_copy_out", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS));
     private static final MethodHandle H_BLOCK_TABLE_COPY_OUT_DEVICE = bind("jgpt_block_table_copy_out_device", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS));
@@ -91,6 +93,7 @@ public final class JgptB200 {
     private static final MethodHandle H_FORWARD_DECODE_SAMPLE = bind("jgpt_forward_decode_sample", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, JAVA_FLOAT, JAVA_INT, ADDRESS, ADDRESS));
     private static final MethodHandle H_SAMPLE_NEXT_TOKEN = bind("jgpt_sample_next_token", FunctionDescriptor.of(JAVA_INT, ADDRESS, JAVA_INT, JAVA_FLOAT, JAVA_INT, JAVA_FLOAT, ADDRESS));
     private static final MethodHandle H_GENERATE_GREEDY = bind("jgpt_generate_greedy", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
+    private static final MethodHandle H_GENERATE_GREEDY_ROLLING = bind("jgpt_generate_greedy_rolling", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
     private static final MethodHandle H_SCHED_CREATE = bind("jgpt_sched_create", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS));
     private static final MethodHandle H_SCHED_DESTROY = bind("jgpt_sched_destroy", FunctionDescriptor.of(JAVA_INT, JAVA_LONG));
     private static final MethodHandle H_SCHED_SUBMIT = bind("jgpt_sched_submit", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS));
@@ -135,6 +138,11 @@ public final class JgptB200 {
     /** jgpt_device_count */
     public static int deviceCount(MemorySegment out) {
         try { return (int) H_DEVICE_COUNT.invokeExact(out); } catch (Throwable t) { throw rethrow(t); }
+    }
+
+    /** jgpt_env_config */
+    public static int envConfig(MemorySegment kv_block_tokens_out, MemorySegment kv_pool_blocks_out, MemorySegment max_seq_len_out, MemorySegment rmsnorm_eps_out, MemorySegment backend_b200_out) {
+        try { return (int) H_ENV_CONFIG.invokeExact(kvBlockTokensOut, kvPoolBlocksOut, maxSeqLenOut, rmsnormEpsOut, backendB200Out); } catch (Throwable t) { throw rethrow(t); }
     }
 
     /** jgpt_dev_alloc */
@@ -277,6 +285,11 @@ public final class JgptB200 {
         try { return (int) H_SEQ_CLEAR.invokeExact(pool, seq, zeroFill); } catch (Throwable t) { throw rethrow(t); }
     }
 
+    /** jgpt_seq_drop_front */
+    public static int seqDropFront(long pool, int seq, int n_blocks, int zero_fill) {
+        try { return (int) H_SEQ_DROP_FRONT.invokeExact(pool, seq, nBlocks, zeroFill); } catch (Throwable t) { throw rethrow(t); }
+    }
+
     /** jgpt_seq_set_block_table */
     public static int seqSetBlockTable(long pool, int seq, MemorySegment blocks_host, int n) {
         try { return (int) H_SEQ_SET_BLOCK_TABLE.invokeExact(pool, seq, blocksHost, n); } catch (Throwable t) { throw rethrow(t); }
@@ -400,6 +413,11 @@ public final class JgptB200 {
     /** jgpt_generate_greedy */
     public static int generateGreedy(long model, long pool, MemorySegment prompt_host, int S, int max_new, MemorySegment out_host, MemorySegment n_sampled_out) {
         try { return (int) H_GENERATE_GREEDY.invokeExact(model, pool, promptHost, S, maxNew, outHost, nSampledOut); } catch (Throwable t) { throw rethrow(t); }
+    }
+
+    /** jgpt_generate_greedy_rolling */
+    public static int generateGreedyRolling(long model, long pool, MemorySegment prompt_host, int S, int max_new, MemorySegment out_host, MemorySegment n_sampled_out) {
+        try { return (int) H_GENERATE_GREEDY_ROLLING.invokeExact(model, pool, promptHost, S, maxNew, outHost, nSampledOut); } catch (Throwable t) { throw rethrow(t); }
     }
 
     /** jgpt_sched_create */

@@ -475,6 +475,27 @@ int32_t jgpt_seq_clear(jgpt_kvpool h, int32_t seq, int32_t zero_fill) {
     return zero_fill ? launch_kv_scrub(p, freed) : JGPT_OK;
 }
 
+// Block-granular rolling window: forget the oldest n_blocks KV blocks of a sequence.  The blocks go back to the free
+// list in table order (the first dropped block is handed out last), the table shifts left, the length drops by
+// n_blocks * 16.  O(blocks of the sequence) host work and one small table upload; no K/V byte moves (the reference
+// clears its cache and re-prefills the whole window instead, GptAutoregressiveGenerator.java:51-88).
+int32_t jgpt_seq_drop_front(jgpt_kvpool h, int32_t seq, int32_t n_blocks, int32_t zero_fill) {
+    GET_POOL(p, h);
+    CHECK_SEQ(p, seq);
+    SeqState &s = p->seqs[(size_t)seq];
+    JGPT_REQUIRE(n_blocks >= 0 && n_blocks <= (int)s.blocks.size() && s.len >= n_blocks * kBlockTokens, JGPT_ERR_INVALID_ARGUMENT,
+                 "cannot drop %d blocks from a sequence of %d tokens in %d blocks", n_blocks, s.len, (int)s.blocks.size());
+    if (n_blocks == 0) return JGPT_OK;
+    std::vector<int> freed(s.blocks.begin(), s.blocks.begin() + n_blocks);
+    for (int b : freed) p->free_list.push_back(b);
+    s.blocks.erase(s.blocks.begin(), s.blocks.begin() + n_blocks);
+    s.len -= n_blocks * kBlockTokens;
+    s.tick = ++p->clock;
+    int32_t rc = pool_upload_table_row(p, seq);
+    if (rc) return rc;
+    return zero_fill ? launch_kv_scrub(p, freed) : JGPT_OK;
+}
+
 int32_t jgpt_seq_set_block_table(jgpt_kvpool h, int32_t seq, const int32_t *blocks_host, int32_t n) {
     GET_POOL(p, h);
     CHECK_SEQ(p, seq);

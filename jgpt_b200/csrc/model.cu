@@ -1421,9 +1421,13 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
                      JGPT_ERR_ILLEGAL_STATE, "KV cache of sequence %d is full (%d tokens)", s, cache_len_before_host[i]);
         JGPT_REQUIRE(ids_host[i] >= 0 && ids_host[i] < m->vocab, JGPT_ERR_INVALID_ARGUMENT, "token id %d outside [0,%d)", ids_host[i],
                      m->vocab);
-        JGPT_REQUIRE(rope_pos_host[i] >= 0 && rope_pos_host[i] < m->max_seq && rope_pos_host[i] < p->max_positions,
-                     JGPT_ERR_INVALID_ARGUMENT, "position %d outside the table of %d rows", rope_pos_host[i], m->max_seq);
-        ids[i] = ids_host[i], posrow[i] = rope_pos_host[i], sid[i] = s, rp[i] = rope_pos_host[i], lens[i] = cache_len_before_host[i] + 1;
+        // A pool created with the reference's geometry (max_positions == max_seq_len) rejects positions beyond the
+        // context, as PositionEmbedding does.  A pool with a longer RoPE table opts in to the rolling window: RoPE at
+        // the absolute position, position-table row = position mod max_seq_len.
+        JGPT_REQUIRE(rope_pos_host[i] >= 0 && rope_pos_host[i] < p->max_positions,
+                     JGPT_ERR_INVALID_ARGUMENT, "position %d outside the table of %d rows", rope_pos_host[i],
+                     std::min(m->max_seq, p->max_positions));
+        ids[i] = ids_host[i], posrow[i] = rope_pos_host[i] % m->max_seq, sid[i] = s, rp[i] = rope_pos_host[i], lens[i] = cache_len_before_host[i] + 1;
         max_len = std::max(max_len, lens[i]);
     }
     for (int i = 0; i < n; i++) {
@@ -1636,6 +1640,50 @@ int32_t jgpt_generate_greedy(jgpt_model h, jgpt_kvpool poolh, const int32_t *pro
     }
     const std::string keep = last_error_ref();
     jgpt_seq_free(poolh, seq);  // cache.close()
+    if (rc) last_error_ref() = keep;
+    if (n_sampled_out) *n_sampled_out = n;
+    return rc;
+}
+
+// Greedy generation with a block-granular rolling window in place of the reference's clear-and-re-prefill: when the
+// sequence has filled its context the oldest KV block is dropped (jgpt_seq_drop_front) and decoding continues; RoPE
+// at absolute positions, position-table row = position mod max_seq_len.  The pool's RoPE table (max_positions) bounds
+// how far generation can run.  Same tokens as jgpt_generate_greedy until the context first fills.
+int32_t jgpt_generate_greedy_rolling(jgpt_model h, jgpt_kvpool poolh, const int32_t *prompt_host, int32_t S, int32_t max_new,
+                                     int32_t *out_host, int32_t *n_sampled_out) {
+    GET_MODEL(m, h);
+    Pool *p = pool_registry().get(poolh);
+    int32_t rc = check_pool(m, p);
+    if (rc) return rc;
+    JGPT_REQUIRE(prompt_host && out_host && S >= 1 && max_new >= 0, JGPT_ERR_INVALID_ARGUMENT, "bad prompt or output buffer");
+    const int cap = std::min(m->max_seq, p->max_blocks_per_seq * kBlockTokens);
+    JGPT_REQUIRE(S <= cap, JGPT_ERR_INVALID_ARGUMENT, "seq_len %d > max_seq_len %d", S, cap);
+    JGPT_REQUIRE(S + max_new - 1 <= p->max_positions, JGPT_ERR_INVALID_ARGUMENT,
+                 "prompt %d + %d new tokens run past the pool's RoPE table of %d positions", S, max_new, p->max_positions);
+    for (int i = 0; i < S + max_new; i++) out_host[i] = i < S ? prompt_host[i] : 0;
+    if (n_sampled_out) *n_sampled_out = 0;
+    if (max_new == 0) return JGPT_OK;
+    int32_t seq = -1;
+    rc = jgpt_seq_alloc(poolh, &seq);
+    if (rc) return rc;
+    int n = 0;
+    int32_t tok = 0;
+    rc = jgpt_forward_prefill(h, poolh, seq, prompt_host, S, 0, nullptr, nullptr, &tok);
+    if (rc == JGPT_OK) {
+        out_host[S] = tok, n = 1;
+        for (int j = 1; j < max_new && tok != 0; j++) {
+            if (p->seqs[(size_t)seq].len >= cap) {
+                rc = jgpt_seq_drop_front(poolh, seq, 1, 0);
+                if (rc) break;
+            }
+            const int32_t prev = out_host[S + j - 1], len_before = p->seqs[(size_t)seq].len, rope = S + j - 1;
+            rc = jgpt_forward_decode(h, poolh, &seq, &prev, &len_before, &rope, 1, nullptr, &tok);
+            if (rc) break;
+            out_host[S + j] = tok, n++;
+        }
+    }
+    const std::string keep = last_error_ref();
+    jgpt_seq_free(poolh, seq);
     if (rc) last_error_ref() = keep;
     if (n_sampled_out) *n_sampled_out = n;
     return rc;

@@ -1,6 +1,9 @@
 // Context, stream, device buffers, events, error reporting.
 #include "common.cuh"
 
+#include <cmath>
+#include <cstdlib>
+
 #include <cstdlib>
 
 namespace jgpt {
@@ -141,6 +144,54 @@ int32_t jgpt_mem_info(jgpt_ctx h, uint64_t *free_bytes_out, uint64_t *total_byte
     JGPT_CUDA_TRY(cudaMemGetInfo(&f, &t));
     if (free_bytes_out) *free_bytes_out = f;
     if (total_bytes_out) *total_bytes_out = t;
+    return JGPT_OK;
+}
+
+// The JGPT_* settings that reach this path, read the way the reference reads them (env first, unparsable or
+// out-of-range values ignored): JGPT_RMSNORM_EPS accepts 0 < v <= 1e-2 and otherwise falls back to 1e-5 with
+// JGPT_FP16_MATMUL on, 1e-6 without (src/main/java/com/veles/llm/jgpt/TensorOpsGpuInit.java:30-101);
+// JGPT_MAX_SEQ_LEN is a positive override of the configured context (training/LLMConfig.java:190-199).
+// JGPT_KV_BLOCK_TOKENS (default 16), JGPT_KV_POOL_BLOCKS (0 = one full context per sequence) and
+// JGPT_KV_BACKEND ("b200", the default, or anything else to keep the reference's own KV path) belong to this library.
+int32_t jgpt_env_config(int32_t *kv_block_tokens_out, int32_t *kv_pool_blocks_out, int32_t *max_seq_len_out, float *rmsnorm_eps_out,
+                        int32_t *backend_b200_out) {
+    auto trimmed = [](const char *name) -> std::string {
+        const char *v = getenv(name);
+        if (!v) return std::string();
+        std::string t(v);
+        const size_t a = t.find_first_not_of(" \t\r\n"), b = t.find_last_not_of(" \t\r\n");
+        return a == std::string::npos ? std::string() : t.substr(a, b - a + 1);
+    };
+    auto positive_int = [&](const char *name, int dflt) {
+        const std::string t = trimmed(name);
+        if (t.empty()) return dflt;
+        char *end = nullptr;
+        const long v = strtol(t.c_str(), &end, 10);
+        return (end && *end == 0 && v > 0 && v <= 0x7fffffffL) ? (int)v : dflt;
+    };
+    auto truthy = [&](const char *name) {
+        std::string t = trimmed(name);
+        for (auto &ch : t) ch = (char)tolower((unsigned char)ch);
+        return t == "1" || t == "true";
+    };
+    if (kv_block_tokens_out) *kv_block_tokens_out = positive_int("JGPT_KV_BLOCK_TOKENS", kBlockTokens);
+    if (kv_pool_blocks_out) *kv_pool_blocks_out = positive_int("JGPT_KV_POOL_BLOCKS", 0);
+    if (max_seq_len_out) *max_seq_len_out = positive_int("JGPT_MAX_SEQ_LEN", 0);
+    if (rmsnorm_eps_out) {
+        float eps = truthy("JGPT_FP16_MATMUL") ? 1e-5f : 1e-6f;
+        const std::string t = trimmed("JGPT_RMSNORM_EPS");
+        if (!t.empty()) {
+            char *end = nullptr;
+            const float v = strtof(t.c_str(), &end);
+            if (end && *end == 0 && v > 0.f && std::isfinite(v) && v <= 1e-2f) eps = v;
+        }
+        *rmsnorm_eps_out = eps;
+    }
+    if (backend_b200_out) {
+        std::string t = trimmed("JGPT_KV_BACKEND");
+        for (auto &ch : t) ch = (char)tolower((unsigned char)ch);
+        *backend_b200_out = (t.empty() || t == "b200") ? 1 : 0;
+    }
     return JGPT_OK;
 }
 

@@ -81,6 +81,10 @@ class KvPool:
     def clear(self, seq, zero_fill=True):
         B.check(self._lib.jgpt_seq_clear(self.handle, seq, 1 if zero_fill else 0))
 
+    def drop_front(self, seq, n_blocks=1, zero_fill=False):
+        """Rolling window: forget the oldest n_blocks KV blocks of the sequence (no K/V byte moves)."""
+        B.check(self._lib.jgpt_seq_drop_front(self.handle, seq, n_blocks, 1 if zero_fill else 0))
+
     def set_block_table(self, seq, blocks):
         b = np.ascontiguousarray(blocks, np.int32)
         B.check(self._lib.jgpt_seq_set_block_table(self.handle, seq, b.ctypes.data, b.size))

@@ -51,10 +51,11 @@ class GPTModel:
         """Writes the parameters as ``veles.weights.v1`` (what ``GptModelWeightsLoader`` reads)."""
         B.check(self._lib.jgpt_model_save_weights(self.handle, os.fsencode(path)))
 
-    def newPool(self, n_blocks, max_seqs, max_blocks_per_seq=None) -> KvPool:
+    def newPool(self, n_blocks, max_seqs, max_blocks_per_seq=None, max_positions=None) -> KvPool:
+        """``max_positions`` > maxSeqLen sizes the RoPE table for the rolling-window mode (positions beyond the context)."""
         mbs = max_blocks_per_seq or -(-self.maxSeqLen // 16)
         return KvPool(self.ctx, self.numLayers, self.numHeads, self.dModel // self.numHeads, n_blocks, max_seqs, mbs,
-                      max_positions=self.maxSeqLen)
+                      max_positions=max_positions or self.maxSeqLen)
 
     # ---- forward step --------------------------------------------------------------------------
     def forwardPrefill(self, inputTokens, cache: KvCacheGpu, ropeOffset=0, all_rows=True):
@@ -146,6 +147,17 @@ class GPTModel:
         finally:
             if own:
                 pool.close()
+
+    def generateGpuKvRolling(self, inputTokens, maxNewTokens, pool: KvPool):
+        """Greedy generation with the block-granular rolling window instead of the clear-and-re-prefill: when the
+        context is full the oldest KV block is dropped and decoding continues.  ``pool`` must have been made with
+        ``max_positions >= len(prompt) + maxNewTokens - 1``.  Returns ids [S + maxNewTokens]."""
+        prompt = np.ascontiguousarray(inputTokens, np.int32).reshape(-1)
+        out = np.zeros(prompt.size + maxNewTokens, np.int32)
+        n = C.c_int32()
+        B.check(self._lib.jgpt_generate_greedy_rolling(self.handle, pool.handle, prompt.ctypes.data, prompt.size, maxNewTokens,
+                                                       out.ctypes.data, C.byref(n)))
+        return out
 
     def sampleNextToken(self, logits, temperature, topK, u01) -> int:
         lg = np.ascontiguousarray(logits, np.float32)

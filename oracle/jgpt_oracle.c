@@ -196,6 +196,24 @@ OG_API void og_cache_clear(og_cache *c) { /* KvCache.clear(): zero-fill + length
     }
     c->length = 0;
 }
+/* Block-granular rolling window (no reference counterpart; the reference clears the cache and re-prefills,
+ * J/model/GptAutoregressiveGenerator.java:51-88): forget the oldest n_tokens cached tokens.  Rows [n, length) of every
+ * head move to [0, length - n) with their payload untouched (keys keep the RoPE of their absolute positions), the
+ * vacated tail is zeroed, the length drops by n.  -1 unless 0 <= n_tokens <= length. */
+OG_API int og_cache_drop_front(og_cache *c, int n_tokens) {
+    if (n_tokens < 0 || n_tokens > c->length) return -1;
+    const size_t row = (size_t)c->dhead;
+    for (int l = 0; l < c->layers; l++)
+        for (int h = 0; h < c->heads; h++) {
+            float *planes[2] = {c->k[l] + (size_t)h * c->max_seq * row, c->v[l] + (size_t)h * c->max_seq * row};
+            for (int t = 0; t < 2; t++) {
+                memmove(planes[t], planes[t] + (size_t)n_tokens * row, sizeof(float) * (size_t)(c->length - n_tokens) * row);
+                memset(planes[t] + (size_t)(c->length - n_tokens) * row, 0, sizeof(float) * (size_t)n_tokens * row);
+            }
+        }
+    c->length -= n_tokens;
+    return 0;
+}
 OG_API int og_cache_length(const og_cache *c) { return c->length; }
 OG_API int og_cache_set_length(og_cache *c, int len) { /* KvCache.setLength: IAE unless 0<=len<=maxSeq */
     if (len < 0 || len > c->max_seq) return -1;
@@ -518,13 +536,27 @@ OG_API int og_forward(const og_model *m, const int *ids, int S, float *logits) {
 
 /* forwardDecode: J/model/GptKvForward.java:92-170.  -1 = IllegalArgument, -2 = IllegalState
  * (cache.length() != cacheLenBefore, or cache full). logits [V]. */
+static int og_forward_decode_rows(const og_model *m, int id, og_cache *cache, int cache_len_before, int rope_position,
+                                  int pos_row, float *logits);
 OG_API int og_forward_decode(const og_model *m, int id, og_cache *cache, int cache_len_before, int rope_position,
                              float *logits) {
+    return og_forward_decode_rows(m, id, cache, cache_len_before, rope_position, rope_position, logits);
+}
+/* The rolling-window form of the same step: RoPE at the token's absolute position (which may lie beyond the context),
+ * position-table row = position mod maxSeq, so that every token keeps the row it was embedded with for as long as it
+ * stays in the window.  Identical to og_forward_decode while rope_position < maxSeq. */
+OG_API int og_forward_decode_rolling(const og_model *m, int id, og_cache *cache, int cache_len_before, int rope_position,
+                                     float *logits) {
+    if (rope_position < 0) return -1;
+    return og_forward_decode_rows(m, id, cache, cache_len_before, rope_position, rope_position % m->max_seq, logits);
+}
+static int og_forward_decode_rows(const og_model *m, int id, og_cache *cache, int cache_len_before, int rope_position,
+                                  int pos_row, float *logits) {
     const int D = m->d_model;
     if (cache->length != cache_len_before) return -2;
     if (cache_len_before >= cache->max_seq) return -2;
     float *x = (float *)malloc(4 * (size_t)D), *xn = (float *)malloc(4 * (size_t)D);
-    if (og_embed(m, &id, 1, rope_position, x)) { free(x), free(xn); return -1; }
+    if (og_embed(m, &id, 1, pos_row, x)) { free(x), free(xn); return -1; }
     for (int l = 0; l < m->layers; l++) {
         og_attn_residual(m, &m->L[l], x, 1, cache, l, 1, cache_len_before, rope_position);
         og_ffn_residual(m, &m->L[l], x, 1);
@@ -622,6 +654,33 @@ OG_API int og_generate_greedy(const og_model *m, const int *prompt, int S, int m
             out[cur] = tok, n++;
             if (tok == 0) break;
         }
+    }
+    og_cache_free(cache), free(logits);
+    return n;
+}
+
+/* Greedy generation with the block-granular rolling window instead of the reference's clear-and-re-prefill: when the
+ * cache is full the oldest `block` tokens are dropped and decoding simply continues (RoPE at absolute positions,
+ * position row = position mod maxSeq).  Same outputs as og_generate_greedy until the context first fills. */
+OG_API int og_generate_greedy_rolling(const og_model *m, const int *prompt, int S, int max_new, int kv_fp16, int block,
+                                      int *out) {
+    const int V = m->vocab, Dh = m->d_model / m->heads;
+    for (int i = 0; i < S + max_new; i++) out[i] = (i < S) ? prompt[i] : 0;
+    if (max_new <= 0) return 0;
+    if (block <= 0 || S > m->max_seq) return -1;
+    og_cache *cache = og_cache_create(m->layers, m->heads, Dh, m->max_seq);
+    cache->kv_fp16 = kv_fp16;
+    float *logits = (float *)malloc(4 * (size_t)m->max_seq * V);
+    int rc = og_forward_prefill(m, prompt, S, cache, 0, logits);
+    if (rc) { og_cache_free(cache), free(logits); return rc; }
+    int n = 0, tok = og_argmax(logits + (size_t)(S - 1) * V, V);
+    out[S] = tok, n = 1;
+    for (int j = 1; j < max_new && tok != 0; j++) {
+        if (cache->length >= cache->max_seq && og_cache_drop_front(cache, block)) { n = -2; break; }
+        rc = og_forward_decode_rolling(m, out[S + j - 1], cache, cache->length, S + j - 1, logits);
+        if (rc) { n = rc; break; }
+        tok = og_argmax(logits, V);
+        out[S + j] = tok, n++;
     }
     og_cache_free(cache), free(logits);
     return n;

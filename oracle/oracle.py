@@ -67,6 +67,9 @@ def lib():
         "og_cache_length": (ci, [vp]),
         "og_cache_set_length": (ci, [vp, ci]),
         "og_cache_set_kv_fp16": (None, [vp, ci]),
+        "og_cache_drop_front": (ci, [vp, ci]),
+        "og_forward_decode_rolling": (ci, [vp, ci, vp, ci, ci, _f32p]),
+        "og_generate_greedy_rolling": (ci, [vp, _i32p, ci, ci, ci, ci, _i32p]),
         "og_cache_k": (C.POINTER(C.c_float), [vp, ci]),
         "og_cache_v": (C.POINTER(C.c_float), [vp, ci]),
         "og_attn_query_one": (None, [_f32p, _f32p, _f32p, ci, ci, cf, _f32p, _f32p]),
@@ -227,6 +230,11 @@ class KvCache:
     def clear(self):
         lib().og_cache_clear(self._h)
 
+    def drop_front(self, n_tokens):
+        """Rolling window: forget the oldest n_tokens (rows shift to the front, payload untouched)."""
+        if lib().og_cache_drop_front(self._h, n_tokens):
+            raise ValueError("cannot drop more tokens than the cache holds")
+
     def close(self):
         if self._h:
             lib().og_cache_free(self._h)
@@ -303,6 +311,24 @@ class Model:
         if rc:
             raise ValueError(f"forward_decode rc={rc}")
         return out
+
+    def forward_decode_rolling(self, tok, cache, cache_len_before, rope_position):
+        """Decode step of the rolling-window mode: RoPE at the absolute position, position row = position mod maxSeq."""
+        out = np.empty(self.vocab, np.float32)
+        rc = lib().og_forward_decode_rolling(self._h, int(tok), cache._h, cache_len_before, rope_position, out)
+        if rc == -2:
+            raise RuntimeError("cache length mismatch or cache full")
+        if rc:
+            raise ValueError(f"forward_decode_rolling rc={rc}")
+        return out
+
+    def generate_greedy_rolling(self, prompt, max_new, kv_fp16=False, block=16):
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros(prompt.size + max_new, np.int32)
+        n = lib().og_generate_greedy_rolling(self._h, prompt, prompt.size, max_new, 1 if kv_fp16 else 0, block, out)
+        if n < 0:
+            raise ValueError(f"generate_rolling rc={n}")
+        return out, n
 
     def generate_greedy(self, prompt, max_new, kv_fp16=False, trace=False):
         prompt = np.ascontiguousarray(prompt, np.int32)
@@ -408,6 +434,18 @@ class PagedAllocatorRef:
         for b in blocks:
             self.free.remove(b)
         self.tables[s] = blocks
+        return True
+
+    def drop_front(self, s, n_blocks):
+        """Rolling window: the oldest n_blocks blocks of s go back to the free list (in table order, so the first
+        dropped block is handed out last), the table shifts left, the length drops by n_blocks * block_tokens."""
+        if n_blocks < 0 or n_blocks > len(self.tables[s]) or self.length[s] < n_blocks * self.bt:
+            return False
+        for b in self.tables[s][:n_blocks]:
+            self.free.append(b)
+        del self.tables[s][:n_blocks]
+        self.length[s] -= n_blocks * self.bt
+        self.touch(s)
         return True
 
     def touch(self, s):

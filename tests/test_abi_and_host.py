@@ -123,3 +123,36 @@ def test_java_ffm_bindings_cover_every_declared_symbol_with_matching_arity():
         assert name in bound, f"{name} has no FFM handle"
         assert len([x for x in bound[name].split(",") if x.strip()]) == 1 + len(args), name
     assert len(bound) == len(binding.declared_functions())
+
+
+def test_env_config_follows_the_reference_parsing_rules(monkeypatch):
+    """jgpt_env_config needs no GPU: JGPT_RMSNORM_EPS in (0, 1e-2] else the default (1e-5 with JGPT_FP16_MATMUL, 1e-6
+    without: TensorOpsGpuInit.resolveRmsNormEps), JGPT_MAX_SEQ_LEN positive or ignored, this library's own keys."""
+    from jgpt_b200 import binding
+
+    lib = binding.load()
+
+    def read():
+        bt, pb, ms, be = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+        eps = C.c_float()
+        assert lib.jgpt_env_config(C.byref(bt), C.byref(pb), C.byref(ms), C.byref(eps), C.byref(be)) == 0
+        return bt.value, pb.value, ms.value, eps.value, be.value
+
+    for k in ("JGPT_KV_BLOCK_TOKENS", "JGPT_KV_POOL_BLOCKS", "JGPT_MAX_SEQ_LEN", "JGPT_RMSNORM_EPS", "JGPT_FP16_MATMUL", "JGPT_KV_BACKEND"):
+        monkeypatch.delenv(k, raising=False)
+    assert read() == (16, 0, 0, np.float32(1e-6), 1)
+    monkeypatch.setenv("JGPT_FP16_MATMUL", "TRUE")
+    assert read()[3] == np.float32(1e-5)
+    monkeypatch.setenv("JGPT_RMSNORM_EPS", " 3e-4 ")
+    assert read()[3] == np.float32(3e-4)
+    for bad in ("0", "-1e-5", "0.5", "nan", "inf", "abc", ""):
+        monkeypatch.setenv("JGPT_RMSNORM_EPS", bad)
+        assert read()[3] == np.float32(1e-5), bad
+    monkeypatch.setenv("JGPT_MAX_SEQ_LEN", "512")
+    monkeypatch.setenv("JGPT_KV_POOL_BLOCKS", "4096")
+    monkeypatch.setenv("JGPT_KV_BACKEND", "Reference")
+    assert read()[:3] == (16, 4096, 512) and read()[4] == 0
+    monkeypatch.setenv("JGPT_MAX_SEQ_LEN", "-7")
+    monkeypatch.setenv("JGPT_KV_BACKEND", "b200")
+    assert read()[2] == 0 and read()[4] == 1
+    assert lib.jgpt_env_config(None, None, None, None, None) == 0

@@ -387,3 +387,50 @@ def test_forward_step_reports_a_failed_device_self_check_itself(ctx, small16):
             pool2.close()
     finally:
         pool.close()
+
+
+def test_rolling_window_generation_matches_the_oracles_rolling_specification(ctx, small16):
+    """Block-granular rolling window instead of the clear-and-re-prefill: the library drops the oldest KV block when the
+    context is full and keeps decoding.  Streams identical to the oracle's restatement of the same policy over three
+    context lengths; the block table after each drop follows the allocator specification; identical to the ordinary
+    generator until the context first fills; a pool with the reference's geometry still rejects positions beyond it."""
+    om, gm = small16
+    V, MS = om.vocab, om.max_seq  # 96, 80
+    prompt = np.array([(i * 7 + 2) % V for i in range(30)], np.int32)
+    max_new = 3 * MS
+    want, n_want = om.generate_greedy_rolling(prompt, max_new, kv_fp16=True)
+    pool = gm.newPool(n_blocks=MS // 16 + 2, max_seqs=1, max_positions=prompt.size + max_new)
+    try:
+        got = gm.generateGpuKvRolling(prompt, max_new, pool)
+        assert np.array_equal(got, want), int(np.argmax(got != want))
+        assert n_want == max_new or want[prompt.size + n_want - 1] == 0
+        assert pool.free_blocks() == MS // 16 + 2  # the sequence was released
+        # until the context fills it is the ordinary generator
+        plain = gm.generateGpuKv(prompt, MS - prompt.size + 1)
+        assert np.array_equal(plain, got[: plain.size])
+        # allocator: drop_front against the specification
+        ref = O.PagedAllocatorRef(MS // 16 + 2, 16, 1, MS // 16)
+        s, rs = pool.seq_alloc(), ref.seq_alloc()
+        pool.reserve(s, MS), ref.reserve(rs, MS)
+        pool.set_length(s, MS)
+        ref.length[rs] = MS
+        pool.drop_front(s, 2), ref.drop_front(rs, 2)
+        assert pool.block_table(s).tolist() == ref.tables[rs] == pool.block_table(s, device=True).tolist()
+        assert pool.length(s) == ref.length[rs] == MS - 32 and pool.free_blocks() == len(ref.free)
+        pool.reserve(s, MS), ref.reserve(rs, MS)
+        assert pool.block_table(s).tolist() == ref.tables[rs]
+        with pytest.raises(ValueError):
+            pool.drop_front(s, 4)  # only 48 tokens are cached
+        pool.seq_free(s)
+    finally:
+        pool.close()
+    strict = gm.newPool(n_blocks=MS // 16, max_seqs=1)  # RoPE table = context, as the reference
+    try:
+        with pytest.raises(ValueError):
+            gm.generateGpuKvRolling(prompt, max_new, strict)
+        s = strict.seq_alloc()
+        gm.forwardPrefillBatch(strict, [s], [prompt])
+        with pytest.raises(ValueError):  # PositionEmbedding: row outside the table
+            gm.forwardDecodeBatch(strict, [s], [1], [30], [MS])
+    finally:
+        strict.close()

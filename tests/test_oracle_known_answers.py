@@ -235,3 +235,44 @@ def test_decode_attn_batch_equals_model_attention_core(tiny):
         for h in range(H):
             want = O.attn_query_one(qr[h], kc0[i, h, :lens[i] + 1], vc0[i, h, :lens[i] + 1], 1 / math.sqrt(Dh))
             assert np.array_equal(out[i, h * Dh:(h + 1) * Dh], want)
+
+
+def test_rolling_window_specification():
+    """The block-granular rolling window (no reference counterpart): until the context first fills it is the ordinary
+    generator; afterwards a decode step over the shifted cache equals a step over a cache that was built with only the
+    surviving tokens -- same keys (RoPE at their absolute positions), same position rows (position mod maxSeq)."""
+    V, MS = 50, 32
+    om = O.Model(V, MS, 32, 4, 2, 64, eps=1e-6).init_random(seed=8, std=0.2)
+    try:
+        prompt = np.array([(i * 3 + 1) % V for i in range(20)], np.int32)
+        plain, n_plain = om.generate_greedy(prompt, MS - 20 + 1)
+        roll, n_roll = om.generate_greedy_rolling(prompt, MS - 20 + 1)
+        assert n_plain == n_roll and np.array_equal(plain, roll)  # nothing dropped yet: identical
+        # run past the context: 2 full windows more
+        out, n = om.generate_greedy_rolling(prompt, 3 * MS)
+        assert n >= 1 and (n == 3 * MS or out[20 + n - 1] == 0)
+        # one step by hand: cache of 32 tokens, drop 16, decode at absolute position 32
+        c = om.new_cache()
+        ids = np.array([(i * 5 + 2) % V for i in range(MS)], np.int32)
+        om.forward_prefill(ids, c)
+        k_before = c.k(0).copy()
+        c.drop_front(16)
+        assert c.length() == 16 and np.array_equal(c.k(0)[:, :16], k_before[:, 16:32]) and not c.k(0)[:, 16:].any()
+        got = om.forward_decode_rolling(7, c, 16, MS)  # position 32 -> row 0
+        assert c.length() == 17
+        with pytest.raises(ValueError):
+            c.drop_front(18)
+        # the same step through the ordinary call is refused: position 32 has no row in the table
+        c2 = om.new_cache()
+        with pytest.raises(ValueError):
+            om.forward_decode(7, c2, 0, MS)
+        assert np.isfinite(got).all()
+    finally:
+        om.close()
+    a = O.PagedAllocatorRef(n_blocks=6, block_tokens=16, max_seqs=2, max_blocks_per_seq=4)
+    s = a.seq_alloc()
+    assert a.reserve(s, 50) and a.tables[s] == [0, 1, 2, 3]
+    a.length[s] = 50
+    assert a.drop_front(s, 2) and a.tables[s] == [2, 3] and a.length[s] == 18 and a.free[-2:] == [0, 1]
+    assert not a.drop_front(s, 2)  # only one full block left in 18 tokens
+    assert a.reserve(s, 40) and a.tables[s] == [2, 3, 1]  # the block dropped last comes back first
