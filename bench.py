@@ -345,6 +345,9 @@ def run_gpu(args, rank, world, local_rank):
     import jgpt_b200 as J
     from jgpt_b200.runtime import Event
 
+    from jgpt_b200.runtime import bind_host_near_gpu
+
+    numa = bind_host_near_gpu(local_rank)  # before any page-locked allocation: the host buffers land next to the GPU
     ctx = J.Context(local_rank)
     lib = ctx._lib
     ranks = Ranks(ctx, rank, world)
@@ -484,7 +487,7 @@ def run_gpu(args, rank, world, local_rank):
                                    "GBps": ALG_BYTES_STEP / (per_layer_ms * 1e-3) / 1e9,
                                    "frac_of_measured": ALG_BYTES_STEP / (per_layer_ms * 1e-3) / 1e9 / peak,
                                    "frac_of_nominal_8TBs": ALG_BYTES_STEP / (per_layer_ms * 1e-3) / 1e9 / 8000.0},
-            "clocks": clocks, "ranks_joined_by": "jgpt_comm (NCCL inside the library)" if world > 1 else "single rank",
+            "host_binding": numa, "clocks": clocks, "ranks_joined_by": "jgpt_comm (NCCL inside the library)" if world > 1 else "single rank",
         }
         line.update(extras)
         if not args.no_cpu:

@@ -70,6 +70,9 @@ JGPT_API const char *jgpt_last_error(void);
 /* cudaStream_t of the context, for callers that enqueue their own work or time with events. */
 JGPT_API int32_t jgpt_ctx_stream(jgpt_ctx ctx, void **stream_out);
 JGPT_API int32_t jgpt_device_count(int32_t *out);
+/* PCI address of a device, lower case ("0000:1b:00.0"), for hosts that bind a rank's thread and page-locked
+ * buffers to the GPU's NUMA node (/sys/bus/pci/devices/<id>/numa_node).  No reference counterpart (one GPU). */
+JGPT_API int32_t jgpt_device_pci_bus_id(int32_t device, char *out, int32_t cap);
 /* The JGPT_* environment settings that reach this path, parsed with the reference's rules
  * (J/TensorOpsGpuInit.java:30-101: JGPT_RMSNORM_EPS in (0, 1e-2], default 1e-5 with JGPT_FP16_MATMUL else
  * 1e-6; J/training/LLMConfig.java:190-199: JGPT_MAX_SEQ_LEN positive, 0 here = not set) plus this
@@ -132,11 +135,16 @@ JGPT_API int32_t jgpt_kvpool_free_blocks(jgpt_kvpool pool, int32_t *n_free_out);
 /* Device address and byte size of the K/V storage (tests poison / inspect it). */
 JGPT_API int32_t jgpt_kvpool_storage(jgpt_kvpool pool, void **dev_out, uint64_t *bytes_out);
 /* Launch tuning of the decode-attention kernel for this pool (the values JGPT_B200_CHUNK_BLOCKS / _STAGES /
- * _HEAD_GROUP / _PERSISTENT give at creation): KV blocks per split-K chunk (0 = automatic, <= 32), copy-ring
- * stages (2..8), heads per CTA (0 = automatic, else a divisor of heads), persistent (<= 0: one CTA per work
- * item; k > 0: k CTAs per SM claiming items from a queue).  Results do not depend on them. */
+ * _HEAD_GROUP / _PERSISTENT / _LAUNCH_OVERLAP give at creation): KV blocks per split-K chunk (0 = automatic,
+ * <= 32), copy-ring stages (2..8), heads per CTA (0 = automatic, else a divisor of heads), persistent (<= 0: one
+ * CTA per work item; k > 0: k CTAs per SM claiming items from a queue), and launch_overlap: 0 = ordinary launches;
+ * 1 = programmatic dependent launch, the kernel starts while the previous kernel on the stream drains but reads
+ * nothing before that kernel has finished; 2 = additionally the copy warp fetches lengths, block-table entries and
+ * the first K/V slabs early -- ONLY for callers whose previous kernel on the stream does not write the K/V of the
+ * launch's layers, the block tables or the index arrays (true for a per-layer decode loop: the predecessor is a
+ * projection or another layer's attention).  Results do not depend on any of them. */
 JGPT_API int32_t jgpt_kvpool_set_tuning(jgpt_kvpool pool, int32_t chunk_blocks, int32_t stages, int32_t head_group,
-                                        int32_t persistent);
+                                        int32_t persistent, int32_t launch_overlap);
 /* Device mirror of the block tables, int32 [max_seqs][row_stride], -1 = unmapped (read-only for
  * callers' own kernels; tests corrupt an entry to exercise the kernels' self-checks). */
 JGPT_API int32_t jgpt_kvpool_table_device(jgpt_kvpool pool, int32_t **dev_out, int32_t *row_stride_out);

@@ -134,6 +134,19 @@ public final class B200Model implements AutoCloseable {
         }
     }
 
+    /**
+     * Greedy generation with the block-granular rolling window instead of the reference's clear-and-re-prefill.  The pool
+     * must have a RoPE table of at least {@code prompt.length + maxNewTokens - 1} positions.  Not an exact-parity mode once
+     * the context has filled.
+     */
+    public int[] generateGreedyRolling(KvPool pool, int[] prompt, int maxNewTokens) {
+        try (Arena a = Arena.ofConfined()) {
+            MemorySegment out = a.allocate(JAVA_INT, prompt.length + maxNewTokens), n = a.allocate(JAVA_INT);
+            check(JgptB200.generateGreedyRolling(handle(), pool.handle(), a.allocateFrom(JAVA_INT, prompt), prompt.length, maxNewTokens, out, n));
+            return out.toArray(JAVA_INT);
+        }
+    }
+
     @Override
     public void close() {
         if (handle != 0) {

@@ -38,6 +38,7 @@ public final class JgptB200 {
     private static final MethodHandle H_LAST_ERROR = bind("jgpt_last_error", FunctionDescriptor.of(ADDRESS));
     private static final MethodHandle H_CTX_STREAM = bind("jgpt_ctx_stream", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_DEVICE_COUNT = bind("jgpt_device_count", FunctionDescriptor.of(JAVA_INT, ADDRESS));
+    private static final MethodHandle H_DEVICE_PCI_BUS_ID = bind("jgpt_device_pci_bus_id", FunctionDescriptor.of(JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT));
     private static final MethodHandle H_ENV_CONFIG = bind("jgpt_env_config", FunctionDescriptor.of(JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS));
     private static final MethodHandle H_DEV_ALLOC = bind("jgpt_dev_alloc", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_DEV_FREE = bind("jgpt_dev_free", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
@@ -59,7 +60,7 @@ public final class JgptB200 {
     private static final MethodHandle H_KVPOOL_DESTROY = bind("jgpt_kvpool_destroy", FunctionDescriptor.of(JAVA_INT, JAVA_LONG));
     private static final MethodHandle H_KVPOOL_FREE_BLOCKS = bind("jgpt_kvpool_free_blocks", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_KVPOOL_STORAGE = bind("jgpt_kvpool_storage", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS));
-    private static final MethodHandle H_KVPOOL_SET_TUNING = bind("jgpt_kvpool_set_tuning", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT));
+    private static final MethodHandle H_KVPOOL_SET_TUNING = bind("jgpt_kvpool_set_tuning", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT));
     private static final MethodHandle H_KVPOOL_TABLE_DEVICE = bind("jgpt_kvpool_table_device", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS));
     private static final MethodHandle H_SEQ_ALLOC = bind("jgpt_seq_alloc", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
     private static final MethodHandle H_SEQ_FREE = bind("jgpt_seq_free", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT));
@@ -138,6 +139,11 @@ public final class JgptB200 {
     /** jgpt_device_count */
     public static int deviceCount(MemorySegment out) {
         try { return (int) H_DEVICE_COUNT.invokeExact(out); } catch (Throwable t) { throw rethrow(t); }
+    }
+
+    /** jgpt_device_pci_bus_id */
+    public static int devicePciBusId(int device, MemorySegment out, int cap) {
+        try { return (int) H_DEVICE_PCI_BUS_ID.invokeExact(device, out, cap); } catch (Throwable t) { throw rethrow(t); }
     }
 
     /** jgpt_env_config */
@@ -246,8 +252,8 @@ public final class JgptB200 {
     }
 
     /** jgpt_kvpool_set_tuning */
-    public static int kvpoolSetTuning(long pool, int chunk_blocks, int stages, int head_group, int persistent) {
-        try { return (int) H_KVPOOL_SET_TUNING.invokeExact(pool, chunkBlocks, stages, headGroup, persistent); } catch (Throwable t) { throw rethrow(t); }
+    public static int kvpoolSetTuning(long pool, int chunk_blocks, int stages, int head_group, int persistent, int launch_overlap) {
+        try { return (int) H_KVPOOL_SET_TUNING.invokeExact(pool, chunkBlocks, stages, headGroup, persistent, launchOverlap); } catch (Throwable t) { throw rethrow(t); }
     }
 
     /** jgpt_kvpool_table_device */

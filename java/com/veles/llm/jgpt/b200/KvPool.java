@@ -86,6 +86,11 @@ public final class KvPool implements AutoCloseable {
         check(JgptB200.seqClear(handle(), seq, zeroFill ? 1 : 0));
     }
 
+    /** Rolling window: forget the oldest {@code nBlocks} KV blocks of the sequence (no K/V byte moves, no re-prefill). */
+    public void dropFront(int seq, int nBlocks, boolean zeroFill) {
+        check(JgptB200.seqDropFront(handle(), seq, nBlocks, zeroFill ? 1 : 0));
+    }
+
     public void markEvictable(int seq, boolean evictable) {
         check(JgptB200.seqMarkEvictable(handle(), seq, evictable ? 1 : 0));
     }

@@ -33,6 +33,12 @@ struct DecodeParams {
     int n, H, HG, n_hg, layer0, n_layers, mbs, n_blocks, max_seqs, max_positions;
     int chunk_blocks, max_chunks, n_items, stages, max_len;
     float scale_log2e;
+    // Launch overlap (programmatic dependent launch).  0: ordinary launch.  1: the launch may start while the previous
+    // kernel on the stream drains; everything that reads memory waits for that kernel first (only the barrier set-up
+    // runs ahead).  2: additionally the producer warp runs ahead -- lengths, block-table entries and the first K/V
+    // slabs are fetched before the previous kernel has finished -- which is only legal when that kernel does not
+    // write the K/V store of these layers, the block tables or the index arrays (the caller's promise).
+    int overlap;
     int dynamic;    // 1: CTAs claim work items from counters[0]; 0: item = blockIdx.x + k * gridDim.x
     int *counters;  // [0] next item, [1] CTAs that have finished (the last one resets both)
 };
@@ -180,6 +186,10 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     __syncthreads();
 
     const bool is_producer = tid >= n_cons;
+    // q / k_new / v_new come from the previous kernel on the stream, and the split-K scratch and counters are shared
+    // with it: the consumers always wait for it.  The producer touches neither; it waits unless the caller has
+    // promised that what it reads (lengths, tables, cached K/V) is not written by that kernel.
+    if (P.overlap && (!is_producer || P.overlap < 2)) griddep_wait();
     uint32_t it = 0;  // KV blocks processed so far by this CTA (producer and consumers count alike)
     int stage = 0;    // it % NS, kept incrementally (no integer division in the block loop)
     uint32_t phase = 0;  // (it / NS) & 1
@@ -269,6 +279,8 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             if (pending == 2) step_resolve(), pending = 1;
             if (pending == 1) step_table();
         }
+        // every copy of this CTA has been issued: the next launch on the stream may begin to move in
+        if (P.overlap) griddep_launch_dependents();
     } else
     for (;;) {
         if (*s_abort) break;  // a bounded wait ran out: stop taking work (status word says why)
@@ -785,7 +797,17 @@ static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int t
     // (kMaxStages stages of a 24 KiB slab), so that no later, smaller request ever lowers the limit again.
     JGPT_CUDA_TRY(decode_opt_in_smem(kern, (fused ? 1 : 0) + (mma ? 2 : 0) + 4 * (DH == 4 ? 0 : DH == 8 ? 1 : DH == 16 ? 2 : 3),
                                      p->ctx->device));
-    kern<<<grid, threads, smem, p->ctx->stream>>>(P);
+    if (P.overlap) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid), cfg.blockDim = dim3((unsigned)threads), cfg.dynamicSmemBytes = smem, cfg.stream = p->ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+        JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, P));
+    } else {
+        kern<<<grid, threads, smem, p->ctx->stream>>>(P);
+    }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
@@ -826,6 +848,7 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
     P.stages = p->stages;
+    P.overlap = p->launch_overlap;
     P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
     const long long items = (long long)n_layers * n * P.n_hg * P.max_chunks;
     JGPT_REQUIRE(items < (1ll << 31), JGPT_ERR_INVALID_ARGUMENT, "too many work items (%lld)", items);
@@ -846,6 +869,7 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
         P.dynamic = 1;
         P.counters = p->d_item_counters;
     }
+    if (P.dynamic && P.overlap > 1) P.overlap = 1;  // the work-queue counters are reset by the previous launch's last CTA
     const bool fused = k_new != nullptr;
     switch (DH) {
         case 4: return launch_decode_t<4>(p, P, fused, threads, smem, grid);
@@ -953,13 +977,24 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
                 p->host_tune_n = n, p->host_tune_layers = n_layers, p->host_tune_calls = 0, p->host_mode = -1;
                 for (double &b : p->host_tune_best) b = 1e30;
             }
-            if (p->host_mode >= 0) {
-                mode = p->host_mode;
+            // Which way wins is a property of the machine AT THAT MOMENT (other ranks load the same host fabric), so
+            // the choice is kept under review: the first nine calls take turns (three samples each), and afterwards
+            // two calls in every 128 go to the ways not in use; each way keeps a running average of what it cost.
+            static const int order[3] = {ZEROCOPY, HYBRID, STAGED};
+            const int c = p->host_tune_calls;
+            if (c < 9) {
+                mode = order[c % 3];
             } else {
-                static const int order[3] = {ZEROCOPY, HYBRID, STAGED};
-                mode = order[p->host_tune_calls % 3];
-                tuning = true;
+                mode = p->host_mode;
+                const int phase = (c - 9) % 128;
+                if (phase == 126 || phase == 127) {
+                    int others[2], k = 0;
+                    for (int mth = 0; mth < 3; mth++)
+                        if (mth != p->host_mode) others[k++] = mth;
+                    mode = others[phase - 126];
+                }
             }
+            tuning = true;
         }
     }
     // The three index arrays travel as ONE copy out of the pool's page-locked staging area (three copies from
@@ -974,12 +1009,18 @@ int32_t jgpt_attn_decode_append_host(jgpt_kvpool pool, int32_t layer0, int32_t n
     auto finish = [&]() {
         if (!tuning) return;
         const double us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_begin).count();
-        p->host_tune_best[mode] = std::min(p->host_tune_best[mode], us);
-        if (++p->host_tune_calls >= 9) {
+        double &avg = p->host_tune_best[mode];
+        // first nine calls: the best of a way's three samples (the very first call of a way pays one-off set-up);
+        // later: a running average that follows the machine's load
+        if (p->host_tune_calls < 9) avg = std::min(avg, us);
+        else avg = avg > 1e29 ? us : 0.75 * avg + 0.25 * us;
+        p->host_tune_calls++;
+        if (p->host_tune_calls >= 9) {
             int best = STAGED;
             for (int mth = 0; mth < 3; mth++)
                 if (p->host_tune_best[mth] < p->host_tune_best[best]) best = mth;
-            p->host_mode = best;
+            // change horses only for a clear gain: the samples are single wall-clock readings
+            if (p->host_mode < 0 || p->host_tune_best[best] < 0.93 * p->host_tune_best[p->host_mode]) p->host_mode = best;
         }
     };
     if (mode == ZEROCOPY || mode == HYBRID) {

@@ -108,6 +108,8 @@ struct Pool {
     int persistent = -1;  // < 0: automatic
     int head_group = 0;  // 0 = automatic
     int decode_mma = 0;  // 1: tensor-core consumer in the decode kernel (dhead 16)
+    int prefill_fast = 0;  // d_head-16 prefill attention with single fp16 q / p operands (JGPT_B200_PREFILL_FAST)
+    int launch_overlap = 0;  // decode attention as a programmatic dependent launch: 0 off, 1 safe subset, 2 + early K/V fetch
     // Unique per pool object (low half) and bumped when a device buffer that kernels are handed is reallocated (high
     // half): captured CUDA graphs are keyed on it, so a pool re-created at the same address never replays an old graph.
     uint64_t generation = 0;
@@ -182,6 +184,6 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
                            int max_len, float *out);
 int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v,
                             const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
-                            int n_seqs, float *out, float *out_image = nullptr, bool skip_append = false);
+                            int n_seqs, float *out, float *out_image = nullptr, bool skip_append = false, int fast_mode = -1);
 
 }  // namespace jgpt

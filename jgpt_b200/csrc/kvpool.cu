@@ -315,6 +315,8 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     p->persistent = env_int("JGPT_B200_PERSISTENT", -1);
     p->head_group = env_int("JGPT_B200_HEAD_GROUP", 0);
     p->decode_mma = env_int("JGPT_B200_DECODE_MMA", 0);
+    p->prefill_fast = env_int("JGPT_B200_PREFILL_FAST", 0);
+    p->launch_overlap = std::min(2, std::max(0, env_int("JGPT_B200_LAUNCH_OVERLAP", 0)));
     p->kv_bytes = (uint64_t)layers * n_blocks * heads * 2 * kBlockTokens * dhead * sizeof(__half);
     cudaError_t e = cudaMalloc(&p->kv, p->kv_bytes);
     if (e != cudaSuccess) {
@@ -385,13 +387,16 @@ int32_t jgpt_kvpool_storage(jgpt_kvpool h, void **dev_out, uint64_t *bytes_out) 
     return JGPT_OK;
 }
 
-int32_t jgpt_kvpool_set_tuning(jgpt_kvpool h, int32_t chunk_blocks, int32_t stages, int32_t head_group, int32_t persistent) {
+int32_t jgpt_kvpool_set_tuning(jgpt_kvpool h, int32_t chunk_blocks, int32_t stages, int32_t head_group, int32_t persistent,
+                               int32_t launch_overlap) {
     GET_POOL(p, h);
     JGPT_REQUIRE(chunk_blocks >= 0 && chunk_blocks <= 32, JGPT_ERR_INVALID_ARGUMENT, "chunk_blocks must be in [0, 32] (0 = automatic)");
     JGPT_REQUIRE(stages >= 2 && stages <= 8, JGPT_ERR_INVALID_ARGUMENT, "stages must be in [2, 8]");
     JGPT_REQUIRE(head_group >= 0 && head_group <= p->heads && (head_group == 0 || p->heads % head_group == 0),
                  JGPT_ERR_INVALID_ARGUMENT, "head_group must be 0 (automatic) or a divisor of %d", p->heads);
+    JGPT_REQUIRE(launch_overlap >= 0 && launch_overlap <= 2, JGPT_ERR_INVALID_ARGUMENT, "launch_overlap must be 0, 1 or 2");
     p->chunk_blocks = chunk_blocks, p->stages = stages, p->head_group = head_group, p->persistent = persistent;
+    p->launch_overlap = launch_overlap;
     p->generation += (uint64_t)1 << 32;  // graphs captured with the old launch shapes must not be replayed
     return JGPT_OK;
 }

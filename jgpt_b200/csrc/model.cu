@@ -65,6 +65,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
+    int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
 };
 
 static void drop_decode_graphs(Model *m) {
@@ -1093,6 +1094,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->strict = env_int("JGPT_B200_STRICT_GEMM", 0);
     m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
+    m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -1353,7 +1355,7 @@ int32_t jgpt_forward_prefill_batch(jgpt_model h, jgpt_kvpool poolh, const int32_
     }
     rc = run_layers(m, rows, paged, [&](int l, float *image, bool kv_in_cache) {
         return launch_attn_prefill(p, l, m->q, m->k, m->v, seq_ids_host, seq_starts_host, rope_offsets_host, n, m->att, image,
-                                   kv_in_cache);
+                                   kv_in_cache, m->prefill_fast);
     });
     if (rc) return rc;
     int n_sel = 0;

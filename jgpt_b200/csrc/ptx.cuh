@@ -53,6 +53,12 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 
+// Programmatic dependent launch.  griddep_wait: blocks until every grid this launch depends on has completed and its
+// memory is visible (returns at once for a launch without such a dependency).  griddep_launch_dependents: this CTA no
+// longer stands in the way of the next launch on the stream; that launch may start once every CTA has said so.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 2^x on the special-function unit (ex2.approx.ftz): max relative error 2^-22, -inf -> 0.
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;

@@ -195,6 +195,19 @@ int32_t jgpt_env_config(int32_t *kv_block_tokens_out, int32_t *kv_pool_blocks_ou
     return JGPT_OK;
 }
 
+// PCI address of a device ("0000:1b:00.0"): lets a host pin its thread and its page-locked buffers to the NUMA
+// node the GPU hangs off (/sys/bus/pci/devices/<id>/numa_node) before it allocates them.
+int32_t jgpt_device_pci_bus_id(int32_t device, char *out, int32_t cap) {
+    JGPT_REQUIRE(out && cap >= 16, JGPT_ERR_INVALID_ARGUMENT, "the bus id needs a buffer of at least 16 bytes");
+    const cudaError_t e = cudaDeviceGetPCIBusId(out, cap, device);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(JGPT_ERR_INVALID_ARGUMENT, "device %d: %s", device, cudaGetErrorString(e));
+    }
+    for (char *c = out; *c; c++) *c = (char)tolower((unsigned char)*c);
+    return JGPT_OK;
+}
+
 int32_t jgpt_ctx_stream(jgpt_ctx h, void **stream_out) {
     Ctx *c = ctx_registry().get(h);
     JGPT_REQUIRE(c, JGPT_ERR_BAD_HANDLE, "bad context handle");

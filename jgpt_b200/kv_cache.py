@@ -49,9 +49,9 @@ class KvPool:
         B.check(self._lib.jgpt_kvpool_storage(self.handle, C.byref(p), C.byref(n)))
         return p.value, n.value
 
-    def set_tuning(self, chunk_blocks=0, stages=4, head_group=0, persistent=-1):
+    def set_tuning(self, chunk_blocks=0, stages=4, head_group=0, persistent=-1, launch_overlap=0):
         """Launch shape of the decode-attention kernel on this pool (results do not depend on it)."""
-        B.check(self._lib.jgpt_kvpool_set_tuning(self.handle, chunk_blocks, stages, head_group, persistent))
+        B.check(self._lib.jgpt_kvpool_set_tuning(self.handle, chunk_blocks, stages, head_group, persistent, launch_overlap))
 
     def table_device(self):
         """(device address, row stride) of the block-table mirror, int32 [max_seqs][row stride]."""

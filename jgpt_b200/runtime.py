@@ -96,6 +96,37 @@ class Graph:
             self.handle = 0
 
 
+def bind_host_near_gpu(device: int) -> dict:
+    """Pins the calling process to the CPUs of the NUMA node the GPU hangs off, so that page-locked buffers allocated
+    afterwards (first touch) and the thread that fills them sit next to it.  With one rank per GPU on a two-socket box
+    this keeps every rank's PCIe traffic off the inter-socket link.  Returns what it found; does nothing when the
+    platform does not say (no sysfs entry, node -1, or an affinity mask that excludes the node)."""
+    import os
+
+    lib = B.load()
+    buf = C.create_string_buffer(32)
+    info = {"device": device, "bound": False}
+    if lib.jgpt_device_pci_bus_id(device, buf, 32) != 0:
+        return info
+    info["pci"] = buf.value.decode()
+    try:
+        node = int(open(f"/sys/bus/pci/devices/{info['pci']}/numa_node").read().strip())
+        info["numa_node"] = node
+        if node < 0:
+            return info
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["bound"], info["cpus"] = True, len(allowed)
+    except (OSError, ValueError):
+        pass
+    return info
+
+
 class Event:
     def __init__(self, ctx: Context):
         self.ctx = ctx
