@@ -39,8 +39,16 @@ struct DecodeParams {
     // slabs are fetched before the previous kernel has finished -- which is only legal when that kernel does not
     // write the K/V store of these layers, the block tables or the index arrays (the caller's promise).
     int overlap;
+    int stream_hint;  // 1: K/V slabs are fetched with an evict-first L2 policy
+    // 1: the launch is made of clusters of max_chunks CTAs, the chunks of one (layer, sequence, head group); their
+    // partial softmax states are merged through distributed shared memory by the CTA of chunk 0 instead of through
+    // global scratch and an arrival counter.  Every thread of the cluster passes two cluster barriers, whatever its path.
+    int cluster;
     int dynamic;    // 1: CTAs claim work items from counters[0]; 0: item = blockIdx.x + k * gridDim.x
     int *counters;  // [0] next item, [1] CTAs that have finished (the last one resets both)
+#ifdef JGPT_B200_DECODE_TRACE
+    long long *trace;  // experiments only: 8 timestamps per CTA (never compiled into the shipped library)
+#endif
 };
 
 constexpr int kMaxStages = 8;
@@ -158,6 +166,8 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     __shared__ uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
     __shared__ int s_last;
     __shared__ int s_abort_mem;
+    constexpr int kMaxHG = (384 / DH) < 30 ? (384 / DH) : 30;  // == max_head_group<DH>()
+    __shared__ float cl_part[kMaxHG * (DH + 2)];  // this CTA's partial (m, l, o[DH]) per head, cluster mode
     // Dynamic mode: the producer warp claims work items from a global counter and hands their ids to the
     // consumers through this small ring, so a resident CTA keeps its copy pipeline full across items and the
     // launch has no wave quantisation (items are a few KV blocks each, claimed as CTAs become free).
@@ -166,6 +176,10 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     volatile int *s_abort = &s_abort_mem;
 
     const int tid = threadIdx.x;
+#ifdef JGPT_B200_DECODE_TRACE
+    long long tr_gt0 = 0, tr_c0 = clock64(), tr_c1 = 0, tr_c2 = 0, tr_c3 = 0, tr_c4 = 0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tr_gt0));
+#endif
     const int n_cons = ((BT * P.HG + 31) / 32) * 32;  // consumer threads (padded to whole warps)
     const int n_cons_warps = n_cons / 32;
     const int stage_bytes = P.HG * HEAD_BYTES;
@@ -185,11 +199,17 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     }
     __syncthreads();
 
+#ifdef JGPT_B200_DECODE_TRACE
+    tr_c1 = clock64();
+#endif
     const bool is_producer = tid >= n_cons;
     // q / k_new / v_new come from the previous kernel on the stream, and the split-K scratch and counters are shared
     // with it: the consumers always wait for it.  The producer touches neither; it waits unless the caller has
     // promised that what it reads (lengths, tables, cached K/V) is not written by that kernel.
-    if (P.overlap && (!is_producer || P.overlap < 2)) griddep_wait();
+    // With overlap 2 the scalar consumers wait later still: right before they read q (see below).
+    const bool late_wait = P.overlap == 2 && !MMA;
+    if (P.overlap && !(P.overlap == 2 && is_producer) && !(late_wait && !is_producer)) griddep_wait();
+    bool waited = !late_wait || is_producer;
     uint32_t it = 0;  // KV blocks processed so far by this CTA (producer and consumers count alike)
     int stage = 0;    // it % NS, kept incrementally (no integer division in the block loop)
     uint32_t phase = 0;  // (it / NS) & 1
@@ -204,6 +224,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
         // entries are three dependent global-memory round trips): the steps are spread over the first copy
         // issues of the current item so their latency never leaves the copy ring empty.
         const int lane = tid & 31;
+        const uint64_t l2_stream = l2_policy_evict_first();
         int raw = 0;                 // pending claim (lane 0 holds the atomic's result in dynamic mode)
         int nid = -1, n_i = 0, n_z = 0, n_hg = 0, n_c = 0, n_len = 0, n_seq = 0;  // next item, partly resolved
         int cur_nb = 0, cur_entry = 0, nxt_nb = 0, nxt_entry = 0;
@@ -252,11 +273,20 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             nxt_base = (((size_t)(P.layer0 + n_z) * P.n_blocks) * P.H + (size_t)n_hg * P.HG) * (size_t)HEAD_BYTES;
         };
         step_claim(), step_resolve(), step_table();
+        bool triggered = false;
         while (nid >= 0 && !*s_abort) {
             cur_nb = nxt_nb, cur_entry = nxt_entry, cur_base = nxt_base;
             step_claim();
+            // static grids know at once whether another item follows; the work queue only after the claim resolves
+            const int nid_after_this = P.dynamic ? 0 : (raw < P.n_items ? raw : -1);
             int pending = 2;  // step_resolve, step_table still to run for the next item
             for (int j = 0; j < cur_nb; j++, it++) {
+                // Overlapped launches: once most of this CTA's copies are out -- and no further item is coming -- the next
+                // launch on the stream may move in, so that ITS first slabs arrive as this launch's last ones are consumed.
+                if (P.overlap && !triggered && nid_after_this < 0 && 5 * j >= 3 * cur_nb) {
+                    griddep_launch_dependents();
+                    triggered = true;
+                }
                 int phys = __shfl_sync(0xffffffffu, cur_entry, j);
                 if (lane == 0) {
                     if (phys < 0 || phys >= P.n_blocks) {
@@ -269,7 +299,8 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
                         mbar_expect_tx(&full_bar[s], (uint32_t)stage_bytes);
                         const unsigned char *src = reinterpret_cast<const unsigned char *>(P.kv) + cur_base +
                                                    (size_t)phys * P.H * (size_t)HEAD_BYTES;
-                        bulk_g2s(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s]);
+                        if (P.stream_hint) bulk_g2s_hint(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s], l2_stream);
+                        else bulk_g2s(smem + (size_t)s * stage_bytes, src, (uint32_t)stage_bytes, &full_bar[s]);
                     }
                 }
                 if (++stage == NS) stage = 0, phase ^= 1u;
@@ -279,11 +310,14 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             if (pending == 2) step_resolve(), pending = 1;
             if (pending == 1) step_table();
         }
-        // every copy of this CTA has been issued: the next launch on the stream may begin to move in
-        if (P.overlap) griddep_launch_dependents();
+        // every copy of this CTA has been issued: at the latest now the next launch on the stream may move in
+        if (P.overlap && !triggered) griddep_launch_dependents();
+        if (P.cluster) cluster_sync(), cluster_sync();  // the two barriers of the consumers' merge
     } else
     for (;;) {
-        if (*s_abort) break;  // a bounded wait ran out: stop taking work (status word says why)
+        // a bounded wait ran out: stop taking work (status word says why).  In cluster mode every warp must still walk
+        // through its one item to the cluster barriers; with the abort flag up its waits return at once.
+        if (*s_abort && !P.cluster) break;
         int item;
         if (!P.dynamic) {
             item = next_static;
@@ -320,11 +354,19 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
         if (!seq_ok && tid == 0) atomicOr(P.status, DEV_STATUS_BAD_SEQ);
         const size_t row = ((size_t)z * P.n + i) * (size_t)(P.H * DH);  // fp32 row of q / k / v / out
         const int head0 = hg * P.HG;
+        const int rp_raw = P.rope_pos[i];
+        if (!waited) {
+            // Late wait (overlap 2): everything the previous kernel on the stream cannot have written -- lengths, ids,
+            // RoPE position -- has been fetched above; q, k_new, v_new and every store come after the wait.
+            griddep_wait();
+            waited = true;
+        }
 
         if (b0 >= b1 || !seq_ok) {
             // Empty chunk.  A sequence without any key (len <= 0) gets a zero output row.
             if ((nblk == 0 || !seq_ok) && c == 0)
                 for (int e = tid; e < P.HG * DH; e += n_cons) P.out[row + (size_t)head0 * DH + e] = 0.f;
+            if (P.cluster) cluster_sync(), cluster_sync();
             continue;
         }
         const int nb = b1 - b0;
@@ -339,7 +381,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             // keep fp32-level accuracy.  Scores and outputs live in the 8 lanes with (lane & 3) == 0.
             static_assert(!MMA || DH == 16, "the tensor-core consumer is written for dhead 16");
             const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-            int rp = P.rope_pos[i];
+            int rp = rp_raw;
             if (rp < 0 || rp >= P.max_positions) {
                 if (tid == 0) atomicOr(P.status, DEV_STATUS_BAD_POSITION);
                 rp = 0;
@@ -561,7 +603,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
         const int hl = tid / BT, t = tid % BT;
         const bool active = hl < P.HG;
         const int h = head0 + (active ? hl : 0);
-        int rp = P.rope_pos[i];
+        int rp = rp_raw;
         if (rp < 0 || rp >= P.max_positions) {
             if (tid == 0) atomicOr(P.status, DEV_STATUS_BAD_POSITION);
             rp = 0;
@@ -639,6 +681,9 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             if (++stage == NS) stage = 0, phase ^= 1u;
             if (!aborted && !mbar_wait_bounded(&full_bar[s], ph, P.status, s_abort)) aborted = true;
             if (aborted) continue;  // keep counting blocks, touch nothing
+#ifdef JGPT_B200_DECODE_TRACE
+            if (j == 0 && tr_c2 == 0) tr_c2 = clock64();
+#endif
             const int tok = (b0 + j) * BT + t;
             if (active && tok < len_cached) {
                 const unsigned char *ktile = smem + (size_t)s * stage_bytes + (size_t)hl * HEAD_BYTES;
@@ -666,6 +711,9 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
         // After a timed-out wait the thread keeps walking the barriers below (so nobody is left
         // waiting for it) but stores nothing; the item loop ends at its next iteration.
 
+#ifdef JGPT_B200_DECODE_TRACE
+        tr_c3 = clock64();
+#endif
         // ---- merge the 16 token lanes of each head (warp shuffles) ----
         swap_halves<DH>(o, t);  // back to natural dimension order
         float M = m;
@@ -687,6 +735,41 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
 #pragma unroll
                 for (int g = 0; g < OPL; g++) P.out[row + (size_t)h * DH + g * 16 + (DH >= 16 ? t : t % DH)] = o[g] * inv;
             }
+            if (P.cluster) cluster_sync(), cluster_sync();
+            continue;
+        }
+        if (P.cluster) {
+            // ---- split-K inside a cluster: partials stay in shared memory, the CTA of chunk 0 merges them ----
+            constexpr int PS = DH + 2;
+            if (writer) {
+                float *pp = cl_part + hl * PS;
+#pragma unroll
+                for (int g = 0; g < OPL; g++) pp[2 + g * 16 + (DH >= 16 ? t : t % DH)] = o[g];
+                if (t == 0) pp[0] = M, pp[1] = l;
+            } else if (active && aborted && t == 0) {
+                cl_part[hl * PS] = -INFINITY, cl_part[hl * PS + 1] = 0.f;  // a chunk that gave up contributes nothing
+            }
+            cluster_sync();
+            if (c == 0 && writer) {
+                const float *pp = cl_part + hl * PS;
+                float Mx = -INFINITY;
+                for (int cc = 0; cc < nsplit; cc++) Mx = fmaxf(Mx, ld_cluster_f32(pp, (uint32_t)cc));
+                float L = 0.f, acc[OPL];
+#pragma unroll
+                for (int g = 0; g < OPL; g++) acc[g] = 0.f;
+                for (int cc = 0; cc < nsplit; cc++) {
+                    const float mc = ld_cluster_f32(pp, (uint32_t)cc);
+                    const float w = mc == -INFINITY ? 0.f : exp2f(mc - Mx);
+                    L = fmaf(ld_cluster_f32(pp + 1, (uint32_t)cc), w, L);
+#pragma unroll
+                    for (int g = 0; g < OPL; g++)
+                        acc[g] = fmaf(ld_cluster_f32(pp + 2 + g * 16 + (DH >= 16 ? t : t % DH), (uint32_t)cc), w, acc[g]);
+                }
+                const float inv = 1.f / fmaxf(L, 1e-12f);
+#pragma unroll
+                for (int g = 0; g < OPL; g++) P.out[row + (size_t)h * DH + g * 16 + (DH >= 16 ? t : t % DH)] = acc[g] * inv;
+            }
+            cluster_sync();  // nobody leaves (and frees its shared memory) before chunk 0 has read it
             continue;
         }
 
@@ -699,6 +782,9 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             for (int g = 0; g < OPL; g++) pp[2 + g * 16 + (DH >= 16 ? t : t % DH)] = o[g];
             if (t == 0) pp[0] = M, pp[1] = l;
         }
+#ifdef JGPT_B200_TRACE_NOMERGE
+        if (P.n > 0) continue;  // timing experiment only: partials written, nobody merges
+#endif
         __threadfence();
         named_bar_sync(1, n_cons);
         int *ticket = P.tickets + ((size_t)z * P.n + i) * P.n_hg + hg;
@@ -733,6 +819,17 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     // Abort path only: before the CTA (and its shared memory) goes away, give the bulk copies that
     // were already issued a bounded chance to land.
     __syncthreads();
+#ifdef JGPT_B200_DECODE_TRACE
+    tr_c4 = clock64();
+    if (tid == 0 && P.trace) {
+        long long gt1;
+        unsigned smid;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt1));
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        long long *tp = P.trace + (size_t)blockIdx.x * 8;
+        tp[0] = tr_gt0, tp[1] = gt1, tp[2] = tr_c1 - tr_c0, tp[3] = tr_c2 - tr_c0, tp[4] = tr_c3 - tr_c0, tp[5] = tr_c4 - tr_c0, tp[6] = smid, tp[7] = 0;
+    }
+#endif
     if (*s_abort && tid == n_cons) {
         const uint32_t first = it > (uint32_t)NS ? it - NS : 0;
         for (uint32_t idx = first; idx < it; idx++)
@@ -797,13 +894,22 @@ static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int t
     // (kMaxStages stages of a 24 KiB slab), so that no later, smaller request ever lowers the limit again.
     JGPT_CUDA_TRY(decode_opt_in_smem(kern, (fused ? 1 : 0) + (mma ? 2 : 0) + 4 * (DH == 4 ? 0 : DH == 8 ? 1 : DH == 16 ? 2 : 3),
                                      p->ctx->device));
-    if (P.overlap) {
+    if (P.overlap || P.cluster) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)grid), cfg.blockDim = dim3((unsigned)threads), cfg.dynamicSmemBytes = smem, cfg.stream = p->ctx->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr, cfg.numAttrs = 1;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (P.overlap) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            na++;
+        }
+        if (P.cluster) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = (unsigned)P.max_chunks, attr[na].val.clusterDim.y = 1, attr[na].val.clusterDim.z = 1;
+            na++;
+        }
+        cfg.attrs = attr, cfg.numAttrs = (unsigned)na;
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, P));
     } else {
         kern<<<grid, threads, smem, p->ctx->stream>>>(P);
@@ -811,6 +917,17 @@ static int32_t launch_decode_t(Pool *p, const DecodeParams &P, bool fused, int t
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
+
+#ifdef JGPT_B200_DECODE_TRACE
+static long long *g_decode_trace = nullptr;
+static int g_decode_trace_items = 0;
+extern "C" __attribute__((visibility("default"))) int jgpt_debug_decode_trace(long long *host_out, int cap_items) {
+    const int n = g_decode_trace_items < cap_items ? g_decode_trace_items : cap_items;
+    cudaDeviceSynchronize();
+    if (g_decode_trace && n > 0) cudaMemcpy(host_out, g_decode_trace, sizeof(long long) * 8 * 65536, cudaMemcpyDeviceToHost);
+    return n;
+}
+#endif
 
 // Split-K chunk length of a launch with `base` (layer, sequence, head group) triples of up to max_blocks KV blocks.
 // Two CTAs fit on an SM.  When the triples alone fill those slots the launch runs in several waves anyway and
@@ -825,7 +942,7 @@ static int pick_chunk_blocks(const Pool *p, long long base, int max_blocks) {
 }
 
 int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, const float *k_new, const float *v_new,
-                           const int *seq_ids, const int *rope_pos, const int *lens, int n, int max_len, float *out) {
+                           const int *seq_ids, const int *rope_pos, const int *lens, int n, int max_len, float *out, int overlap) {
     DecodeParams P;
     memset(&P, 0, sizeof(P));
     const int DH = p->dhead;
@@ -848,17 +965,32 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
     P.stages = p->stages;
-    P.overlap = p->launch_overlap;
+    P.overlap = overlap >= 0 ? overlap : p->launch_overlap;
+    P.stream_hint = p->stream_hint;
     P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
     const long long items = (long long)n_layers * n * P.n_hg * P.max_chunks;
     JGPT_REQUIRE(items < (1ll << 31), JGPT_ERR_INVALID_ARGUMENT, "too many work items (%lld)", items);
     P.n_items = (int)items;
-    if (P.max_chunks > 1) {
+    // The chunks of one sequence as one thread-block cluster (up to the portable size of 8): merge in shared memory.
+    // Not for the work queue (its CTAs take several items) nor for the tensor-core consumer (its own epilogue).
+    P.cluster = (p->cluster_merge && !dynamic && !p->decode_mma && P.max_chunks >= 2 && P.max_chunks <= 8) ? 1 : 0;
+    if (P.max_chunks > 1 && !P.cluster) {
         int32_t rc = pool_ensure_split_scratch(p, (uint64_t)n_layers * n * P.max_chunks * p->heads * (DH + 2),
                                                (uint64_t)n_layers * n * P.n_hg);
         if (rc) return rc;
     }
     P.partials = p->d_partials, P.tickets = p->d_tickets;
+#ifdef JGPT_B200_DECODE_TRACE
+    {
+        static long long *d_trace = nullptr;
+        static int launch_no = 0;
+        if (!d_trace) cudaMalloc(&d_trace, sizeof(long long) * 8 * 65536);
+        // two halves used in turn: the last two launches can be compared (where did the second start / the first end)
+        P.trace = P.n_items <= 32768 ? d_trace + (size_t)(launch_no & 1) * 8 * 32768 : nullptr;
+        launch_no++;
+        g_decode_trace = d_trace, g_decode_trace_items = P.n_items;
+    }
+#endif
     const int n_cons = ((kBlockTokens * P.HG + 31) / 32) * 32;
     const int threads = n_cons + 32;
     const size_t stage_bytes = (size_t)P.HG * 2 * kBlockTokens * DH * 2;
@@ -1191,6 +1323,7 @@ static int32_t launch_attn_decode_static(Pool *p, int layer, const float *q, con
     P.n = n, P.H = p->heads, P.layer0 = layer, P.n_layers = 1, P.mbs = p->max_blocks_per_seq;
     P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
     // same launch shape as jgpt_attn_decode gives a one-layer call (small batches get lighter CTAs)
+    P.stream_hint = p->stream_hint;
     P.HG = pick_head_group(p->heads, DH, p->head_group, (long long)n, 2ll * p->ctx->sm_count);
     P.n_hg = p->heads / P.HG;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);

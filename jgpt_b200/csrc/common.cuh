@@ -109,6 +109,8 @@ struct Pool {
     int head_group = 0;  // 0 = automatic
     int decode_mma = 0;  // 1: tensor-core consumer in the decode kernel (dhead 16)
     int prefill_fast = 0;  // d_head-16 prefill attention with single fp16 q / p operands (JGPT_B200_PREFILL_FAST)
+    int cluster_merge = 1;  // split-K chunks of a sequence as a thread-block cluster, merged in shared memory (JGPT_B200_CLUSTER_MERGE=0: off)
+    int stream_hint = 1;  // decode attention fetches K/V with an evict-first L2 policy (JGPT_B200_STREAM_HINT=0: off)
     int launch_overlap = 0;  // decode attention as a programmatic dependent launch: 0 off, 1 safe subset, 2 + early K/V fetch
     // Unique per pool object (low half) and bumped when a device buffer that kernels are handed is reallocated (high
     // half): captured CUDA graphs are keyed on it, so a pool re-created at the same address never replays an old graph.
@@ -181,7 +183,7 @@ int32_t launch_kv_gather(Pool *p, int layer, int seq, int len, int max_seq_len, 
 int32_t launch_kv_scrub(Pool *p, const std::vector<int> &blocks);
 int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, const float *k_new,
                            const float *v_new, const int *seq_ids, const int *rope_pos, const int *lens, int n,
-                           int max_len, float *out);
+                           int max_len, float *out, int overlap = -1);  // overlap < 0: the pool's setting
 int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, const float *v,
                             const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
                             int n_seqs, float *out, float *out_image = nullptr, bool skip_append = false, int fast_mode = -1);

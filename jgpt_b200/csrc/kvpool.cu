@@ -316,6 +316,8 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     p->head_group = env_int("JGPT_B200_HEAD_GROUP", 0);
     p->decode_mma = env_int("JGPT_B200_DECODE_MMA", 0);
     p->prefill_fast = env_int("JGPT_B200_PREFILL_FAST", 0);
+    p->stream_hint = env_int("JGPT_B200_STREAM_HINT", 1);
+    p->cluster_merge = env_int("JGPT_B200_CLUSTER_MERGE", 1);
     p->launch_overlap = std::min(2, std::max(0, env_int("JGPT_B200_LAUNCH_OVERLAP", 0)));
     p->kv_bytes = (uint64_t)layers * n_blocks * heads * 2 * kBlockTokens * dhead * sizeof(__half);
     cudaError_t e = cudaMalloc(&p->kv, p->kv_bytes);

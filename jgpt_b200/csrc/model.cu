@@ -9,6 +9,7 @@
 // output element over k in ascending order in one thread (mul, then add), which is bit-reproducible against a
 // scalar CPU loop.
 #include "common.cuh"
+#include "ptx.cuh"
 #include "gemm_umma.cuh"
 
 #include <algorithm>
@@ -65,6 +66,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
+    int step_overlap = 0;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP, 0..3)
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
 };
 
@@ -377,6 +379,10 @@ struct SmallFuse {
     float *ss_out;
     int parts_in;
     float eps;
+    // Programmatic dependent launch.  bit 0: this launch carries the attribute, i.e. it may have started before the
+    // previous kernel on the stream finished: wait for that kernel before touching memory.  bit 1: let the NEXT
+    // launch on the stream move in early (it waits for this kernel itself before it reads this kernel's output).
+    int pdl = 0;
 };
 
 // MT = 2: 32-row tiles (two MMA row blocks per warp share every weight fragment) for the larger decode batches.
@@ -392,6 +398,8 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     const float *__restrict__ W = z == 0 ? B.W[0] : (z == 1 ? B.W[1] : B.W[2]);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (F.pdl & 1) griddep_wait();
+    if (F.pdl & 2) griddep_launch_dependents();  // the whole grid is resident: the next launch cannot get in its way
 
     // this thread's copy slots: MT 16-byte chunks of A (rows a_r, a_r + 16), two of W per k tile
     const int a_r = tid >> 4, a_c = (tid & 15) * 4;
@@ -920,12 +928,17 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     JGPT_CUDA_TRY(opt_in_shared_memory(m->ctx));
     GemmBatch B;
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.blockDim = dim3(256), cfg.stream = m->ctx->stream, cfg.attrs = attr, cfg.numAttrs = (fuse.pdl & 1) ? 1 : 0;
     if (M >= small_rows_for_wide_tiles()) {
-        dim3 grid((N + 31) / 32, (M + 31) / 32, nb);
-        gemm_tc_small_kernel<4, NORM, EPI, 2><<<grid, 256, gemm_small_smem_bytes<4, 2>(), m->ctx->stream>>>(A, B, M, K, N, rowsel, fuse);
+        cfg.gridDim = dim3((N + 31) / 32, (M + 31) / 32, nb), cfg.dynamicSmemBytes = gemm_small_smem_bytes<4, 2>();
+        JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 2>, A, B, M, K, N, rowsel, fuse));
     } else {
-        dim3 grid((N + 31) / 32, (M + 15) / 16, nb);
-        gemm_tc_small_kernel<4, NORM, EPI, 1><<<grid, 256, gemm_small_smem_bytes<4, 1>(), m->ctx->stream>>>(A, B, M, K, N, rowsel, fuse);
+        cfg.gridDim = dim3((N + 31) / 32, (M + 15) / 16, nb), cfg.dynamicSmemBytes = gemm_small_smem_bytes<4, 1>();
+        JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 1>, A, B, M, K, N, rowsel, fuse));
     }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
@@ -938,7 +951,11 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         const LayerW &y = m->L[(size_t)l];
         int32_t rc;
         // x's sums of squares: one partial per row from the embedding, `parts` from a residual projection
-        const SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps};
+        // Launch overlap inside the step (m->step_overlap): 1 = the attention launch moves in under the Q,K,V product
+        // (its copy warp fetches tables and K/V slabs meanwhile; that product writes q / k / v only); 2 = the Wo product
+        // moves in under the attention's tail as well; 3 = every projection of the layer chain.
+        const int ov = m->step_overlap;
+        const SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps, (ov >= 1 ? 2 : 0) | ((ov >= 3 && l > 0) ? 1 : 0)};
         const float *Wqkv[3] = {y.wq, y.wk, y.wv};
         float *Cqkv[3] = {m->q, m->k, m->v};
         if ((rc = small_launch<true, 0>(m, m->x, rows, D, D, 3, Wqkv, Cqkv, nullptr, nullptr, n1))) return rc;
@@ -946,14 +963,17 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         const float *Wo[1] = {y.wo};
         float *Cx[1] = {m->x};
         const float *Rx[1] = {m->x};  // x1 = x + attn.Wo (each element read then written by the same thread)
-        if ((rc = small_launch<false, 1>(m, m->att, rows, D, D, 1, Wo, Cx, Rx, nullptr, SmallFuse{nullptr, nullptr, m->ss_b, 0, 0.f}))) return rc;
+        if ((rc = small_launch<false, 1>(m, m->att, rows, D, D, 1, Wo, Cx, Rx, nullptr,
+                                         SmallFuse{nullptr, nullptr, m->ss_b, 0, 0.f, (ov >= 2 ? 1 : 0) | (ov >= 3 ? 2 : 0)}))) return rc;
         const float *pair = nullptr;
         if ((rc = pair_interleaved(m, y.w1, y.w3, D, F, &pair))) return rc;
         const float *Wp[1] = {pair};
         float *Ch[1] = {m->h1};
-        if ((rc = small_launch<true, 2>(m, m->x, rows, D, 2 * F, 1, Wp, Ch, nullptr, nullptr, SmallFuse{y.norm2, m->ss_b, nullptr, parts, m->eps}))) return rc;
+        if ((rc = small_launch<true, 2>(m, m->x, rows, D, 2 * F, 1, Wp, Ch, nullptr, nullptr,
+                                        SmallFuse{y.norm2, m->ss_b, nullptr, parts, m->eps, ov >= 3 ? 3 : 0}))) return rc;
         const float *W2[1] = {y.w2};
-        if ((rc = small_launch<false, 1>(m, m->h1, rows, F, D, 1, W2, Cx, Rx, nullptr, SmallFuse{nullptr, nullptr, m->ss_a, 0, 0.f}))) return rc;
+        if ((rc = small_launch<false, 1>(m, m->h1, rows, F, D, 1, W2, Cx, Rx, nullptr,
+                                         SmallFuse{nullptr, nullptr, m->ss_a, 0, 0.f, ov >= 3 ? 3 : 0}))) return rc;
     }
     return JGPT_OK;
 }
@@ -1056,6 +1076,9 @@ int32_t jgpt_matmul_device(jgpt_ctx ctxh, const float *a_dev, const float *b_dev
     JGPT_CUDA_TRY(make_current(c));
     const float *W[1] = {b_dev};
     float *C[1] = {c_dev};
+    // Two getenv calls per call (a test knob that tests flip between calls; ~100 ns).  The stateless primitive has to
+    // re-tile its weight operand on every call because nothing says the caller has not changed it -- the forward-step
+    // entry points keep tiled weights cached instead.
     const int min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     const int strict = env_int("JGPT_B200_STRICT_GEMM", 0);
     if (strict || min_rows <= 0 || M < min_rows || !umma::shape_ok(K, N))
@@ -1095,6 +1118,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
+    m->step_overlap = std::min(3, std::max(0, env_int("JGPT_B200_STEP_OVERLAP", 0)));
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -1453,7 +1477,8 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
         embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
         int32_t r2 = run_layers(m, n, nullptr, [&](int l, float *, bool) {
-            return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att);
+            return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att,
+                                      (m->step_overlap >= 1 && small_mode(m, n)) ? 2 : 0);
         });
         if (r2) return r2;
         r2 = lm_head(m, n, 0, spec);

@@ -48,10 +48,39 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gmem_src, u
                  "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+// The same copy for data that is read once (a K/V slab of a decode step): the lines are marked evict-first in L2, so a
+// stream of hundreds of megabytes does not push the small, hot arrays (lengths, block tables, q, split-K partials)
+// out of the cache between launches.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+                 : "memory");
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+
+// Thread-block clusters: the CTAs of one cluster are co-resident and can read each other's shared memory.
+// cluster_sync: every thread of every CTA of the cluster (exited threads count as arrived) meets here; shared-memory
+// writes made before it are visible to the other CTAs after it.  A hardware barrier like bar.sync, not a spin on memory.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Reads a float at the same shared-memory offset in the CTA of rank `rank` of this cluster.
+__device__ __forceinline__ float ld_cluster_f32(const float *local_smem, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
 
 // Programmatic dependent launch.  griddep_wait: blocks until every grid this launch depends on has completed and its
 // memory is visible (returns at once for a launch without such a dependency).  griddep_launch_dependents: this CTA no

@@ -434,3 +434,37 @@ def test_rolling_window_generation_matches_the_oracles_rolling_specification(ctx
             gm.forwardDecodeBatch(strict, [s], [1], [30], [MS])
     finally:
         strict.close()
+
+
+@pytest.mark.parametrize("level", [1, 2, 3])
+def test_overlapped_launches_inside_the_decode_step_change_nothing(ctx, level, monkeypatch):
+    """JGPT_B200_STEP_OVERLAP: kernels of the decode step start while their predecessor drains (programmatic dependent
+    launches; the attention's copy warp already fetches K/V under the Q,K,V product).  Logits, sampled ids and the cache
+    payload are bit-identical to the ordinary step, eager and replayed as a graph."""
+    om = O.Model(96, 80, 64, 4, 3, 128, eps=1e-5).init_random(seed=4, std=0.15)
+    outs = []
+    for lv in (0, level):
+        monkeypatch.setenv("JGPT_B200_STEP_OVERLAP", str(lv))
+        gm = GPTModel(ctx, 96, 80, 64, 4, 3, 128, rmsNormEps=1e-5)
+        gm.setParameters(om.tensors())
+        pool = gm.newPool(n_blocks=3 * 5, max_seqs=3)
+        try:
+            seqs = [pool.seq_alloc() for _ in range(3)]
+            prompts = [np.array([(i * 7 + s) % 96 for i in range(n)], np.int32) for s, n in enumerate((33, 5, 16))]
+            _, toks = gm.forwardPrefillBatch(pool, seqs, prompts)
+            lens = np.array([33, 5, 16], np.int32)
+            rec = []
+            for step in range(6):  # step 0 eager, step 1 captures, later steps replay the graph
+                logits, toks = gm.forwardDecodeBatch(pool, seqs, toks, lens, lens)
+                lens = lens + 1
+                rec.append((logits.copy(), toks.copy()))
+            kd, vd = ctx.alloc((4, 80, 16)), ctx.alloc((4, 80, 16))
+            pool.gather(2, seqs[0], int(lens[0]), 80, kd, vd)
+            outs.append((rec, kd.to_host(), vd.to_host()))
+        finally:
+            pool.close(), gm.close()
+    om.close()
+    (r0, k0, v0), (r1, k1, v1) = outs
+    for (l0, t0), (l1, t1) in zip(r0, r1):
+        assert np.array_equal(l0, l1) and np.array_equal(t0, t1)
+    assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
