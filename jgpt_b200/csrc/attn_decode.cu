@@ -952,7 +952,14 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.status = p->ctx->d_status;
     P.n = n, P.H = p->heads, P.layer0 = layer0, P.n_layers = n_layers, P.mbs = p->max_blocks_per_seq;
     P.n_blocks = p->n_blocks, P.max_seqs = p->max_seqs, P.max_positions = p->max_positions;
-    P.HG = pick_head_group(p->heads, DH, p->head_group, (long long)n_layers * n, 2ll * p->ctx->sm_count);
+    const int ov = overlap >= 0 ? overlap : p->launch_overlap;
+    // Head group and ring depth.  An overlapped single-layer launch (the per-layer decode loop) runs best with all
+    // heads in one CTA (one 24 KiB slab per copy) and a three-stage ring, so that three CTAs fit on an SM and the next
+    // launch's CTAs can move in beside the ones still draining: 20.7 us per layer at batch 64 / context 1024 against
+    // 22.7 us for the ordinary launch (6-8 heads per CTA, four stages).
+    const bool overlapped_single = ov >= 1 && n_layers == 1 && p->persistent <= 0;
+    P.HG = overlapped_single ? pick_head_group(p->heads, DH, p->head_group)
+                             : pick_head_group(p->heads, DH, p->head_group, (long long)n_layers * n, 2ll * p->ctx->sm_count);
     P.n_hg = p->heads / P.HG;
     const int max_blocks = std::min(p->max_blocks_per_seq, (max_len + kBlockTokens - 1) / kBlockTokens);
     // Work distribution.  Default (persistent <= 0): one CTA per work item, the hardware block scheduler hands
@@ -964,8 +971,8 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.chunk_blocks = p->chunk_blocks > 0 ? p->chunk_blocks : pick_chunk_blocks(p, (long long)n_layers * n * P.n_hg, max_blocks);
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
-    P.stages = p->stages;
-    P.overlap = overlap >= 0 ? overlap : p->launch_overlap;
+    P.stages = p->stages > 0 ? p->stages : (overlapped_single ? 3 : 4);
+    P.overlap = ov;
     P.stream_hint = p->stream_hint;
     P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
     const long long items = (long long)n_layers * n * P.n_hg * P.max_chunks;
@@ -973,7 +980,11 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     P.n_items = (int)items;
     // The chunks of one sequence as one thread-block cluster (up to the portable size of 8): merge in shared memory.
     // Not for the work queue (its CTAs take several items) nor for the tensor-core consumer (its own epilogue).
-    P.cluster = (p->cluster_merge && !dynamic && !p->decode_mma && P.max_chunks >= 2 && P.max_chunks <= 8) ? 1 : 0;
+    // Only for launches of a wave or two: there the merge's global round trips are a visible part of the launch (per-layer
+    // launch at batch 64 / context 1024: 24.1 -> 22.7 us).  A launch of many waves hides them behind other CTAs' copies,
+    // and co-scheduling pairs of CTAs costs it more than it saves (12-layer launch: 198 us without, 202 us with).
+    P.cluster = (p->cluster_merge && !dynamic && !p->decode_mma && P.max_chunks >= 2 && P.max_chunks <= 8 &&
+                 items <= 4ll * p->ctx->sm_count) ? 1 : 0;
     if (P.max_chunks > 1 && !P.cluster) {
         int32_t rc = pool_ensure_split_scratch(p, (uint64_t)n_layers * n * P.max_chunks * p->heads * (DH + 2),
                                                (uint64_t)n_layers * n * P.n_hg);
@@ -1330,7 +1341,7 @@ static int32_t launch_attn_decode_static(Pool *p, int layer, const float *q, con
     P.chunk_blocks = p->chunk_blocks > 0 ? p->chunk_blocks : pick_chunk_blocks(p, (long long)n * P.n_hg, max_blocks);
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
-    P.stages = p->stages;
+    P.stages = p->stages > 0 ? p->stages : 4;
     P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
     const long long items = (long long)n * P.n_hg * P.max_chunks;
     JGPT_REQUIRE(items < (1ll << 31), JGPT_ERR_INVALID_ARGUMENT, "too many work items (%lld)", items);

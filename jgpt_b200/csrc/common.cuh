@@ -104,14 +104,14 @@ struct Pool {
     uint64_t clock = 0;
     // launch tuning (read once from the environment at creation)
     int chunk_blocks = 0;  // 0 = automatic
-    int stages = 4;
+    int stages = 0;  // copy-ring stages, 0 = automatic
     int persistent = -1;  // < 0: automatic
     int head_group = 0;  // 0 = automatic
     int decode_mma = 0;  // 1: tensor-core consumer in the decode kernel (dhead 16)
     int prefill_fast = 0;  // d_head-16 prefill attention with single fp16 q / p operands (JGPT_B200_PREFILL_FAST)
     int cluster_merge = 1;  // split-K chunks of a sequence as a thread-block cluster, merged in shared memory (JGPT_B200_CLUSTER_MERGE=0: off)
     int stream_hint = 1;  // decode attention fetches K/V with an evict-first L2 policy (JGPT_B200_STREAM_HINT=0: off)
-    int launch_overlap = 0;  // decode attention as a programmatic dependent launch: 0 off, 1 safe subset, 2 + early K/V fetch
+    int launch_overlap = 1;  // decode attention as a programmatic dependent launch: 0 off, 1 safe subset, 2 + early K/V fetch
     // Unique per pool object (low half) and bumped when a device buffer that kernels are handed is reallocated (high
     // half): captured CUDA graphs are keyed on it, so a pool re-created at the same address never replays an old graph.
     uint64_t generation = 0;

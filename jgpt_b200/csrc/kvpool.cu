@@ -311,14 +311,15 @@ int32_t jgpt_kvpool_create(jgpt_ctx ctxh, int32_t layers, int32_t heads, int32_t
     p->layers = layers, p->heads = heads, p->dhead = dhead, p->n_blocks = n_blocks, p->max_seqs = max_seqs;
     p->max_blocks_per_seq = max_blocks_per_seq, p->max_positions = max_positions, p->rope_base = rope_base;
     p->chunk_blocks = std::min(32, std::max(0, env_int("JGPT_B200_CHUNK_BLOCKS", 0)));  // 0 = automatic
-    p->stages = std::min(8, std::max(2, env_int("JGPT_B200_STAGES", 4)));
+    p->stages = env_int("JGPT_B200_STAGES", 0);  // 0 = automatic
+    if (p->stages != 0) p->stages = std::min(8, std::max(2, p->stages));
     p->persistent = env_int("JGPT_B200_PERSISTENT", -1);
     p->head_group = env_int("JGPT_B200_HEAD_GROUP", 0);
     p->decode_mma = env_int("JGPT_B200_DECODE_MMA", 0);
     p->prefill_fast = env_int("JGPT_B200_PREFILL_FAST", 0);
     p->stream_hint = env_int("JGPT_B200_STREAM_HINT", 1);
     p->cluster_merge = env_int("JGPT_B200_CLUSTER_MERGE", 1);
-    p->launch_overlap = std::min(2, std::max(0, env_int("JGPT_B200_LAUNCH_OVERLAP", 0)));
+    p->launch_overlap = std::min(2, std::max(0, env_int("JGPT_B200_LAUNCH_OVERLAP", 1)));
     p->kv_bytes = (uint64_t)layers * n_blocks * heads * 2 * kBlockTokens * dhead * sizeof(__half);
     cudaError_t e = cudaMalloc(&p->kv, p->kv_bytes);
     if (e != cudaSuccess) {
@@ -393,7 +394,7 @@ int32_t jgpt_kvpool_set_tuning(jgpt_kvpool h, int32_t chunk_blocks, int32_t stag
                                int32_t launch_overlap) {
     GET_POOL(p, h);
     JGPT_REQUIRE(chunk_blocks >= 0 && chunk_blocks <= 32, JGPT_ERR_INVALID_ARGUMENT, "chunk_blocks must be in [0, 32] (0 = automatic)");
-    JGPT_REQUIRE(stages >= 2 && stages <= 8, JGPT_ERR_INVALID_ARGUMENT, "stages must be in [2, 8]");
+    JGPT_REQUIRE(stages == 0 || (stages >= 2 && stages <= 8), JGPT_ERR_INVALID_ARGUMENT, "stages must be 0 (automatic) or in [2, 8]");
     JGPT_REQUIRE(head_group >= 0 && head_group <= p->heads && (head_group == 0 || p->heads % head_group == 0),
                  JGPT_ERR_INVALID_ARGUMENT, "head_group must be 0 (automatic) or a divisor of %d", p->heads);
     JGPT_REQUIRE(launch_overlap >= 0 && launch_overlap <= 2, JGPT_ERR_INVALID_ARGUMENT, "launch_overlap must be 0, 1 or 2");

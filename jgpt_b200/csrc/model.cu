@@ -66,7 +66,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
-    int step_overlap = 0;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP, 0..3)
+    int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = by batch size)
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
 };
 
@@ -944,6 +944,12 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     return JGPT_OK;
 }
 
+// How far the launches of a decode step overlap.  Measured on the JGPT-35M shapes (ms per step at batch 1 / 64 / 256):
+// level 0: 0.475 / 0.625 / 1.270; 1: 0.455 / 0.610 / 1.257; 2: 0.447 / 0.653 / 1.295; 3: 0.444 / 0.677 / 1.353 --
+// with a handful of rows every kernel is a latency chain and letting each move in early pays; with full batches the
+// early CTAs only take room from the kernel that is still working.
+static int step_overlap_level(const Model *m, int rows) { return m->step_overlap >= 0 ? m->step_overlap : (rows <= 16 ? 3 : 1); }
+
 template <class AttnFn>
 static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
     const int D = m->d_model, F = m->d_ff, parts = (D + 31) / 32;
@@ -954,7 +960,7 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         // Launch overlap inside the step (m->step_overlap): 1 = the attention launch moves in under the Q,K,V product
         // (its copy warp fetches tables and K/V slabs meanwhile; that product writes q / k / v only); 2 = the Wo product
         // moves in under the attention's tail as well; 3 = every projection of the layer chain.
-        const int ov = m->step_overlap;
+        const int ov = step_overlap_level(m, rows);
         const SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps, (ov >= 1 ? 2 : 0) | ((ov >= 3 && l > 0) ? 1 : 0)};
         const float *Wqkv[3] = {y.wq, y.wk, y.wv};
         float *Cqkv[3] = {m->q, m->k, m->v};
@@ -1118,7 +1124,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
-    m->step_overlap = std::min(3, std::max(0, env_int("JGPT_B200_STEP_OVERLAP", 0)));
+    m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = by batch size
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -1478,7 +1484,7 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
         int32_t r2 = run_layers(m, n, nullptr, [&](int l, float *, bool) {
             return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att,
-                                      (m->step_overlap >= 1 && small_mode(m, n)) ? 2 : 0);
+                                      (small_mode(m, n) && step_overlap_level(m, n) >= 1) ? 2 : -1);
         });
         if (r2) return r2;
         r2 = lm_head(m, n, 0, spec);

@@ -49,7 +49,7 @@ class KvPool:
         B.check(self._lib.jgpt_kvpool_storage(self.handle, C.byref(p), C.byref(n)))
         return p.value, n.value
 
-    def set_tuning(self, chunk_blocks=0, stages=4, head_group=0, persistent=-1, launch_overlap=0):
+    def set_tuning(self, chunk_blocks=0, stages=0, head_group=0, persistent=-1, launch_overlap=1):
         """Launch shape of the decode-attention kernel on this pool (results do not depend on it)."""
         B.check(self._lib.jgpt_kvpool_set_tuning(self.handle, chunk_blocks, stages, head_group, persistent, launch_overlap))
 

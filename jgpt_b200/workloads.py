@@ -113,26 +113,46 @@ def run_prefill(ctx, batch=32, seq_len=1024, repeats=3):
             _, nxt = model.forwardPrefillBatch(pool, seqs, prompts)
             e1.record()
             best = min(best, e0.elapsed_ms(e1))
-        # attention alone on the same shapes
+        # attention alone on the same shapes: the exact mode (fp16 high + low operands, the standalone entry point's
+        # default) and the single-fp16 mode the model's forward uses
+        import os
+
         n_rows = batch * seq_len
         q = ctx.alloc((n_rows, D_MODEL))
         q.copy_from(rng.standard_normal((n_rows, D_MODEL), dtype=np.float32))
         out = ctx.alloc((n_rows, D_MODEL))
         starts = np.arange(batch + 1, dtype=np.int32) * seq_len
         ro = np.zeros(batch, np.int32)
-        for _ in range(2):
-            pool.attn_prefill(0, q, q, q, seqs, starts, ro, out)
-        ctx.synchronize()
-        e0.record()
-        for layer in range(LAYERS):
-            pool.attn_prefill(layer, q, q, q, seqs, starts, ro, out)
-        e1.record()
-        attn_ms = e0.elapsed_ms(e1)
+        attn = {}
+        for label, fast in (("exact", "0"), ("fast", "1")):
+            old_env = os.environ.get("JGPT_B200_PREFILL_FAST")
+            os.environ["JGPT_B200_PREFILL_FAST"] = fast
+            try:
+                p2 = model.newPool(n_blocks=batch * seq_len // 16, max_seqs=batch)
+            finally:
+                if old_env is None:
+                    os.environ.pop("JGPT_B200_PREFILL_FAST")
+                else:
+                    os.environ["JGPT_B200_PREFILL_FAST"] = old_env
+            s2 = [p2.seq_alloc() for _ in range(batch)]
+            for s in s2:
+                p2.reserve(s, seq_len)
+            for _ in range(2):
+                p2.attn_prefill(0, q, q, q, s2, starts, ro, out)
+            ctx.synchronize()
+            e0.record()
+            for layer in range(LAYERS):
+                p2.attn_prefill(layer, q, q, q, s2, starts, ro, out)
+            e1.record()
+            attn[label] = e0.elapsed_ms(e1)
+            p2.close()
+        attn_ms = attn["fast"]
         flops = 12 * batch * HEADS * 2.0 * seq_len * seq_len * DHEAD  # causal: (4 S^2 Dh)/2 per (seq, head), 12 layers
         return {
             "workload": f"causal prefill filling the paged cache: batch {batch} x {seq_len}, 12 layers, 24 heads, d_head 16 (ids seed 7)",
             "full_model_ms": best, "prompt_tokens_per_s": n_rows / (best * 1e-3),
-            "attention_append_12_layers_ms": attn_ms, "attention_tflops_causal": flops / (attn_ms * 1e-3) / 1e12,
+            "attention_append_12_layers_ms": attn_ms, "attention_append_12_layers_ms_exact_mode": attn["exact"],
+            "attention_tflops_causal": flops / (attn_ms * 1e-3) / 1e12,
             "next_tokens_head": nxt[:4].tolist(), "timing": "CUDA events on the library stream, best of %d" % repeats,
         }
     finally:
