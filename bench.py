@@ -556,6 +556,12 @@ def run_secondary(args, rank, world, local_rank):
         line.update(W.run_prefill(ctx))
     elif args.workload == "kvstore":
         line.update(W.run_kvstore(ctx))
+    elif args.workload == "phases":
+        pool, seqs, _ = build_workload(ctx, rank)
+        line["workload"] = "per-CTA phase timing of per-layer decode-attention launches (batch 64, context 1024; trace build)"
+        line["overlap_2"] = W.run_phases(ctx, pool, seqs, BATCH, LAYERS, D, CTX_LEN, overlap=2)
+        line["overlap_0"] = W.run_phases(ctx, pool, seqs, BATCH, LAYERS, D, CTX_LEN, overlap=0)
+        pool.close()
     elif args.workload == "contbatch":
         uid = None
         if world > 1:
@@ -597,7 +603,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="device-resident timing only (used under a profiler)")
     ap.add_argument("--per-layer", action="store_true", help="with --quick: one launch per layer instead of one per step")
     ap.add_argument("--batch", type=int, default=64, help="sequences per step for --workload decodestep")
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore"],
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore", "phases"],
                     help="microbench (default) is the headline KV-append + decode-attention step; the others are the "
                          "remaining named configurations (reported, not the contract line)")
     args = ap.parse_args()

@@ -33,9 +33,9 @@ def _deps_mtime():
     return max(os.path.getmtime(f) for f in files)
 
 
-def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(LIBDIR, os.path.basename(src)[:-3] + ".o")
-    cmd = [NVCC, *ARCH, *CFLAGS, "-c", src, "-o", obj]
+def _compile(src: str, verbose: bool, defines=(), tag: str = "") -> str:
+    obj = os.path.join(LIBDIR, os.path.basename(src)[:-3] + tag + ".o")
+    cmd = [NVCC, *ARCH, *CFLAGS, *[f"-D{d}" for d in defines], "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -64,5 +64,26 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TRACE_LIB = os.path.join(LIBDIR, "libjgpt_b200_trace.so")
+
+
+def build_trace() -> str:
+    """The same library with in-kernel phase timing compiled into the decode-attention kernel
+    (``-DJGPT_B200_DECODE_TRACE``): every CTA records when it started, when its first K/V slab arrived, when its block
+    loop ended and when it left.  For ``bench.py --workload phases`` only; never the library a host should load."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        objs = list(ex.map(lambda s: _compile(s, False, ("JGPT_B200_DECODE_TRACE",), ".trace"), _sources()))
+    r = subprocess.run([NVCC, *ARCH, "-shared", "-o", TRACE_LIB, *objs, "-ccbin", "/usr/bin/g++", "-ldl"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    for o in objs:
+        os.remove(o)
+    return TRACE_LIB
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build_trace())
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

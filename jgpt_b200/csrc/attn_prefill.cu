@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) kv_append_rows_kernel(const PrefillParams
 // dhead 16: tensor-core kernel
 // ------------------------------------------------------------------------------------------------
 constexpr int kQTile = 64;     // query rows per CTA (4 warps x 16)
-constexpr int kStageBlocks = 4;  // KV blocks per pipeline stage (64 keys, 4 KiB)
+constexpr int kStageBlocks = 8;  // KV blocks per pipeline stage (128 keys, 8 KiB)
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -124,8 +124,8 @@ __device__ __forceinline__ void split_half2(float a, float b, uint32_t &hi, uint
 // FAST: Q and the probabilities enter the tensor cores as single fp16 values instead of fp16 high + low pairs: half the
 // MMAs and none of the split arithmetic.  The cached K / V are fp16 anyway, so the only new error is the rounding of q
 // (2^-11 relative, i.e. ~1e-3 in a log2-domain score of magnitude a few) and of p (2^-11 relative): attention outputs
-// stay within ~2e-4 of the exact mode on N(0,1) inputs and logits of the JGPT-35M shapes within 5e-4 of an fp32 CPU
-// evaluation, against a budget of 2e-3.  The exact mode (2e-5) remains the default of the standalone entry point.
+// stay within ~1e-3 of the exact mode on N(0,1) inputs (whose scores are far larger than a model's: measured 6.9e-4) and
+// the logits of the JGPT-35M shapes within 5e-4 of an fp32 CPU evaluation, against a budget of 2e-3.  The exact mode (2e-5) remains the default of the standalone entry point.
 template <bool FAST>
 __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillParams P) {
     constexpr int DH = 16, BT = kBlockTokens, TILE_BYTES = 2 * BT * DH * 2;  // 1 KiB: K tile | V tile
@@ -215,6 +215,60 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillPara
             for (int b = 0; b < nb; b++) {
                 const int kb = c * kStageBlocks + b;
                 if (kb > diag) break;
+                if constexpr (FAST) {
+                    // Two KV blocks (32 keys) below the diagonal share one online-softmax update: one running maximum,
+                    // one correction factor and one rescale of the output tile instead of two.
+                    if (b + 1 < nb && kb + 1 < diag) {
+                        const unsigned char *t0 = &tiles[c & 1][b][0], *t1 = &tiles[c & 1][b + 1][0];
+                        uint32_t k0[4], k1[4];
+                        ldmatrix_x4(k0, t0 + k_off);
+                        ldmatrix_x4(k1, t1 + k_off);
+                        float s4[4][4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+#pragma unroll
+                            for (int e = 0; e < 4; e++) s4[j][e] = 0.f;
+                        mma_16816(s4[0], a_hi, k0[0], k0[1]);
+                        mma_16816(s4[1], a_hi, k0[2], k0[3]);
+                        mma_16816(s4[2], a_hi, k1[0], k1[1]);
+                        mma_16816(s4[3], a_hi, k1[2], k1[3]);
+                        float mxA = fmaxf(fmaxf(fmaxf(s4[0][0], s4[0][1]), fmaxf(s4[1][0], s4[1][1])),
+                                          fmaxf(fmaxf(s4[2][0], s4[2][1]), fmaxf(s4[3][0], s4[3][1])));
+                        float mxB = fmaxf(fmaxf(fmaxf(s4[0][2], s4[0][3]), fmaxf(s4[1][2], s4[1][3])),
+                                          fmaxf(fmaxf(s4[2][2], s4[2][3]), fmaxf(s4[3][2], s4[3][3])));
+                        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+                        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+                        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+                        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+                        const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+                        const float cA = fast_exp2(mA - nA), cB = fast_exp2(mB - nB);
+                        mA = nA, mB = nB;
+                        float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            s4[j][0] = fast_exp2(s4[j][0] - nA), s4[j][1] = fast_exp2(s4[j][1] - nA);
+                            s4[j][2] = fast_exp2(s4[j][2] - nB), s4[j][3] = fast_exp2(s4[j][3] - nB);
+                            sumA += s4[j][0] + s4[j][1], sumB += s4[j][2] + s4[j][3];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 2; j++) o[j][0] *= cA, o[j][1] *= cA, o[j][2] *= cB, o[j][3] *= cB;
+                        lA = lA * cA + sumA, lB = lB * cB + sumB;
+                        uint32_t v0[4], v1[4];
+                        ldmatrix_x4_trans(v0, t0 + v_off);
+                        ldmatrix_x4_trans(v1, t1 + v_off);
+                        const uint32_t p0[4] = {pack_half2(s4[0][0], s4[0][1]), pack_half2(s4[0][2], s4[0][3]),
+                                                pack_half2(s4[1][0], s4[1][1]), pack_half2(s4[1][2], s4[1][3])};
+                        const uint32_t p1[4] = {pack_half2(s4[2][0], s4[2][1]), pack_half2(s4[2][2], s4[2][3]),
+                                                pack_half2(s4[3][0], s4[3][1]), pack_half2(s4[3][2], s4[3][3])};
+#pragma unroll
+                        for (int j = 0; j < 2; j++) {
+                            mma_16816(o[j], p0, v0[2 * j], v0[2 * j + 1]);
+                            mma_16816(o[j], p1, v1[2 * j], v1[2 * j + 1]);
+                        }
+                        b++;  // two blocks done
+                        continue;
+                    }
+                }
                 const unsigned char *tile = &tiles[c & 1][b][0];
                 uint32_t kf[4];
                 ldmatrix_x4(kf, tile + k_off);

@@ -320,6 +320,61 @@ def run_kvstore(ctx, batch=64, ctx_len=1024, n_blocks=4096, repeats=7):
         pool.close()
 
 
+def run_phases(ctx, pool, seqs, batch, layers, d_model, ctx_len, overlap=2):
+    """Where the time of a per-layer decode-attention launch goes: needs the library built by
+    ``python -m jgpt_b200.build --trace`` (loaded through JGPT_B200_LIB).  Runs the per-layer chain as a CUDA graph, then
+    reads the per-CTA timestamps of the last two launches: start and end on the global timer, and inside a CTA the
+    cycle counts to "barriers initialised", "first K/V slab consumed", "block loop done", "exit"."""
+    import ctypes as C
+
+    lib = ctx._lib
+    if not hasattr(lib, "jgpt_debug_decode_trace"):
+        raise RuntimeError("this library was not built with --trace (python -m jgpt_b200.build --trace; JGPT_B200_LIB=...)")
+    lib.jgpt_debug_decode_trace.restype = C.c_int
+    rng = np.random.default_rng(5)
+    q, k, v = (ctx.from_host(rng.standard_normal((layers, batch, d_model), dtype=np.float32)) for _ in range(3))
+    out = ctx.alloc((layers, batch, d_model))
+    seq_d = ctx.from_host(np.asarray(seqs, np.int32))
+    lens_d, rope_d = ctx.from_host(np.full(batch, ctx_len, np.int32)), ctx.from_host(np.full(batch, ctx_len - 1, np.int32))
+    slab = batch * d_model * 4
+    pool.set_tuning(launch_overlap=overlap)
+
+    def chain():
+        for layer in range(layers):
+            pool.attn_decode_append(layer, 1, q.ptr + layer * slab, k.ptr + layer * slab, v.ptr + layer * slab, seq_d, rope_d, lens_d,
+                                    batch, ctx_len, out.ptr + layer * slab)
+
+    chain()
+    ctx.synchronize()
+    g = ctx.capture(chain)
+    for _ in range(3):
+        g.launch()
+    e0, e1 = Event(ctx), Event(ctx)
+    e0.record()
+    for _ in range(20):
+        g.launch()
+    e1.record()
+    us_layer = e0.elapsed_ms(e1) / 20 / layers * 1e3
+    ctx.synchronize()
+    g.close()
+    buf = np.zeros((65536, 8), np.int64)
+    n = lib.jgpt_debug_decode_trace(buf.ctypes.data_as(C.c_void_p), 65536)
+    a, b = buf[:n], buf[32768:32768 + n]
+    if a[:, 0].min() > b[:, 0].min():
+        a, b = b, a  # a = the earlier of the two launches
+    g0 = a[:, 0].min()
+    res = {"us_per_layer_with_tracing": us_layer, "ctas_per_launch": int(n), "launch_overlap": overlap, "launches": []}
+    for t in (a, b):
+        start, end = (t[:, 0] - g0) / 1e3, (t[:, 1] - g0) / 1e3
+        ph = t[:, 2:6] / 1.9e3  # cycles -> us at 1.9 GHz
+        res["launches"].append({
+            "cta_start_us": [float(start.min()), float(np.median(start)), float(start.max())],
+            "cta_end_us": [float(end.min()), float(np.median(end)), float(end.max())],
+            "per_cta_median_us": {"barriers_ready": float(np.median(ph[:, 0])), "first_slab_consumed": float(np.median(ph[:, 1])),
+                                  "block_loop_done": float(np.median(ph[:, 2])), "exit": float(np.median(ph[:, 3]))}})
+    return res
+
+
 def run_longctx(ctx, rank, world, n_seqs_total=512, steps=20, warmup=3):
     """Decode attention + append at long context: 512 sequences (seed 3) with lengths U[1024, 8192], RoPE positions
     to 8192, dealt in contiguous shards to the ranks; one fused 12-layer launch per step."""

@@ -126,10 +126,13 @@ def test_forward_step_on_the_tcgen05_projections(ctx, F):
         want = om.forward_prefill(ids, om.new_cache(kv_fp16=True))
         # the two projection kernels differ by a few 1e-6 relative; where that moves a K/V element across an
         # fp16 rounding boundary (N(0, 0.15) toy weights, logits of magnitude ~3) single logits move by a few
-        # 1e-4: TOL = 1e-3, well inside the 5e-3 this geometry is allowed against the fp32 oracle
-        TOL = 1e-3
-        assert np.abs(a - b).max() < TOL
-        assert np.abs(b - want).max() < TOL
+        # 1e-4: TOL = 1e-3 for the decode steps, well inside the 5e-3 this geometry is allowed against the fp32 oracle.
+        # The prefill attention of the forward step takes q and the probabilities as fp16 (the configuration's "fp16
+        # Q/K/V into the attention kernel"): with these large toy activations that adds up to ~2e-3 on a logit
+        # (measured 1.7e-3; 5e-4 on the JGPT-35M shapes), so the prefill rows get 3e-3, still inside the 5e-3.
+        TOL, TOL_PREFILL = 1e-3, 3e-3
+        assert np.abs(a - b).max() < TOL_PREFILL
+        assert np.abs(b - want).max() < TOL_PREFILL
         tok = int(np.argmax(b[-1]))
         for _ in range(8):
             da = gm_def.forwardDecode([tok], c1, c1.length(), c1.length())
@@ -142,7 +145,7 @@ def test_forward_step_on_the_tcgen05_projections(ctx, F):
         c2.clear()
         b2 = gm_big.forwardPrefill(ids, c2)
         want2 = om2.forward_prefill(ids, om2.new_cache(kv_fp16=True))
-        assert np.abs(b2 - want2).max() < TOL
+        assert np.abs(b2 - want2).max() < TOL_PREFILL
         om2.close()
     finally:
         c1.close(), c2.close(), gm_def.close(), gm_big.close(), om.close()
