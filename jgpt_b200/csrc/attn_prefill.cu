@@ -121,11 +121,13 @@ __device__ __forceinline__ void split_half2(float a, float b, uint32_t &hi, uint
     lo = pack_half2(a - __half2float(ha), b - __half2float(hb));
 }
 
-// FAST: Q and the probabilities enter the tensor cores as single fp16 values instead of fp16 high + low pairs: half the
-// MMAs and none of the split arithmetic.  The cached K / V are fp16 anyway, so the only new error is the rounding of q
-// (2^-11 relative, i.e. ~1e-3 in a log2-domain score of magnitude a few) and of p (2^-11 relative): attention outputs
-// stay within ~1e-3 of the exact mode on N(0,1) inputs (whose scores are far larger than a model's: measured 6.9e-4) and
-// the logits of the JGPT-35M shapes within 5e-4 of an fp32 CPU evaluation, against a budget of 2e-3.  The exact mode (2e-5) remains the default of the standalone entry point.
+// FAST: the probabilities enter the P.V product as single fp16 values instead of fp16 high + low pairs (half the
+// MMAs of that product and none of the split arithmetic, which was the larger part of the instruction count), and two
+// KV blocks share one online-softmax update.  q keeps its high + low split (done once per CTA), so the scores are as
+// exact as before; the cached K / V are fp16 anyway.  The only new error is the rounding of p (2^-11 relative):
+// attention outputs stay within ~4e-4 of the exact mode on N(0,1) inputs and the logits of the JGPT-35M shapes within
+// 5e-4 of an fp32 CPU evaluation, against a budget of 2e-3.  The exact mode (2e-5) remains the default of the
+// standalone entry point.
 template <bool FAST>
 __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillParams P) {
     constexpr int DH = 16, BT = kBlockTokens, TILE_BYTES = 2 * BT * DH * 2;  // 1 KiB: K tile | V tile
@@ -190,8 +192,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillPara
         }
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-            if constexpr (FAST) a_hi[e] = pack_half2(x[e].x, x[e].y), a_lo[e] = 0u;
-            else split_half2(x[e].x, x[e].y, a_hi[e], a_lo[e]);
+            split_half2(x[e].x, x[e].y, a_hi[e], a_lo[e]);  // once per CTA: q keeps fp32-level accuracy in both modes
         }
     }
 
@@ -232,6 +233,10 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillPara
                         mma_16816(s4[1], a_hi, k0[2], k0[3]);
                         mma_16816(s4[2], a_hi, k1[0], k1[1]);
                         mma_16816(s4[3], a_hi, k1[2], k1[3]);
+                        mma_16816(s4[0], a_lo, k0[0], k0[1]);
+                        mma_16816(s4[1], a_lo, k0[2], k0[3]);
+                        mma_16816(s4[2], a_lo, k1[0], k1[1]);
+                        mma_16816(s4[3], a_lo, k1[2], k1[3]);
                         float mxA = fmaxf(fmaxf(fmaxf(s4[0][0], s4[0][1]), fmaxf(s4[1][0], s4[1][1])),
                                           fmaxf(fmaxf(s4[2][0], s4[2][1]), fmaxf(s4[3][0], s4[3][1])));
                         float mxB = fmaxf(fmaxf(fmaxf(s4[0][2], s4[0][3]), fmaxf(s4[1][2], s4[1][3])),
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(const PrefillPara
 #pragma unroll
                     for (int e = 0; e < 4; e++) s[j][e] = 0.f;
                     mma_16816(s[j], a_hi, kf[2 * j], kf[2 * j + 1]);
-                    if constexpr (!FAST) mma_16816(s[j], a_lo, kf[2 * j], kf[2 * j + 1]);
+                    mma_16816(s[j], a_lo, kf[2 * j], kf[2 * j + 1]);
                 }
                 if (kb == diag) {  // causal mask inside the diagonal block
 #pragma unroll

@@ -151,12 +151,19 @@ struct DevBuf {
         if (p) cudaFree(p);
     }
     cudaError_t alloc(size_t bytes) { return cudaMalloc(&p, bytes ? bytes : 4); }
+    // Copies go on the harness stream, in front of / behind the kernels they feed: that stream is non-blocking, so a
+    // plain cudaMemcpy from pageable memory (which may return before its DMA has landed) would not be ordered with it.
     cudaError_t up(const void* h, size_t bytes) {
         cudaError_t e = alloc(bytes);
-        if (e != cudaSuccess) return e;
-        return bytes ? cudaMemcpy(p, h, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+        if (e != cudaSuccess || !bytes) return e;
+        e = cudaMemcpyAsync(p, h, bytes, cudaMemcpyHostToDevice, jgpt_cuda_stream_handle());
+        return e != cudaSuccess ? e : cudaStreamSynchronize(jgpt_cuda_stream_handle());
     }
-    cudaError_t down(void* h, size_t bytes) const { return bytes ? cudaMemcpy(h, p, bytes, cudaMemcpyDeviceToHost) : cudaSuccess; }
+    cudaError_t down(void* h, size_t bytes) const {
+        if (!bytes) return cudaSuccess;
+        cudaError_t e = cudaMemcpyAsync(h, p, bytes, cudaMemcpyDeviceToHost, jgpt_cuda_stream_handle());
+        return e != cudaSuccess ? e : cudaStreamSynchronize(jgpt_cuda_stream_handle());
+    }
     template <class T>
     T* as() const { return (T*) p; }
 };

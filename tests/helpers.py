@@ -10,6 +10,25 @@ from jgpt_b200 import KvPool
 BT = 16
 
 
+class exact_prefill:
+    """Models created inside use the exact prefill attention (fp16 high + low probabilities): what the toy geometries
+    need to stay within their tight tolerances.  The default mode (single fp16 probabilities) is tested on its own."""
+
+    def __enter__(self):
+        import os
+
+        self.old = os.environ.get("JGPT_B200_PREFILL_EXACT")
+        os.environ["JGPT_B200_PREFILL_EXACT"] = "1"
+
+    def __exit__(self, *a):
+        import os
+
+        if self.old is None:
+            os.environ.pop("JGPT_B200_PREFILL_EXACT", None)
+        else:
+            os.environ["JGPT_B200_PREFILL_EXACT"] = self.old
+
+
 class PagedCase:
     """n sequences of given lengths, K/V ~ N(0,1), block tables = a seeded permutation of the pool."""
 

@@ -114,15 +114,14 @@ def test_prefill_argument_checks(ctx):
 
 
 def test_fast_operand_mode_stays_inside_its_stated_tolerance(ctx, monkeypatch):
-    """JGPT_B200_PREFILL_FAST=1: q and the probabilities go to the tensor cores as single fp16 values (half the MMAs).
-    The cache payload is still bit-exact (the append does not change).  On N(0,1) q and k the scaled scores reach
-    magnitudes of 8 and more, so rounding q to fp16 (2^-11 relative) moves a score by up to ~4e-3 and a probability by
-    as much relatively: attention outputs stay within 1.5e-3 of the oracle (measured 6.9e-4; the exact mode: 2e-5).  The
-    forward step of the model uses this mode by default; there the activations are small and the logits are held to
-    5e-4 against the oracle by the model tests (budget 2e-3)."""
+    """JGPT_B200_PREFILL_FAST=1: the probabilities go to the tensor cores as single fp16 values (q keeps its fp16
+    high + low split, so the scores are exact).  The cache payload is still bit-exact (the append does not change);
+    attention outputs on N(0,1) inputs stay within 6e-4 of the oracle (2^-11 relative on every probability, measured
+    3.9e-4; the exact mode: 2e-5).  The forward step of the model uses this mode by default and is held to the logits budget by the
+    model tests."""
     monkeypatch.setenv("JGPT_B200_PREFILL_FAST", "1")
     worst = _run_case(ctx, 24, 16, [64, 65, 130, 1024], [0, 3, 0, 0], seed=41)
-    assert worst < 1.5e-3, worst
+    assert worst < 6e-4, worst
     monkeypatch.delenv("JGPT_B200_PREFILL_FAST")
     exact = _run_case(ctx, 24, 16, [64, 65, 130, 1024], [0, 3, 0, 0], seed=41)
     assert exact < TOL, exact

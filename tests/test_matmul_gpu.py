@@ -115,9 +115,10 @@ def test_forward_step_on_the_tcgen05_projections(ctx, F):
     kernels and as the oracle's; weight images follow a weight update."""
     V, MS, D, H, L = 96, 80, 64, 4, 3
     om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=4, std=0.15)
-    gm_def = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5)
-    with _env(JGPT_B200_UMMA_MIN_ROWS=1):
-        gm_big = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5)
+    with _env(JGPT_B200_PREFILL_EXACT=1):  # toy weights: the exact prefill attention keeps the tight tolerance below
+        gm_def = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5)
+        with _env(JGPT_B200_UMMA_MIN_ROWS=1):
+            gm_big = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5)
     gm_def.setParameters(om.tensors()), gm_big.setParameters(om.tensors())
     ids = np.array([(i * 5 + 1) % V for i in range(40)], np.int32)
     c1, c2 = (KvCacheGpu(L, H, om.dhead, MS, ctx=ctx) for _ in range(2))
@@ -126,18 +127,17 @@ def test_forward_step_on_the_tcgen05_projections(ctx, F):
         want = om.forward_prefill(ids, om.new_cache(kv_fp16=True))
         # the two projection kernels differ by a few 1e-6 relative; where that moves a K/V element across an
         # fp16 rounding boundary (N(0, 0.15) toy weights, logits of magnitude ~3) single logits move by a few
-        # 1e-4: TOL = 1e-3 for the decode steps, well inside the 5e-3 this geometry is allowed against the fp32 oracle.
-        # The prefill attention of the forward step takes q and the probabilities as fp16 (the configuration's "fp16
-        # Q/K/V into the attention kernel"): with these large toy activations that adds up to ~2e-3 on a logit
-        # (measured 1.7e-3; 5e-4 on the JGPT-35M shapes), so the prefill rows get 3e-3, still inside the 5e-3.
-        TOL, TOL_PREFILL = 1e-3, 3e-3
+        # 1e-4: TOL = 1e-3, well inside the 5e-3 this geometry is allowed against the fp32 oracle
+        TOL = TOL_PREFILL = 1e-3
         assert np.abs(a - b).max() < TOL_PREFILL
         assert np.abs(b - want).max() < TOL_PREFILL
         tok = int(np.argmax(b[-1]))
         for _ in range(8):
             da = gm_def.forwardDecode([tok], c1, c1.length(), c1.length())
             db = gm_big.forwardDecode([tok], c2, c2.length(), c2.length())
-            assert np.abs(da - db).max() < TOL
+            # the decode steps read the two caches the two prefills left, which differ in more elements than the two
+            # projection kernels alone would make them differ (fp16 roundings of p are discontinuous)
+            assert np.abs(da - db).max() < TOL_PREFILL
             tok = int(np.argmax(db))
         # new weights: the cached weight images must be rebuilt
         om2 = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=9, std=0.15)
@@ -201,7 +201,7 @@ def test_ragged_batched_prefill_on_the_tcgen05_path(ctx):
     layer-0 payload on the oracle's fp16 values, slots past each prompt zero."""
     V, MS, D, H, L, F = 96, 64, 64, 4, 2, 128
     om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=31, std=0.15)
-    with _env(JGPT_B200_UMMA_MIN_ROWS=1):
+    with _env(JGPT_B200_UMMA_MIN_ROWS=1, JGPT_B200_PREFILL_EXACT=1):
         gm = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=128)
     gm.setParameters(om.tensors())
     pool = gm.newPool(3 * MS // 16, 3)
