@@ -39,7 +39,7 @@ ALG_BYTES_LAYER = BATCH * HEADS * (CTX_LEN * DHEAD * 2 * 2 + DHEAD * 2 * 2 + DHE
 ALG_BYTES_STEP = ALG_BYTES_LAYER * LAYERS
 # dram__bytes_read.sum + dram__bytes_write.sum of one 12-layer launch of attn_decode_kernel<16,true>, from an ncu
 # capture of this same workload (the launch holds 1.3 GB on the device, so it was captured at full size).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1_246_196_776
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1_231_777_616
 MIN_TIMED_MS = 50.0   # every timed figure covers at least this much device time ...
 MIN_REPEATS = 5       # ... in at least this many repeats of the --steps region; the median repeat is reported
 
@@ -395,7 +395,7 @@ def run_gpu(args, rank, world, local_rank):
                                         seq_d, rope_d, lens_d, BATCH, CTX_LEN, out_d.ptr + layer * slab_q)
 
         if args.per_layer:
-            pool.set_tuning(launch_overlap=2)
+            pool.set_tuning(launch_overlap=args.launch_overlap)
             step_device = step_quick_per_layer
             step_device()
             ctx.synchronize()
@@ -602,6 +602,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--quick", action="store_true", help="device-resident timing only (used under a profiler)")
     ap.add_argument("--per-layer", action="store_true", help="with --quick: one launch per layer instead of one per step")
+    ap.add_argument("--launch-overlap", type=int, default=2, help="with --quick --per-layer: 0 ordinary launches, 1 / 2 overlapped")
     ap.add_argument("--batch", type=int, default=64, help="sequences per step for --workload decodestep")
     ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore", "phases"],
                     help="microbench (default) is the headline KV-append + decode-attention step; the others are the "
