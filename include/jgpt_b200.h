@@ -199,6 +199,11 @@ JGPT_API int32_t jgpt_kv_append(jgpt_kvpool pool, int32_t layer, const float *k_
  * (J/ops/TensorOps.java:2333-2339). */
 JGPT_API int32_t jgpt_kv_gather(jgpt_kvpool pool, int32_t layer, int32_t seq, int32_t len, int32_t max_seq_len,
                                 float *k_out_dev, float *v_out_dev);
+/* The same for n caches in one launch: sequence i's planes at k_out_dev + i * heads * max_seq_len * dhead
+ * (a launch per cache moves only a few megabytes and is launch-bound). */
+JGPT_API int32_t jgpt_kv_gather_batch(jgpt_kvpool pool, int32_t layer, const int32_t *seq_ids_host,
+                                      const int32_t *lens_host, int32_t n, int32_t max_seq_len, float *k_out_dev,
+                                      float *v_out_dev);
 
 /* Decode attention.  Replaces the per-head chain of TensorOps.scaledDotProductAttentionQueryOne
  * (J/ops/TensorOps.java:1088-1140) inside multiHeadAttentionWithRoPEDecode (:2239-2309).

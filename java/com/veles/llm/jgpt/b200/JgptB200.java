@@ -76,6 +76,7 @@ public final class JgptB200 {
     private static final MethodHandle H_KV_EVICT_LRU = bind("jgpt_kv_evict_lru", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS));
     private static final MethodHandle H_KV_APPEND = bind("jgpt_kv_append", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT));
     private static final MethodHandle H_KV_GATHER = bind("jgpt_kv_gather", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
+    private static final MethodHandle H_KV_GATHER_BATCH = bind("jgpt_kv_gather_batch", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS));
     private static final MethodHandle H_ATTN_DECODE = bind("jgpt_attn_decode", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS));
     private static final MethodHandle H_ATTN_DECODE_APPEND = bind("jgpt_attn_decode_append", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, JAVA_INT, ADDRESS));
     private static final MethodHandle H_ATTN_DECODE_APPEND_HOST = bind("jgpt_attn_decode_append_host", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, ADDRESS));
@@ -329,6 +330,11 @@ public final class JgptB200 {
     /** jgpt_kv_gather */
     public static int kvGather(long pool, int layer, int seq, int len, int max_seq_len, MemorySegment k_out_dev, MemorySegment v_out_dev) {
         try { return (int) H_KV_GATHER.invokeExact(pool, layer, seq, len, maxSeqLen, kOutDev, vOutDev); } catch (Throwable t) { throw rethrow(t); }
+    }
+
+    /** jgpt_kv_gather_batch */
+    public static int kvGatherBatch(long pool, int layer, MemorySegment seq_ids_host, MemorySegment lens_host, int n, int max_seq_len, MemorySegment k_out_dev, MemorySegment v_out_dev) {
+        try { return (int) H_KV_GATHER_BATCH.invokeExact(pool, layer, seqIdsHost, lensHost, n, maxSeqLen, kOutDev, vOutDev); } catch (Throwable t) { throw rethrow(t); }
     }
 
     /** jgpt_attn_decode */

@@ -79,6 +79,8 @@ struct Pool {
     int *d_tickets = nullptr;     // split-K arrival counters (self-resetting)
     int *d_item_counters = nullptr;  // [2] work-queue counters of the dynamic decode launch (self-resetting)
     uint64_t n_tickets = 0;
+    int *d_gather_idx = nullptr;  // (sequence, length) pairs of a batched gather
+    int gather_idx_cap = 0;
     int *d_evict_list = nullptr;  // freed block ids for the scrub kernel
     int evict_cap = 0;
     // copy streams + events of the pipelined host-buffer entry point (created on first use)

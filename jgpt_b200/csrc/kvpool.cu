@@ -80,7 +80,16 @@ template <int DH>
 __global__ void __launch_bounds__(256) kv_gather_kernel(const __half *__restrict__ kv, const int *__restrict__ table_row,
                                                         float *__restrict__ k_out, float *__restrict__ v_out, int H,
                                                         int layer, int n_blocks, int len, int max_seq_len,
-                                                        int *__restrict__ status) {
+                                                        int *__restrict__ status, const int *__restrict__ batch_idx, int mbs) {
+    // Batched form (blockIdx.z = which sequence): batch_idx holds (sequence slot, length) pairs, table_row is the
+    // whole table and the outputs are laid back to back, one [H, max_seq_len, DH] plane per sequence.
+    if (batch_idx) {
+        const int seq = batch_idx[2 * blockIdx.z];
+        len = batch_idx[2 * blockIdx.z + 1];
+        table_row += (size_t)seq * mbs;
+        k_out += (size_t)blockIdx.z * H * max_seq_len * DH;
+        v_out += (size_t)blockIdx.z * H * max_seq_len * DH;
+    }
     constexpr int CH = DH < 8 ? DH : 8;
     constexpr int CPR = DH / CH;
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -166,7 +175,30 @@ int32_t launch_kv_gather(Pool *p, int layer, int seq, int len, int max_seq_len, 
     const int *row = p->d_table + (size_t)seq * p->max_blocks_per_seq;
     JGPT_DISPATCH_DH(p->dhead, (kv_gather_kernel<DH><<<grid, threads, 0, p->ctx->stream>>>(
                                    p->kv, row, k_out, v_out, p->heads, layer, p->n_blocks, len, max_seq_len,
-                                   p->ctx->d_status)));
+                                   p->ctx->d_status, nullptr, 0)));
+    JGPT_CUDA_TRY(cudaGetLastError());
+    return JGPT_OK;
+}
+
+// n sequences in ONE launch (a launch per sequence moves 4.7 MB at d_head 16 / context 1024 and is launch-bound).
+static int32_t launch_kv_gather_batch(Pool *p, int layer, const std::vector<int> &seq_len_pairs, int max_seq_len, float *k_out,
+                                      float *v_out) {
+    const int n = (int)seq_len_pairs.size() / 2;
+    if (n > p->gather_idx_cap) {
+        if (p->d_gather_idx) JGPT_CUDA_TRY(cudaFree(p->d_gather_idx));
+        p->d_gather_idx = nullptr;
+        p->gather_idx_cap = std::max(n, 2 * p->gather_idx_cap);
+        JGPT_CUDA_TRY(cudaMalloc(&p->d_gather_idx, sizeof(int) * 2 * (size_t)p->gather_idx_cap));
+    }
+    // pageable source: staged by the runtime before the call returns
+    JGPT_CUDA_TRY(cudaMemcpyAsync(p->d_gather_idx, seq_len_pairs.data(), sizeof(int) * seq_len_pairs.size(), cudaMemcpyHostToDevice,
+                                  p->ctx->stream));
+    const int cpr = p->dhead / (p->dhead < 8 ? p->dhead : 8);
+    const long long total = (long long)p->heads * max_seq_len * cpr;
+    const dim3 grid((unsigned)((total + 255) / 256), 1, (unsigned)n);
+    JGPT_DISPATCH_DH(p->dhead, (kv_gather_kernel<DH><<<grid, 256, 0, p->ctx->stream>>>(
+                                   p->kv, p->d_table, k_out, v_out, p->heads, layer, p->n_blocks, 0, max_seq_len,
+                                   p->ctx->d_status, p->d_gather_idx, p->max_blocks_per_seq)));
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
@@ -267,6 +299,7 @@ static void release_pool(Pool *p) {
     cudaFree(p->d_evict_list), cudaFree(p->d_stage_f), cudaFree(p->d_stage_i);
     cudaFree(p->d_prefill_desc);
     cudaFree(p->d_item_counters);
+    cudaFree(p->d_gather_idx);
     if (p->s_in) {
         cudaStreamDestroy(p->s_in), cudaStreamDestroy(p->s_out), cudaEventDestroy(p->ev_start);
         for (int g = 0; g < 4; g++) cudaEventDestroy(p->ev_in[g]), cudaEventDestroy(p->ev_done[g]);
@@ -610,6 +643,25 @@ int32_t jgpt_kv_gather(jgpt_kvpool h, int32_t layer, int32_t seq, int32_t len, i
                  "len %d beyond the reserved blocks", len);
     JGPT_REQUIRE(k_out_dev && v_out_dev, JGPT_ERR_INVALID_ARGUMENT, "null output");
     return launch_kv_gather(p, layer, seq, len, max_seq_len, k_out_dev, v_out_dev);
+}
+
+// getK / getV of many caches at once: sequence i's planes land at k_out_dev + i * heads * max_seq_len * dhead.
+int32_t jgpt_kv_gather_batch(jgpt_kvpool h, int32_t layer, const int32_t *seq_ids_host, const int32_t *lens_host, int32_t n,
+                             int32_t max_seq_len, float *k_out_dev, float *v_out_dev) {
+    GET_POOL(p, h);
+    JGPT_REQUIRE(layer >= 0 && layer < p->layers, JGPT_ERR_OUT_OF_RANGE, "layer %d outside [0,%d)", layer, p->layers);
+    if (n == 0) return JGPT_OK;
+    JGPT_REQUIRE(n > 0 && n <= 65535 && seq_ids_host && lens_host && k_out_dev && v_out_dev && max_seq_len > 0, JGPT_ERR_INVALID_ARGUMENT,
+                 "null pointer or bad count");
+    std::vector<int> pairs((size_t)2 * n);
+    for (int i = 0; i < n; i++) {
+        const int seq = seq_ids_host[i], len = lens_host[i];
+        CHECK_SEQ(p, seq);
+        JGPT_REQUIRE(len >= 0 && len <= max_seq_len && len <= (int)p->seqs[(size_t)seq].blocks.size() * kBlockTokens,
+                     JGPT_ERR_INVALID_ARGUMENT, "len %d of sequence %d beyond max_seq_len or its reserved blocks", len, seq);
+        pairs[(size_t)2 * i] = seq, pairs[(size_t)2 * i + 1] = len;
+    }
+    return launch_kv_gather_batch(p, layer, pairs, max_seq_len, k_out_dev, v_out_dev);
 }
 
 }  // extern "C"

@@ -114,6 +114,12 @@ class KvPool:
     def gather(self, layer, seq, length, max_seq_len, k_out_dev, v_out_dev):
         B.check(self._lib.jgpt_kv_gather(self.handle, layer, seq, length, max_seq_len, _ptr(k_out_dev), _ptr(v_out_dev)))
 
+    def gather_batch(self, layer, seqs, lens, max_seq_len, k_out_dev, v_out_dev):
+        """``gather`` for several sequences in one launch: outputs [n, H, max_seq_len, Dh]."""
+        sq, ln = np.ascontiguousarray(seqs, np.int32), np.ascontiguousarray(lens, np.int32)
+        B.check(self._lib.jgpt_kv_gather_batch(self.handle, layer, sq.ctypes.data, ln.ctypes.data, sq.size, max_seq_len,
+                                               _ptr(k_out_dev), _ptr(v_out_dev)))
+
     def attn_decode(self, layer0, n_layers, q_dev, seq_ids_dev, rope_pos_dev, lens_dev, n, max_len, out_dev):
         B.check(self._lib.jgpt_attn_decode(self.handle, layer0, n_layers, _ptr(q_dev), _ptr(seq_ids_dev),
                                            _ptr(rope_pos_dev), _ptr(lens_dev), n, max_len, _ptr(out_dev)))

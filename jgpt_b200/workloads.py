@@ -288,6 +288,13 @@ def run_kvstore(ctx, batch=64, ctx_len=1024, n_blocks=4096, repeats=7):
         out["kv_gather_kernel"] = {"ms": ms, "algorithmic_bytes": alg, "GBps": alg / ms / 1e6, "frac": alg / ms / 1e6 / peak,
                                    "launches": batch, "unit": "64 sequences x 1024 positions of one layer, one launch per sequence "
                                    "(4.7 MB each: launch-bound)"}
+        kb = [ctx.alloc((batch, HEADS, ctx_len, DHEAD)) for _ in range(2)]
+        gb = iter(range(10 ** 9))
+        ms = timed(lambda: pool.gather_batch(next(gb) % LAYERS, seqs, [ctx_len] * batch, ctx_len, kb[0], kb[1]))
+        out["kv_gather_kernel_batched"] = {"ms": ms, "algorithmic_bytes": alg, "GBps": alg / ms / 1e6, "frac": alg / ms / 1e6 / peak,
+                                           "launches": 1, "unit": "the same 64 sequences in one launch (jgpt_kv_gather_batch)"}
+        for b in kb:
+            b.close()
         # scrub: free every sequence with zero fill (all 4096 blocks x 12 layers), then map them again
         def scrub_all():
             for s in seqs:

@@ -172,3 +172,25 @@ def test_kv_cache_gpu_facade_contract(ctx):
     finally:
         c.close()
         c.close()  # idempotent
+
+
+def test_batched_gather_equals_per_sequence_gather(ctx):
+    """jgpt_kv_gather_batch: n caches in one launch give exactly the planes of n single gathers (ragged lengths, one empty)."""
+    lens = [40, 0, 16, 129]
+    case = PagedCase(ctx, lens, H=6, Dh=16, layers=2, seed=9)
+    try:
+        ms = case.max_seq
+        kb, vb = ctx.alloc((len(lens), 6, ms, 16)), ctx.alloc((len(lens), 6, ms, 16))
+        kb.fill_bytes(0x7F), vb.fill_bytes(0x7F)
+        case.pool.gather_batch(1, case.seqs, lens, ms, kb, vb)
+        ctx.synchronize()
+        K, V = kb.to_host(), vb.to_host()
+        k1, v1 = ctx.alloc((6, ms, 16)), ctx.alloc((6, ms, 16))
+        for i, (s, l) in enumerate(zip(case.seqs, lens)):
+            case.pool.gather(1, s, l, ms, k1, v1)
+            assert np.array_equal(K[i], k1.to_host()) and np.array_equal(V[i], v1.to_host()), i
+            assert np.array_equal(K[i], case.kc[1, i]) and np.array_equal(V[i], case.vc[1, i]), i
+        with pytest.raises(ValueError):
+            case.pool.gather_batch(1, case.seqs, [ms + 1] * 4, ms, kb, vb)
+    finally:
+        case.close()
