@@ -157,6 +157,8 @@ int32_t status_check_after_sync(Ctx *c, Pool *p, const char *what);
 // Grow-only staging helpers (never called on the steady-state decode path once sized).
 int32_t pool_ensure_staging(Pool *p, uint64_t n_floats, uint64_t n_ints);
 int32_t pool_ensure_split_scratch(Pool *p, uint64_t partial_floats, uint64_t tickets);
+// Returns the blocks reserved beyond n_tokens (and beyond the sequence's length) to the free list, last first.
+int32_t pool_trim_reservation(Pool *p, int seq, int n_tokens);
 // Push rows of the host block table to the device mirror.
 int32_t pool_upload_table_row(Pool *p, int seq);
 
@@ -177,6 +179,50 @@ struct PagedAppendArgs {
 // Validates the prompts of a prefill call against the pool and uploads their descriptors (p->d_prefill_desc).
 int32_t prefill_upload_descriptors(Pool *p, const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
                                    int n_seqs, int *max_S_out, int *n_rows_out);
+
+// Device addresses of one layer's tensors (fp32, row-major [in, out] as GPTModel keeps them).
+struct LayerW {
+    float *wq, *wk, *wv, *wo, *w1, *w2, *w3, *norm1, *norm2;
+};
+
+// A whole decode step (or several greedy steps) of up to fused_step_max_rows() rows as one cooperative launch
+// (decode_fused.cu).  The caller fills the model / pool / scratch fields; fused_step_plan fills the splits.
+constexpr int kFusedMaxKSplit = 8;   // k ranges a narrow projection (Wo, W2) is cut into at most
+constexpr int kFusedMaxChunks = 16;  // attention chunks per (row, head) at most
+struct FusedStepArgs {
+    // model
+    const float *tok, *pos, *norm_final, *lm_head;
+    const LayerW *L;  // device array [layers]
+    int vocab, max_seq, D, H, layers, F;
+    float eps;
+    // paged store
+    __half *kv;
+    const int *table;
+    const float2 *rope;
+    int n_blocks, mbs;
+    // rows: idx = [5][n] token ids, position rows (unused here), sequence ids, RoPE positions, lengths after the append
+    const int *idx;
+    int n, steps, stop_on_zero;
+    // scratch (rows padded to the kernel's row count, 4 at most)
+    float *qkv;     // [rows][3 D]
+    float *part;    // [rows][H][kFusedMaxChunks][18]
+    float *po;      // [kFusedMaxKSplit][rows][D]
+    float *pw2;     // [kFusedMaxKSplit][rows][D]
+    float *act;     // [rows][F]
+    float *logits;  // [n][vocab]
+    float *cand_v;  // [grid][rows] best logit of each CTA's columns
+    int *cand_i;    //              and its index
+    int *next;      // [steps][n] tokens picked
+    int *steps_done;
+    unsigned *sync_words;  // [3] meeting counter, leave counter, abort word; zero between launches
+    int *status;
+    // plan
+    int grid, nch, cb, ks_o, kl_o, ks_2, kl_2, amax;
+    float scale_log2e;
+};
+int fused_step_max_rows();
+void fused_step_plan(FusedStepArgs &A, int sm_count, int max_len);
+int32_t launch_decode_fused(Ctx *ctx, FusedStepArgs &A);
 
 // Kernel launchers (defined in the .cu files)
 int32_t launch_kv_append(Pool *p, int layer, const float *k, const float *v, const int *seq_ids,

@@ -241,6 +241,22 @@ static int32_t pool_upload_table_entries(Pool *p, int seq, int first, int count)
     return JGPT_OK;
 }
 
+// Hands back the blocks a sequence holds beyond what n_tokens need, last block first: exactly the reverse of the
+// pops jgpt_seq_reserve made, so reserving ahead and trimming leaves the allocator as if it had never reserved.
+int32_t pool_trim_reservation(Pool *p, int seq, int n_tokens) {
+    SeqState &s = p->seqs[(size_t)seq];
+    const int keep = std::max((n_tokens + kBlockTokens - 1) / kBlockTokens, (s.len + kBlockTokens - 1) / kBlockTokens);
+    const int have = (int)s.blocks.size();
+    if (keep >= have) return JGPT_OK;
+    while ((int)s.blocks.size() > keep) {
+        p->free_list.push_back(s.blocks.back());
+        s.blocks.pop_back();
+    }
+    JGPT_CUDA_TRY(cudaMemsetAsync(p->d_table + (size_t)seq * p->max_blocks_per_seq + keep, 0xFF, sizeof(int) * (size_t)(have - keep),
+                                  p->ctx->stream));
+    return JGPT_OK;
+}
+
 int32_t pool_ensure_staging(Pool *p, uint64_t n_floats, uint64_t n_ints) {
     if (n_floats > p->stage_f_floats) {
         JGPT_CUDA_TRY(cudaStreamSynchronize(p->ctx->stream));

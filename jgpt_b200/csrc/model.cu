@@ -19,10 +19,6 @@
 
 namespace jgpt {
 
-struct LayerW {
-    float *wq, *wk, *wv, *wo, *w1, *w2, *w3, *norm1, *norm2;
-};
-
 struct Model {
     Ctx *ctx = nullptr;
     int vocab = 0, max_seq = 0, d_model = 0, heads = 0, layers = 0, d_ff = 0, max_rows = 0;
@@ -68,7 +64,14 @@ struct Model {
     int decode_graph_enabled = 1;
     int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = by batch size)
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
+    // Steps of up to four rows as one cooperative launch (decode_fused.cu; JGPT_B200_FUSED_STEP=0: off).  Sized on first use.
+    int fused_step = 1;
+    LayerW *d_layers = nullptr;
+    float *f_floats = nullptr;  // qkv, attention partials, projection partials, activation, candidates
+    int *f_ints = nullptr;      // candidate indices, tokens of a multi-step launch, steps done, meeting words
+    int *h_fused = nullptr;     // pinned: [kFusedMaxSteps * 4] tokens + steps done
 };
+constexpr int kFusedMaxSteps = 256;  // greedy steps one launch runs at most
 
 static void drop_decode_graphs(Model *m) {
     for (auto &g : m->decode_graphs)
@@ -1050,6 +1053,58 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
     return JGPT_OK;
 }
 
+// ---- the fused step (decode_fused.cu) ----
+static bool fused_ok(const Model *m, const Pool *p, int n) {
+    const size_t smem = sizeof(float) * 4 * ((size_t)m->d_model + (size_t)std::max(m->d_model, m->d_ff)) + 4096;
+    return m->fused_step && !m->strict && n >= 1 && n <= fused_step_max_rows() && p->dhead == 16 && m->d_model == m->heads * 16 &&
+           m->d_model % 8 == 0 && m->d_ff % 8 == 0 && m->vocab % 8 == 0 && smem <= 60 * 1024;
+}
+static int32_t ensure_fused(Model *m) {
+    if (m->d_layers) return JGPT_OK;
+    const size_t D = m->d_model, F = m->d_ff, H = m->heads, G = m->ctx->sm_count, R = 4;
+    const size_t nf = R * 3 * D + R * H * kFusedMaxChunks * 18 + 2 * (size_t)kFusedMaxKSplit * R * D + R * F + G * R;
+    const size_t ni = G * R + (size_t)kFusedMaxSteps * R + 4 + 4;
+    JGPT_CUDA_TRY(cudaMalloc(&m->f_floats, sizeof(float) * nf));
+    JGPT_CUDA_TRY(cudaMalloc(&m->f_ints, sizeof(int) * ni));
+    JGPT_CUDA_TRY(cudaMemsetAsync(m->f_ints, 0, sizeof(int) * ni, m->ctx->stream));
+    JGPT_CUDA_TRY(cudaHostAlloc(&m->h_fused, sizeof(int) * ((size_t)kFusedMaxSteps * R + 4), cudaHostAllocDefault));
+    LayerW *dl = nullptr;
+    JGPT_CUDA_TRY(cudaMalloc(&dl, sizeof(LayerW) * m->L.size()));
+    JGPT_CUDA_TRY(cudaMemcpyAsync(dl, m->L.data(), sizeof(LayerW) * m->L.size(), cudaMemcpyHostToDevice, m->ctx->stream));
+    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
+    m->d_layers = dl;
+    return JGPT_OK;
+}
+// Enqueues `steps` decode steps of the n rows described in m->d_idx (already uploaded).  Tokens go to `next_dev`
+// ([steps][n]); with stop_on_zero (n == 1) the launch ends after a sampled 0.
+static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_zero, int max_len_after, int *next_dev) {
+    const size_t D = m->d_model, F = m->d_ff, H = m->heads, G = m->ctx->sm_count, R = 4;
+    FusedStepArgs A = {};
+    A.tok = m->tok, A.pos = m->pos, A.norm_final = m->norm_final, A.lm_head = m->lm_head, A.L = m->d_layers;
+    A.vocab = m->vocab, A.max_seq = m->max_seq, A.D = m->d_model, A.H = m->heads, A.layers = m->layers, A.F = m->d_ff, A.eps = m->eps;
+    A.kv = p->kv, A.table = p->d_table, A.rope = p->d_rope, A.n_blocks = p->n_blocks, A.mbs = p->max_blocks_per_seq;
+    A.idx = m->d_idx, A.n = n, A.steps = steps, A.stop_on_zero = stop_on_zero;
+    float *f = m->f_floats;
+    A.qkv = f, f += R * 3 * D;
+    A.part = f, f += R * H * kFusedMaxChunks * 18;
+    A.po = f, f += (size_t)kFusedMaxKSplit * R * D;
+    A.pw2 = f, f += (size_t)kFusedMaxKSplit * R * D;
+    A.act = f, f += R * F;
+    A.cand_v = f;
+    A.logits = m->logits;
+    int *ip = m->f_ints;
+    A.cand_i = ip, ip += G * R;
+    ip += (size_t)kFusedMaxSteps * R;  // tokens of a multi-step launch (next_dev points here or at d_next)
+    A.steps_done = ip, ip += 4;
+    A.sync_words = reinterpret_cast<unsigned *>(ip);
+    A.next = next_dev;
+    A.status = m->ctx->d_status;
+    fused_step_plan(A, m->ctx->sm_count, max_len_after);
+    return launch_decode_fused(m->ctx, A);
+}
+static int *fused_tokens_dev(Model *m) { return m->f_ints + (size_t)m->ctx->sm_count * 4; }
+static int *fused_steps_done_dev(Model *m) { return fused_tokens_dev(m) + (size_t)kFusedMaxSteps * 4; }
+
 }  // namespace jgpt
 
 using namespace jgpt;
@@ -1125,6 +1180,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
     m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = by batch size
+    m->fused_step = env_int("JGPT_B200_FUSED_STEP", 1);
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -1179,6 +1235,7 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     drop_weight_images(m);  // and the decode graphs
     cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b), cudaFree(m->d_u), cudaFree(m->d_samp);
     cudaFreeHost(m->h_u);
+    cudaFree(m->d_layers), cudaFree(m->f_floats), cudaFree(m->f_ints), cudaFreeHost(m->h_fused);
     delete m;
     return JGPT_OK;
 }
@@ -1494,7 +1551,19 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         return JGPT_OK;
     };
     Model::DecodeGraph *slot = nullptr;
-    if (m->decode_graph_enabled && small_mode(m, n)) {
+    if (fused_ok(m, p, n)) {  // a handful of rows: the whole step is one cooperative launch
+        if ((rc = ensure_fused(m))) return rc;
+        if ((rc = ensure_logits(m, n))) return rc;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+        if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
+        if ((rc = fused_enqueue(m, p, n, 1, 0, max_len, m->d_next))) return rc;
+        if (sampled) {
+            sample_kernel<<<n, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
+            JGPT_CUDA_TRY(cudaGetLastError());
+        }
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
+    } else if (m->decode_graph_enabled && small_mode(m, n)) {
         // Key: the pool object and its generation (unique per pool, bumped whenever a device buffer the kernels are
         // handed is reallocated), every other buffer address baked into the captured launches, and the pool geometry.
         auto make_key = [&]() {
@@ -1633,6 +1702,44 @@ int32_t jgpt_sample_next_token(const float *logits_host, int32_t vocab, float te
     return JGPT_OK;
 }
 
+// Up to T greedy steps of one sequence in one launch (each step's argmax is the next step's input; the launch ends
+// after a sampled 0).  Returns false - nothing done - when the blocks for T tokens cannot be reserved at once or
+// the step is not valid as a single step either (the caller then takes the single step, which reports the error
+// at the moment the reference would).  On true: *rc is the status, tokens[0..*done) the sampled ids, the cache length
+// advanced by *done, blocks reserved beyond that handed back.
+static bool fused_greedy_steps(Model *m, Pool *p, jgpt_kvpool poolh, int32_t seq, int32_t first_id, int32_t len_before, int32_t rope, int T,
+                               int32_t *tokens, int *done, int32_t *rc) {
+    *done = 0, *rc = JGPT_OK;
+    if (first_id < 0 || first_id >= m->vocab || rope < 0 || len_before >= m->max_seq || len_before + T > p->max_blocks_per_seq * kBlockTokens ||
+        len_before + T > m->max_seq || rope + T > p->max_positions)
+        return false;
+    if (jgpt_seq_reserve(poolh, seq, len_before + T) != JGPT_OK) return false;
+    cudaStream_t st = m->ctx->stream;
+    auto run = [&]() -> int32_t {
+        int32_t r2;
+        if ((r2 = ensure_fused(m))) return r2;
+        if ((r2 = ensure_logits(m, 1))) return r2;
+        int *ids = m->h_idx;  // packed [5][1]
+        ids[0] = first_id, ids[1] = rope % m->max_seq, ids[2] = seq, ids[3] = rope, ids[4] = len_before + 1;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5, cudaMemcpyHostToDevice, st));
+        if ((r2 = fused_enqueue(m, p, 1, T, 1, len_before + T, fused_tokens_dev(m)))) return r2;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_fused, fused_tokens_dev(m), sizeof(int) * (size_t)T, cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_fused + (size_t)kFusedMaxSteps * 4, fused_steps_done_dev(m), sizeof(int), cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
+        JGPT_CUDA_TRY(cudaStreamSynchronize(st));
+        if ((r2 = status_check_after_sync(m->ctx, p, "jgpt_generate_greedy"))) return r2;
+        const int nd = m->h_fused[(size_t)kFusedMaxSteps * 4];
+        JGPT_REQUIRE(nd >= 1 && nd <= T, JGPT_ERR_DEVICE_CHECK, "fused decode steps reported %d of %d done", nd, T);
+        for (int i = 0; i < nd; i++) tokens[i] = m->h_fused[i];
+        *done = nd;
+        return jgpt_seq_set_length(poolh, seq, len_before + nd);
+    };
+    *rc = run();
+    const int32_t trc = pool_trim_reservation(p, seq, p->seqs[(size_t)seq].len);
+    if (*rc == JGPT_OK) *rc = trc;
+    return true;
+}
+
 // GPTModel.generateGpuKv with temperature <= 0 (GptAutoregressiveGenerator.java:108-206).
 int32_t jgpt_generate_greedy(jgpt_model h, jgpt_kvpool poolh, const int32_t *prompt_host, int32_t S, int32_t max_new,
                              int32_t *out_host, int32_t *n_sampled_out) {
@@ -1665,6 +1772,14 @@ int32_t jgpt_generate_greedy(jgpt_model h, jgpt_kvpool poolh, const int32_t *pro
                 rc = jgpt_forward_prefill(h, poolh, seq, out_host + start, len, start, nullptr, nullptr, &tok);
             } else {
                 const int32_t prev = out_host[S + j - 1], len_before = p->seqs[(size_t)seq].len, rope = S + j - 1;
+                // as many of the remaining steps as fit before the window starts to slide, in one launch
+                const int T = std::min(std::min(max_new - j, m->max_seq - cur + 1), std::min(p->max_positions - rope, kFusedMaxSteps));
+                int done = 0;
+                if (T >= 2 && fused_ok(m, p, 1) && fused_greedy_steps(m, p, poolh, seq, prev, len_before, rope, T, out_host + cur, &done, &rc)) {
+                    if (rc) break;
+                    n += done, j += done - 1, tok = out_host[cur + done - 1];
+                    continue;
+                }
                 rc = jgpt_forward_decode(h, poolh, &seq, &prev, &len_before, &rope, 1, nullptr, &tok);
             }
             if (rc) break;

@@ -1,0 +1,135 @@
+"""The decode step of one to four rows as ONE cooperative launch (csrc/decode_fused.cu), and greedy generation with
+several steps per launch, against the multi-launch step of the same library (JGPT_B200_FUSED_STEP=0), the CPU oracle
+and the allocator specification.
+
+Tolerances: logits of the two step forms within 1e-4 of each other (both compute fp32 products with different
+summation orders: split-TF32 tensor-core tiles against plain FMA chains) and within 2e-3 of the oracle run with the
+fp16-rounded cache (over 20 steps the one-ulp differences of appended payloads add up on this toy geometry); K/V payloads within one fp16 ulp (the fp32 value being rounded may differ in its last bit);
+greedy token streams identical; block tables and free lists identical."""
+import numpy as np
+import pytest
+
+import oracle as O
+from helpers import exact_prefill
+from jgpt_b200 import GPTModel
+
+pytestmark = pytest.mark.gpu
+GEOM = (96, 80, 64, 4, 3, 128)  # vocab, max_seq, d_model, heads (d_head 16), layers, d_ff
+
+
+def _three(ctx, geom, seed, std, monkeypatch):
+    """The oracle, a model that takes the fused step, a model that does not."""
+    om = O.Model(*geom, eps=1e-5).init_random(seed=seed, std=std)
+    with exact_prefill():
+        fused = GPTModel(ctx, *geom, rmsNormEps=1e-5)
+        monkeypatch.setenv("JGPT_B200_FUSED_STEP", "0")
+        plain = GPTModel(ctx, *geom, rmsNormEps=1e-5)
+        monkeypatch.delenv("JGPT_B200_FUSED_STEP")
+    fused.setParameters(om.tensors()), plain.setParameters(om.tensors())
+    return om, fused, plain
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4])
+def test_fused_step_against_the_multi_launch_step_and_the_oracle(ctx, n, monkeypatch):
+    om, fused, plain = _three(ctx, GEOM, 4, 0.15, monkeypatch)
+    V, MS = GEOM[0], GEOM[1]
+    plens = (31, 3, 47, 16)[:n]  # steps below cross 16-token block boundaries for every row
+    prompts = [np.array([(i * 7 + 3 * s) % V for i in range(p)], np.int32) for s, p in enumerate(plens)]
+    pools = [g.newPool(n_blocks=n * 5, max_seqs=n) for g in (fused, plain)]
+    caches = [om.new_cache(kv_fp16=True) for _ in range(n)]
+    try:
+        seqs = [[pool.seq_alloc() for _ in range(n)] for pool in pools]
+        toks = None
+        for g, pool, sq in zip((fused, plain), pools, seqs):
+            _, t = g.forwardPrefillBatch(pool, sq, prompts)
+            assert toks is None or np.array_equal(toks, t)
+            toks = t
+        for i in range(n):
+            om.forward_prefill(prompts[i], caches[i])
+        lens = np.array(plens, np.int32)
+        for step in range(20):
+            lf, tf = fused.forwardDecodeBatch(pools[0], seqs[0], toks, lens, lens)
+            lp, tp = plain.forwardDecodeBatch(pools[1], seqs[1], toks, lens, lens)
+            assert np.abs(lf - lp).max() < 1e-4, step
+            for i in range(n):
+                want = om.forward_decode(int(toks[i]), caches[i], int(lens[i]), int(lens[i]))
+                assert np.abs(lf[i] - want).max() < 2e-3, (step, i)
+                assert tf[i] == int(np.argmax(lf[i]))  # the kernel's own argmax: first index of the maximum
+            top = np.sort(lp, axis=1)[:, ::-1]
+            assert np.array_equal(tf, tp) or (top[:, 0] - top[:, 1]).min() < 1e-4
+            toks, lens = tp, lens + 1
+        for layer in (0, GEOM[4] - 1):  # what the step appended, as the store holds it
+            for i in range(n):
+                planes = []
+                for pool, sq in zip(pools, seqs):
+                    kd, vd = ctx.alloc((GEOM[3], MS, 16)), ctx.alloc((GEOM[3], MS, 16))
+                    pool.gather(layer, sq[i], int(lens[i]), MS, kd, vd)
+                    planes.append((kd.to_host(), vd.to_host()))
+                for a, b in zip(planes[0], planes[1]):
+                    assert np.all(np.abs(a - b) <= np.abs(b) * 2.0 ** -10 + 1e-7)
+                ok = caches[i].k(layer)[:, :lens[i]]  # the oracle's payload: equal up to one fp16 ulp, nearly all bits equal
+                gk = planes[0][0][:, :lens[i]]
+                assert np.all(np.abs(gk - ok) <= np.abs(ok) * 2.0 ** -10 + 1e-7)
+                assert (gk != ok).mean() < 0.01
+    finally:
+        for pool in pools:
+            pool.close()
+        for c in caches:
+            c.close()
+        fused.close(), plain.close(), om.close()
+
+
+@pytest.mark.parametrize("max_seq,prompt_len,max_new", [(80, 10, 60), (48, 9, 55), (80, 79, 1), (80, 78, 2)])
+def test_generation_with_many_steps_per_launch(ctx, max_seq, prompt_len, max_new, monkeypatch):
+    """jgpt_generate_greedy runs the steps up to the point where the window starts to slide in one launch (each step's
+    argmax feeds the next): the stream of the one-step-per-call loop and of the oracle, the allocator left as that
+    loop leaves it."""
+    geom = (96, max_seq, 64, 4, 3, 128)
+    om, fused, plain = _three(ctx, geom, 4, 0.15, monkeypatch)
+    pools = [g.newPool(n_blocks=12, max_seqs=2) for g in (fused, plain)]
+    try:
+        for mult in (7, 11):
+            prompt = np.array([(i * mult + 3) % 96 for i in range(prompt_len)], np.int32)
+            want, _ = om.generate_greedy(prompt, max_new, kv_fp16=True)
+            got_f = fused.generateGpuKv(prompt, max_new, pool=pools[0])
+            got_p = plain.generateGpuKv(prompt, max_new, pool=pools[1])
+            assert np.array_equal(got_f, got_p), (got_f, got_p)
+            assert np.array_equal(got_f, want)
+            assert pools[0].free_blocks() == pools[1].free_blocks() == 12
+            tables = []
+            for pool in pools:  # the next sequence gets the same blocks in the same order
+                s = pool.seq_alloc()
+                pool.reserve(s, 70)
+                tables.append(pool.block_table(s).tolist())
+                pool.seq_free(s)
+            assert tables[0] == tables[1]
+    finally:
+        for pool in pools:
+            pool.close()
+        fused.close(), plain.close(), om.close()
+
+
+def test_a_sampled_zero_ends_the_launch(ctx, monkeypatch):
+    """Generation stops after id 0 (the reference's end marker); inside a launch of many steps the kernel itself
+    stops there.  A vocabulary of 8 makes a zero likely; the seed is searched on the CPU."""
+    geom = (8, 64, 32, 2, 2, 64)
+    prompt = np.array([3, 5, 1, 7, 2], np.int32)
+    found = None
+    for seed in range(200):
+        om = O.Model(*geom, eps=1e-5).init_random(seed=seed, std=0.3)
+        want, n = om.generate_greedy(prompt, 40, kv_fp16=True)
+        om.close()
+        if 4 <= n < 40:
+            found = (seed, want, n)
+            break
+    assert found, "no seed with an early stop"
+    seed, want, n = found
+    om, fused, plain = _three(ctx, geom, seed, 0.3, monkeypatch)
+    pool = fused.newPool(n_blocks=8, max_seqs=1)
+    try:
+        got = fused.generateGpuKv(prompt, 40, pool=pool)
+        assert np.array_equal(got, want) and got[5 + n - 1] == 0 and not got[5 + n:].any()
+        assert np.array_equal(plain.generateGpuKv(prompt, 40), want)
+        assert pool.free_blocks() == 8
+    finally:
+        pool.close(), fused.close(), plain.close(), om.close()

@@ -299,24 +299,24 @@ def test_graph_replayed_decode_steps_equal_eager_ones_and_follow_weight_updates(
     length-bucket boundaries and for two batch sizes; after a weight update the old graphs must be gone."""
     V, MS, D, H, L, F = 96, 320, 64, 4, 2, 128
     om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=11, std=0.15)
-    gm_graph = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=512)
+    gm_graph = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=1024)
     os.environ["JGPT_B200_DECODE_GRAPH"] = "0"
     try:
-        gm_eager = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=512)
+        gm_eager = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=1024)
     finally:
         os.environ.pop("JGPT_B200_DECODE_GRAPH")
     gm_graph.setParameters(om.tensors()), gm_eager.setParameters(om.tensors())
-    pools = [g.newPool(n_blocks=3 * MS // 16, max_seqs=3) for g in (gm_graph, gm_eager)]
-    try:
-        prompts = [np.array([(i * 7 + s) % V for i in range(100 + 9 * s)], np.int32) for s in range(3)]
+    pools = [g.newPool(n_blocks=6 * MS // 16, max_seqs=6) for g in (gm_graph, gm_eager)]
+    try:  # 6 and 5 rows: above the row count that runs as one fused launch, which is not replayed as a graph
+        prompts = [np.array([(i * 7 + s) % V for i in range(100 + (9 * s) % 19)], np.int32) for s in range(6)]
         state = []
         for g, pool in zip((gm_graph, gm_eager), pools):
-            seqs = [pool.seq_alloc() for _ in range(3)]
+            seqs = [pool.seq_alloc() for _ in range(6)]
             _, nxt = g.forwardPrefillBatch(pool, seqs, prompts)
             state.append((seqs, nxt.copy(), [len(p) for p in prompts]))
         assert np.array_equal(state[0][1], state[1][1])
         for step in range(60):  # lengths 100..178: crosses 16-token blocks and the 128-token bucket
-            active = 3 if step < 40 else 2  # a second batch size: new graphs
+            active = 6 if step < 40 else 5  # a second batch size: new graphs
             outs = []
             for (g, pool), (seqs, nxt, lens) in zip(zip((gm_graph, gm_eager), pools), state):
                 lg, nx = g.forwardDecodeBatch(pool, seqs[:active], nxt[:active], lens[:active], lens[:active])
@@ -333,8 +333,8 @@ def test_graph_replayed_decode_steps_equal_eager_ones_and_follow_weight_updates(
         for _ in range(3):
             outs = []
             for (g, pool), (seqs, nxt, lens) in zip(zip((gm_graph, gm_eager), pools), state):
-                outs.append(g.forwardDecodeBatch(pool, seqs[:2], nxt[:2], lens[:2], lens[:2]))
-                for i in range(2):
+                outs.append(g.forwardDecodeBatch(pool, seqs[:5], nxt[:5], lens[:5], lens[:5]))
+                for i in range(5):
                     lens[i] += 1
             assert np.array_equal(outs[0][0], outs[1][0])
         om2.close()
@@ -484,12 +484,13 @@ def test_overlapped_launches_inside_the_decode_step_change_nothing(ctx, level, m
         monkeypatch.setenv("JGPT_B200_STEP_OVERLAP", str(lv))
         gm = GPTModel(ctx, 96, 80, 64, 4, 3, 128, rmsNormEps=1e-5)
         gm.setParameters(om.tensors())
-        pool = gm.newPool(n_blocks=3 * 5, max_seqs=3)
-        try:
-            seqs = [pool.seq_alloc() for _ in range(3)]
-            prompts = [np.array([(i * 7 + s) % 96 for i in range(n)], np.int32) for s, n in enumerate((33, 5, 16))]
+        pool = gm.newPool(n_blocks=6 * 5, max_seqs=6)
+        try:  # six rows: the multi-launch step (up to four rows run as one fused launch instead)
+            seqs = [pool.seq_alloc() for _ in range(6)]
+            plens = (33, 5, 16, 40, 1, 27)
+            prompts = [np.array([(i * 7 + s) % 96 for i in range(n)], np.int32) for s, n in enumerate(plens)]
             _, toks = gm.forwardPrefillBatch(pool, seqs, prompts)
-            lens = np.array([33, 5, 16], np.int32)
+            lens = np.array(plens, np.int32)
             rec = []
             for step in range(6):  # step 0 eager, step 1 captures, later steps replay the graph
                 logits, toks = gm.forwardDecodeBatch(pool, seqs, toks, lens, lens)
