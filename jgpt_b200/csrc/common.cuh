@@ -187,12 +187,13 @@ struct LayerW {
 
 // A whole decode step (or several greedy steps) of up to fused_step_max_rows() rows as one cooperative launch
 // (decode_fused.cu).  The caller fills the model / pool / scratch fields; fused_step_plan fills the splits.
-constexpr int kFusedMaxKSplit = 8;   // k ranges a narrow projection (Wo, W2) is cut into at most
-constexpr int kFusedMaxChunks = 16;  // attention chunks per (row, head) at most
+constexpr int kFusedMaxLayers = 40;
+constexpr int kFusedMaxKSplit = 4;   // k ranges a narrow projection (Wo, W2) is cut into at most
+constexpr int kFusedMaxChunks = 8;   // attention chunks per (row, head) at most
 struct FusedStepArgs {
     // model
     const float *tok, *pos, *norm_final, *lm_head;
-    const LayerW *L;  // device array [layers]
+    LayerW Lw[kFusedMaxLayers];  // by value: the kernel reads the addresses from its parameter space
     int vocab, max_seq, D, H, layers, F;
     float eps;
     // paged store
@@ -203,18 +204,18 @@ struct FusedStepArgs {
     // rows: idx = [5][n] token ids, position rows (unused here), sequence ids, RoPE positions, lengths after the append
     const int *idx;
     int n, steps, stop_on_zero;
-    // scratch (rows padded to the kernel's row count, 4 at most)
-    float *qkv;     // [rows][3 D]
-    float *part;    // [rows][H][kFusedMaxChunks][18]
-    float *po;      // [kFusedMaxKSplit][rows][D]
-    float *pw2;     // [kFusedMaxKSplit][rows][D]
-    float *act;     // [rows][F]
-    float *logits;  // [n][vocab]
-    float *cand_v;  // [grid][rows] best logit of each CTA's columns
-    int *cand_i;    //              and its index
-    int *next;      // [steps][n] tokens picked
+    // exchange buffers: (value, stamp) pairs, rows padded to the kernel's row count (4 at most)
+    uint2 *ll_qkv;   // [rows][3 D]
+    uint2 *ll_part;  // [rows][H][nch][18]
+    uint2 *ll_po;    // [kFusedMaxKSplit][rows][D]
+    uint2 *ll_pw2;   // [kFusedMaxKSplit][rows][D]
+    uint2 *ll_act;   // [rows][F]
+    uint2 *ll_cand;  // [grid][rows][2] best logit of each CTA's columns and its index
+    unsigned stamp0;  // stamps of this launch: stamp0 + 1 ... stamp0 + steps * layers
+    float *logits;   // [n][vocab]
+    int *next;       // [steps][n] tokens picked
     int *steps_done;
-    unsigned *sync_words;  // [3] meeting counter, leave counter, abort word; zero between launches
+    unsigned *sync_words;  // [1] abort word: holds stamp0 + 1 of a launch that gave up
     int *status;
     // plan
     int grid, nch, cb, ks_o, kl_o, ks_2, kl_2, amax;

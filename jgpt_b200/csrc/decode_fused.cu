@@ -4,21 +4,27 @@
 //
 // With 1-4 rows every kernel of the layer chain (norm + Q,K,V, attention, Wo, norm + W1/W3 + SwiGLU, W2) moves a few
 // kilobytes per SM and lasts a few microseconds; a step of 63 dependent launches is then nothing but launch and
-// drain latencies.  Here one grid of one CTA per SM walks the same chain, the CTAs meet at a counter in global
-// memory between the phases (5 per layer), and everything a phase reads that does not depend on the previous one -
-// its slice of the weights - is already on its way when the CTAs arrive at the counter.  The residual row lives in
-// every CTA's shared memory (each CTA applies the same updates in the same order, so the copies stay bit-identical);
-// the narrow projections (Wo, W2) are split over k and their partial rows are summed by the reader in a fixed
-// order, so a step is deterministic.  Several steps can run in one launch (greedy generation: the argmax of one step
-// is the input of the next), which also removes the host round trip between tokens.
+// drain latencies.  Here one grid of one CTA per SM walks the same chain.  What one phase hands to the next (a few
+// kilobytes of activations) travels through global memory as (value, stamp) pairs written with one 8-byte store:
+// a reader polls the words it needs until they carry the stamp of the step and layer it is working on, so there
+// is no grid-wide barrier, no fence and no atomic on the path - one store and one load between two phases.  (A
+// buffer is rewritten one layer later; by then every CTA has consumed it, because each phase needs the output of
+// ALL CTAs of the phase before.)  Everything a phase reads that does not depend on the previous one - its slice
+// of the weights - is already on its way while it polls.  The residual row lives in every CTA's shared memory
+// (each CTA applies the same updates in the same order, so the copies stay bit-identical); the narrow projections
+// (Wo, W2) are split over k and their partial rows are summed by the reader in a fixed order, so a step is
+// deterministic and a row's result does not depend on the other rows of the batch.  Several steps can run in one
+// launch (greedy generation: the argmax of one step is the input of the next), which also removes the host round
+// trip between tokens.
 //
 // Arithmetic: plain fp32 FMA for the projections (a row-vector times a matrix has no tile for a tensor core), the
 // attention as in attn_decode.cu: RoPE (adjacent pairs, apply_rope_4d_kernel) on q and on the appended k, K/V
 // rounded to fp16 in the paged store, scores and softmax in fp32 in the log2 domain, split over the sequence.
 //
-// The CTAs wait for one another, so the launch is cooperative (all CTAs resident or the launch is refused), and
-// every wait is bounded: a CTA that runs out of polls records DEV_STATUS_WAIT_TIMEOUT, raises the launch's abort
-// word and leaves; the others see the word and leave too.
+// The CTAs wait for one another's data, so the launch is cooperative (all CTAs resident or the launch is refused),
+// and every wait is bounded: a thread that runs out of polls records DEV_STATUS_WAIT_TIMEOUT, publishes the
+// launch's tag in the abort word and its CTA leaves; the others see the tag and leave too.  Stamps grow from launch
+// to launch, so whatever an abandoned launch left behind is never mistaken for data.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -37,38 +43,71 @@ constexpr int kTileK = 3 * kSlices;    // k rows one register tile of a unit cov
 constexpr int DH = 16;                 // head size of this path
 constexpr int PS = DH + 2;             // an attention partial: running maximum, sum, DH unnormalised outputs
 constexpr unsigned kPollLimit = 1u << 21;
+constexpr int kCandBatch = 5;          // per-CTA candidates a lane polls at a time when the tokens are picked
 
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned *p) {
     unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// Two (value, stamp) pairs.  Each 8-byte half is written with one store, so a half is never seen torn.
+__device__ __forceinline__ uint4 ld_pairs(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_pair(uint2 *p, float v, unsigned stamp) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
+}
 
-// All CTAs of the grid meet: the counter runs up by gridDim.x per meeting.  Returns false once the launch is aborted.
-__device__ __forceinline__ bool grid_meet(const FusedStepArgs &A, unsigned &meetings, int *s_abort) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned target = (++meetings) * gridDim.x;
-        __threadfence();
-        atomicAdd(A.sync_words, 1u);
-        unsigned polls = 0;
-        while (ld_acquire_u32(A.sync_words) < target) {
-            if ((++polls & 255u) == 0u && ld_acquire_u32(A.sync_words + 2) != 0u) {
-                *s_abort = 1;
-                break;
-            }
+#ifdef JGPT_B200_DECODE_TRACE
+// Timing build only: per CTA, SM clock at the marks of one layer (the second layer of the launch's last step).
+constexpr int kTraceMarks = 16;
+__device__ long long g_fused_trace[256 * kTraceMarks];
+#define FUSED_MARK(i)                                                                            \
+    do {                                                                                         \
+        if (tracing && threadIdx.x == 0) g_fused_trace[blockIdx.x * kTraceMarks + (i)] = clock64(); \
+    } while (0)
+#else
+#define FUSED_MARK(i) \
+    do {              \
+    } while (0)
+#endif
+
+struct Poll {
+    unsigned *abort_word;
+    unsigned tag;  // this launch's value of the abort word
+    int *status;
+    int failed;
+};
+
+// v[i] = the two pairs at addr(i), i < cnt, re-read until both carry `stamp`.  On a timeout or an abort the values
+// come back as zeros and pl.failed is set (the CTA leaves at its next block barrier).
+template <int N, class AddrFn>
+__device__ __forceinline__ void ll_load(uint4 (&v)[N], int cnt, unsigned stamp, Poll &pl, AddrFn addr) {
+#pragma unroll
+    for (int i = 0; i < N; i++) v[i] = i < cnt ? ld_pairs(addr(i)) : make_uint4(0u, stamp, 0u, stamp);
+    unsigned polls = 0;
+    for (;;) {
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; i++) ok = ok && v[i].y == stamp && v[i].w == stamp;
+        if (ok) return;
+        if ((++polls & 255u) == 0u) {
+            if (ld_relaxed_u32(pl.abort_word) == pl.tag) break;
             if (polls > kPollLimit) {
-                atomicOr(A.status, DEV_STATUS_WAIT_TIMEOUT);
-                atomicExch(A.sync_words + 2, 1u);
-                *s_abort = 1;
+                atomicOr(pl.status, DEV_STATUS_WAIT_TIMEOUT);
+                atomicExch(pl.abort_word, pl.tag);
                 break;
             }
         }
-    } else {
-        ++meetings;
+#pragma unroll
+        for (int i = 0; i < N; i++)
+            if (i < cnt && !(v[i].y == stamp && v[i].w == stamp)) v[i] = ld_pairs(addr(i));
     }
-    __syncthreads();
-    return *s_abort == 0;
+    pl.failed = 1;
+#pragma unroll
+    for (int i = 0; i < N; i++) v[i] = make_uint4(0u, stamp, 0u, stamp);
 }
 
 // Register tile of a projection unit: for up to two matrices, the thread's 4 columns of 3 k rows.
@@ -156,97 +195,150 @@ __device__ __forceinline__ void unit_reduce(float (&acc)[NW][R][4], float *red, 
     __syncthreads();
 }
 
-// x[r][:] += p[0][r][:] + p[1][r][:] + ... (ks partial rows, summed in that order), rows < n.
-template <int R>
-__device__ __forceinline__ void add_partials(float *x, const float *p, int ks, int n, int D) {
-    for (int e = threadIdx.x; e < n * D; e += kThreads) {
-        float s = __ldcg(p + e);
-        for (int j = 1; j < ks; j++) s += __ldcg(p + (size_t)j * R * D + e);
-        x[e] += s;
+constexpr int kGammaRegs = 4;  // norm weights a thread keeps in registers: columns tid, tid + 256, ... (d_model <= 1024)
+struct Gamma {
+    float g[kGammaRegs];
+};
+// Issued before a wait, so that the weights are in registers when the rows arrive.
+__device__ __forceinline__ void gamma_load(Gamma &gm, const float *gamma, int D) {
+#pragma unroll
+    for (int i = 0; i < kGammaRegs; i++) {
+        const int j = threadIdx.x + kThreads * i;
+        gm.g[i] = j < D ? __ldg(gamma + j) : 0.f;
     }
-    __syncthreads();
 }
 
-// a[r][:] = x[r][:] * inv_rms(x[r]) * gamma  (rms_norm_fwd_block_kernel, jgpt_cuda_extra_kernels_launches.inl:694-713)
+// x[r][:] += p[0][r][:] + p[1][r][:] + ... (ks partial rows, summed in that order; p == nullptr: nothing to add), then
+// a[r][:] = x[r][:] * inv_rms(x[r]) * gamma, rows < n  (rms_norm_fwd_block_kernel,
+// jgpt_cuda_extra_kernels_launches.inl:694-713).  Returns false when a wait gave up.
 template <int R>
-__device__ __forceinline__ void rms_norm_rows(const float *x, const float *gamma, float *a, int D, float eps, float *red) {
+__device__ __forceinline__ bool residual_norm(float *x, const uint2 *p, int ks, int n, int D, unsigned stamp, Poll &pl, const Gamma &gm,
+                                              float *a, float eps, float *red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float ss[R];
 #pragma unroll
+    for (int r = 0; r < R; r++) ss[r] = 0.f;
+    const int half = D / 2;
+    for (int e2 = threadIdx.x; e2 < n * half; e2 += kThreads) {
+        float v0 = x[2 * e2], v1 = x[2 * e2 + 1];
+        if (p) {
+            uint4 v[kFusedMaxKSplit];
+            ll_load<kFusedMaxKSplit>(v, ks, stamp, pl, [&](int j) { return p + (size_t)j * R * D + 2 * e2; });
+            float s0 = __uint_as_float(v[0].x), s1 = __uint_as_float(v[0].z);
+#pragma unroll
+            for (int j = 1; j < kFusedMaxKSplit; j++)
+                if (j < ks) s0 += __uint_as_float(v[j].x), s1 += __uint_as_float(v[j].z);
+            v0 += s0, v1 += s1;
+            x[2 * e2] = v0, x[2 * e2 + 1] = v1;
+        }
+        const int r = e2 / half;
+#pragma unroll
+        for (int rr = 0; rr < R; rr++)
+            if (rr == r) ss[rr] = fmaf(v0, v0, fmaf(v1, v1, ss[rr]));
+    }
+#pragma unroll
     for (int r = 0; r < R; r++) {
-        ss[r] = 0.f;
-        for (int j = threadIdx.x; j < D; j += kThreads) ss[r] = fmaf(x[r * D + j], x[r * D + j], ss[r]);
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], off);
         if (lane == 0) red[warp * R + r] = ss[r];
     }
-    __syncthreads();
+    if (__syncthreads_or(pl.failed)) return false;
 #pragma unroll
     for (int r = 0; r < R; r++) {
-        float s = 0.f;
+        float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; w++) s += red[w * R + r];
-        const float rms = sqrtf(s / (float)D + eps);
+        for (int w = 0; w < kWarps; w++) sum += red[w * R + r];
+        const float rms = sqrtf(sum / (float)D + eps);
         const float inv = (rms > 0.f && isfinite(rms)) ? (1.f / rms) : 0.f;
-        for (int j = threadIdx.x; j < D; j += kThreads) a[r * D + j] = x[r * D + j] * inv * __ldg(gamma + j);
+#pragma unroll
+        for (int i = 0; i < kGammaRegs; i++) {
+            const int j = threadIdx.x + kThreads * i;
+            if (j < D) a[r * D + j] = x[r * D + j] * inv * gm.g[i];
+        }
     }
     __syncthreads();
+    return true;
 }
 
 // One (row, head, chunk) of the attention: RoPE on q, the new token appended by the chunk that owns its slot, a
-// partial (maximum, sum, outputs) of this chunk's tokens left in `part`.
-__device__ __forceinline__ void attention_unit(const FusedStepArgs &A, int layer, int r, int h, int c, int step, float *red) {
+// partial (maximum, sum, outputs) of this chunk's tokens left in `part`.  `sq` = 3 * DH floats of shared memory.
+__device__ __forceinline__ bool attention_unit(const FusedStepArgs &A, int layer, int r, int h, int c, int step, unsigned stamp, Poll &pl,
+                                               float *red, float *sq) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = A.n;
     const int seq = A.idx[2 * n + r], rp = A.idx[3 * n + r] + step, len = A.idx[4 * n + r] + step;
     const int nbk = (len + 15) >> 4;
     const int b0 = c * A.cb, b1 = min(nbk, b0 + A.cb);  // a row shorter than the launch's longest leaves chunks empty
     const int t0 = b0 * 16, t1 = min(len, b1 * 16);
-    const float *row = A.qkv + (size_t)r * 3 * A.D;
     const float2 *cs = A.rope + (size_t)rp * (DH / 2);
+    const size_t layer_base = (size_t)layer * A.n_blocks;
+    // Rows of the cache do not depend on this step (the appended one apart): the first token of every thread is on its
+    // way before q has arrived.  A row appended in an earlier step of this launch was written by this same CTA (the
+    // unit -> CTA map is fixed for a launch), so a block barrier orders it; L1 is bypassed all the same.
+    __align__(16) __half kh[DH], vh[DH];
+    auto row_ptr = [&](int tok, __half *&kp) -> bool {
+        const int phys = __ldcg(A.table + (size_t)seq * A.mbs + (tok >> 4));
+        if (phys < 0 || phys >= A.n_blocks) {
+            atomicOr(A.status, DEV_STATUS_BAD_BLOCK);
+            return false;
+        }
+        kp = A.kv + ((layer_base + phys) * A.H + h) * (size_t)(2 * 16 * DH) + (size_t)(tok & 15) * DH;
+        return true;
+    };
+    auto row_load = [&](const __half *kp) {
+        reinterpret_cast<uint4 *>(kh)[0] = __ldcg(reinterpret_cast<const uint4 *>(kp));
+        reinterpret_cast<uint4 *>(kh)[1] = __ldcg(reinterpret_cast<const uint4 *>(kp) + 1);
+        reinterpret_cast<uint4 *>(vh)[0] = __ldcg(reinterpret_cast<const uint4 *>(kp + 16 * DH));
+        reinterpret_cast<uint4 *>(vh)[1] = __ldcg(reinterpret_cast<const uint4 *>(kp + 16 * DH) + 1);
+    };
+    __half *kp0 = nullptr;
+    const int tok0 = t0 + tid;
+    const bool ok0 = tok0 < t1 && row_ptr(tok0, kp0);
+    if (ok0 && tok0 != len - 1) row_load(kp0);
+    float2 rope[DH / 2];
+#pragma unroll
+    for (int j = 0; j < DH / 2; j++) rope[j] = __ldg(cs + j);
+    // this head's q, k, v of the row: 3 x 8 pairs
+    if (tid < 3 * DH / 2) {
+        uint4 v[1];
+        const uint2 *src = A.ll_qkv + (size_t)r * 3 * A.D + (size_t)(tid / (DH / 2)) * A.D + h * DH + 2 * (tid % (DH / 2));
+        ll_load<1>(v, 1, stamp, pl, [&](int) { return src; });
+        sq[2 * tid] = __uint_as_float(v[0].x), sq[2 * tid + 1] = __uint_as_float(v[0].z);
+    }
+    if (__syncthreads_or(pl.failed)) return false;
     float q[DH];
 #pragma unroll
-    for (int j = 0; j < DH / 4; j++) {
-        const float4 v = __ldcg(reinterpret_cast<const float4 *>(row + h * DH) + j);
-        const float2 w0 = __ldg(cs + 2 * j), w1 = __ldg(cs + 2 * j + 1);
-        q[4 * j] = __fsub_rn(__fmul_rn(v.x, w0.x), __fmul_rn(v.y, w0.y)) * A.scale_log2e;
-        q[4 * j + 1] = __fadd_rn(__fmul_rn(v.x, w0.y), __fmul_rn(v.y, w0.x)) * A.scale_log2e;
-        q[4 * j + 2] = __fsub_rn(__fmul_rn(v.z, w1.x), __fmul_rn(v.w, w1.y)) * A.scale_log2e;
-        q[4 * j + 3] = __fadd_rn(__fmul_rn(v.z, w1.y), __fmul_rn(v.w, w1.x)) * A.scale_log2e;
+    for (int j = 0; j < DH / 2; j++) {
+        const float2 w = rope[j];
+        const float x0 = sq[2 * j], x1 = sq[2 * j + 1];
+        q[2 * j] = __fsub_rn(__fmul_rn(x0, w.x), __fmul_rn(x1, w.y)) * A.scale_log2e;
+        q[2 * j + 1] = __fadd_rn(__fmul_rn(x0, w.y), __fmul_rn(x1, w.x)) * A.scale_log2e;
     }
     float m = -INFINITY, l = 0.f, o[DH];
 #pragma unroll
     for (int d = 0; d < DH; d++) o[d] = 0.f;
-    const size_t layer_base = (size_t)layer * A.n_blocks;
-    for (int tok = t0 + tid; tok < t1; tok += kThreads) {
-        const int phys = __ldcg(A.table + (size_t)seq * A.mbs + (tok >> 4));
-        if (phys < 0 || phys >= A.n_blocks) {
-            atomicOr(A.status, DEV_STATUS_BAD_BLOCK);
-            continue;
+    for (int tok = tok0; tok < t1; tok += kThreads) {
+        __half *kp = kp0;
+        if (tok == tok0) {
+            if (!ok0) continue;
+        } else {
+            if (!row_ptr(tok, kp)) continue;
+            if (tok != len - 1) row_load(kp);
         }
-        __half *kp = A.kv + ((layer_base + phys) * A.H + h) * (size_t)(2 * 16 * DH) + (size_t)(tok & 15) * DH;
-        __align__(16) __half kh[DH], vh[DH];
         if (tok == len - 1) {  // the appended token: RoPE'd k and raw v, rounded to fp16, stored and scored from registers
-            const float *kn = row + A.D + h * DH, *vn = row + 2 * A.D + h * DH;
 #pragma unroll
             for (int j = 0; j < DH / 2; j++) {
-                const float2 xk = __ldcg(reinterpret_cast<const float2 *>(kn) + j);
-                const float2 xv = __ldcg(reinterpret_cast<const float2 *>(vn) + j);
-                const float2 w = __ldg(cs + j);
-                kh[2 * j] = __float2half_rn(__fsub_rn(__fmul_rn(xk.x, w.x), __fmul_rn(xk.y, w.y)));
-                kh[2 * j + 1] = __float2half_rn(__fadd_rn(__fmul_rn(xk.x, w.y), __fmul_rn(xk.y, w.x)));
-                vh[2 * j] = __float2half_rn(xv.x);
-                vh[2 * j + 1] = __float2half_rn(xv.y);
+                const float2 w = rope[j];
+                const float k0 = sq[DH + 2 * j], k1 = sq[DH + 2 * j + 1];
+                kh[2 * j] = __float2half_rn(__fsub_rn(__fmul_rn(k0, w.x), __fmul_rn(k1, w.y)));
+                kh[2 * j + 1] = __float2half_rn(__fadd_rn(__fmul_rn(k0, w.y), __fmul_rn(k1, w.x)));
+                vh[2 * j] = __float2half_rn(sq[2 * DH + 2 * j]);
+                vh[2 * j + 1] = __float2half_rn(sq[2 * DH + 2 * j + 1]);
             }
             reinterpret_cast<uint4 *>(kp)[0] = reinterpret_cast<const uint4 *>(kh)[0];
             reinterpret_cast<uint4 *>(kp)[1] = reinterpret_cast<const uint4 *>(kh)[1];
             reinterpret_cast<uint4 *>(kp + 16 * DH)[0] = reinterpret_cast<const uint4 *>(vh)[0];
             reinterpret_cast<uint4 *>(kp + 16 * DH)[1] = reinterpret_cast<const uint4 *>(vh)[1];
-        } else {  // L1 is bypassed: in a launch of several steps another CTA wrote the rows of the earlier steps
-            reinterpret_cast<uint4 *>(kh)[0] = __ldcg(reinterpret_cast<const uint4 *>(kp));
-            reinterpret_cast<uint4 *>(kh)[1] = __ldcg(reinterpret_cast<const uint4 *>(kp) + 1);
-            reinterpret_cast<uint4 *>(vh)[0] = __ldcg(reinterpret_cast<const uint4 *>(kp + 16 * DH));
-            reinterpret_cast<uint4 *>(vh)[1] = __ldcg(reinterpret_cast<const uint4 *>(kp + 16 * DH) + 1);
         }
         float sc = 0.f;
 #pragma unroll
@@ -272,26 +364,33 @@ __device__ __forceinline__ void attention_unit(const FusedStepArgs &A, int layer
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
 #pragma unroll
-    for (int d = 0; d < DH; d++) {
-        float v = o[d] * f;
+    for (int d = 0; d < DH; d++) o[d] *= f;
+    // sum of the 32 lanes' o[0..16) with 16 shuffles: at every stage a lane keeps one half of what it still holds and
+    // adds its partner's copy of that half; lane L ends with dimension L >> 1
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        o[d] = v;
+    for (int width = DH / 2, off = 16; width >= 1; width >>= 1, off >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int j = 0; j < DH / 2; j++)
+            if (j < width) {
+                const float mine = upper ? o[j + width] : o[j], theirs = upper ? o[j] : o[j + width];
+                o[j] = mine + __shfl_xor_sync(0xffffffffu, theirs, off);
+            }
     }
-    if (lane == 0) {
+    o[0] += __shfl_xor_sync(0xffffffffu, o[0], 1);
+    {
         float *w = red + warp * PS;
-        w[0] = M, w[1] = l;
-#pragma unroll
-        for (int d = 0; d < DH; d++) w[2 + d] = o[d];
+        if (lane == 0) w[0] = M, w[1] = l;
+        if ((lane & 1) == 0) w[2 + (lane >> 1)] = o[0];
     }
     __syncthreads();
     if (tid < PS) {
         float Mx = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kWarps; w++) Mx = fmaxf(Mx, red[w * PS]);
-        float *dst = A.part + (((size_t)r * A.H + h) * A.nch + c) * PS;
+        uint2 *dst = A.ll_part + (((size_t)r * A.H + h) * A.nch + c) * PS;
         if (tid == 0) {
-            dst[0] = Mx;
+            st_pair(dst, Mx, stamp);
         } else {
             float s = 0.f;
 #pragma unroll
@@ -299,30 +398,47 @@ __device__ __forceinline__ void attention_unit(const FusedStepArgs &A, int layer
                 const float mw = red[w * PS];
                 s = fmaf(red[w * PS + tid], mw == -INFINITY ? 0.f : exp2f(mw - Mx), s);
             }
-            dst[tid] = s;
+            st_pair(dst + tid, s, stamp);
         }
     }
     __syncthreads();
+    return true;
 }
 
-// Merged attention output for model columns [k0, k1) of rows < n into a[r * lda + (k - k0)].
-__device__ __forceinline__ void merge_attention(const FusedStepArgs &A, float *a, int lda, int k0, int k1) {
-    const int span = k1 - k0;
-    for (int e = threadIdx.x; e < A.n * span; e += kThreads) {
-        const int r = e / span, k = k0 + e % span, h = k / DH, d = k % DH;
-        const float *pp = A.part + (((size_t)r * A.H + h) * A.nch) * PS;
-        float Mx = -INFINITY;
-        for (int c = 0; c < A.nch; c++) Mx = fmaxf(Mx, __ldcg(pp + c * PS));
-        float L = 0.f, acc = 0.f;
-        for (int c = 0; c < A.nch; c++) {
-            const float mc = __ldcg(pp + c * PS);
-            const float w = mc == -INFINITY ? 0.f : exp2f(mc - Mx);
-            L = fmaf(__ldcg(pp + c * PS + 1), w, L);
-            acc = fmaf(__ldcg(pp + c * PS + 2 + d), w, acc);
+// Merged attention output for model columns [k0, k1) (whole heads) of rows < n into a[r * lda + (k - k0)].  One thread
+// per (pair of adjacent dimensions, chunk) fetches that chunk's (maximum, sum) and its two outputs; the chunks meet in
+// shared memory (`stage`, 4 floats per item).
+__device__ __forceinline__ bool merge_attention(const FusedStepArgs &A, float *a, int lda, int k0, int k1, unsigned stamp, Poll &pl,
+                                               float *stage) {
+    const int span2 = (k1 - k0) / 2, items = A.n * span2 * A.nch;
+    const int per = (kThreads / A.nch) * A.nch;  // items of a pass: whole groups of chunks
+    for (int base = 0; base < items; base += per) {
+        const int it = (int)threadIdx.x < per ? base + (int)threadIdx.x : items;
+        if (it < items) {
+            const int c = it % A.nch, e = it / A.nch, r = e / span2, k = k0 + 2 * (e % span2), h = k / DH, d = k % DH;
+            const uint2 *pp = A.ll_part + (((size_t)r * A.H + h) * A.nch + c) * PS;
+            uint4 v[2];
+            ll_load<2>(v, 2, stamp, pl, [&](int i) { return pp + (i ? 2 + d : 0); });
+            reinterpret_cast<float4 *>(stage)[threadIdx.x] =
+                make_float4(__uint_as_float(v[0].x), __uint_as_float(v[0].z), __uint_as_float(v[1].x), __uint_as_float(v[1].z));
         }
-        a[r * lda + (k - k0)] = acc / fmaxf(L, 1e-12f);
+        if (__syncthreads_or(pl.failed)) return false;
+        if (it < items && it % A.nch == 0) {
+            const int e = it / A.nch, r = e / span2, k = k0 + 2 * (e % span2);
+            const float4 *st = reinterpret_cast<const float4 *>(stage) + threadIdx.x;
+            float Mx = -INFINITY, L = 0.f, acc0 = 0.f, acc1 = 0.f;
+            for (int c = 0; c < A.nch; c++) Mx = fmaxf(Mx, st[c].x);
+            for (int c = 0; c < A.nch; c++) {
+                const float4 pc = st[c];
+                const float w = pc.x == -INFINITY ? 0.f : exp2f(pc.x - Mx);
+                L = fmaf(pc.y, w, L), acc0 = fmaf(pc.z, w, acc0), acc1 = fmaf(pc.w, w, acc1);
+            }
+            const float inv = 1.f / fmaxf(L, 1e-12f);
+            a[r * lda + (k - k0)] = acc0 * inv, a[r * lda + (k - k0) + 1] = acc1 * inv;
+        }
+        __syncthreads();
     }
-    __syncthreads();
+    return true;
 }
 
 template <int R>
@@ -331,24 +447,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
     float *x = sm;                    // [R][D]  the residual rows
     float *a = x + R * A.D;           // [R][max(D, F)]  what the current projection multiplies
     float *red = a + R * A.amax;      // reductions
-    __shared__ int s_abort;
+    float *sq = red + kWarps * 2 * 2 * R * 4 + kWarps * PS;  // q, k, v of one head
+    float *stage = sq + 3 * DH;                              // [256][4] chunk partials on their way to be merged
     __shared__ int s_tok[R];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, G = gridDim.x, n = A.n, D = A.D, F = A.F;
     const int half_col = (tid & 1) * 4;
-    if (tid == 0) s_abort = 0;
     for (int e = tid; e < R * D; e += kThreads) x[e] = 0.f;
     for (int e = tid; e < R * A.amax; e += kThreads) a[e] = 0.f;
     __syncthreads();
-    unsigned meetings = 0;
+    Poll pl{A.sync_words, A.stamp0 + 1u, A.status, 0};
     const int nA = 3 * D / 8, nO = D / 8, nD = F / 8, nL = A.vocab / 8;
     const int kso = A.ks_o, klo = A.kl_o, ks2 = A.ks_2, kl2 = A.kl_2;
+    const bool out_lane = warp == 0 && lane < R * 8 && (lane >> 3) < n;  // lanes that hold a unit's results
+    const int out_r = lane >> 3, out_c = lane & 7;
 
     WTile t;
+    Gamma gam;
     bool have = false;
     auto load_A = [&](int l, int u) {  // unit u of the Q,K,V product: 8 columns of one of the three matrices
         const int z = u / nO, c0 = (u % nO) * 8;
-        const float *W = z == 0 ? A.L[l].wq : (z == 1 ? A.L[l].wk : A.L[l].wv);
+        const float *W = z == 0 ? A.Lw[l].wq : (z == 1 ? A.Lw[l].wk : A.Lw[l].wv);
         tile_load<1>(t, W, nullptr, D, c0 + half_col, 0, D);
     };
     if (b < nA) load_A(0, b), have = true;
@@ -364,100 +483,117 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
         }
         __syncthreads();
 
+        gamma_load(gam, A.Lw[0].norm1, D);
         for (int l = 0; l < A.layers; l++) {
+            const unsigned stamp = A.stamp0 + (unsigned)(step * A.layers + l) + 1u;  // of everything this layer writes
+#ifdef JGPT_B200_DECODE_TRACE
+            const bool tracing = step == A.steps - 1 && l == 1;
+#endif
+            FUSED_MARK(0);
             // ---- A: norm1 + Q,K,V
-            if (l > 0) add_partials<R>(x, A.pw2, ks2, n, D);
-            rms_norm_rows<R>(x, A.L[l].norm1, a, D, A.eps, red);
+            if (!residual_norm<R>(x, l > 0 ? A.ll_pw2 : nullptr, ks2, n, D, stamp - 1u, pl, gam, a, A.eps, red)) goto leave;
+            FUSED_MARK(2);
             for (int u = b; u < nA; u += G) {
                 const int z = u / nO, c0 = (u % nO) * 8;
-                const float *W = z == 0 ? A.L[l].wq : (z == 1 ? A.L[l].wk : A.L[l].wv);
+                const float *W = z == 0 ? A.Lw[l].wq : (z == 1 ? A.Lw[l].wk : A.Lw[l].wv);
                 float acc[1][R][4], res[1];
                 unit_fma<R, 1>(t, have && u == b, W, nullptr, D, c0 + half_col, 0, D, a, D, 0, acc);
+                FUSED_MARK(1);
                 unit_reduce<R, 1>(acc, red, res);
-                if (warp == 0 && lane < R * 8 && (lane >> 3) < n) A.qkv[(size_t)(lane >> 3) * 3 * D + z * D + c0 + (lane & 7)] = res[0];
+                FUSED_MARK(7);
+                if (out_lane) st_pair(A.ll_qkv + (size_t)out_r * 3 * D + z * D + c0 + out_c, res[0], stamp);
             }
             have = false;
-            if (!grid_meet(A, meetings, &s_abort)) goto leave;
+            if (b < nO * kso) {  // Wo: unit = 8 columns x one k range; on its way while the attention runs
+                const int c0 = (b % nO) * 8, k0 = (b / nO) * klo;
+                tile_load<1>(t, A.Lw[l].wo, nullptr, D, c0 + half_col, k0, min(D, k0 + klo));
+                have = true;
+            }
 
+            gamma_load(gam, A.Lw[l].norm2, D);
+            FUSED_MARK(3);
             // ---- B: append + attention partials
             for (int u = b; u < n * A.H * A.nch; u += G) {
                 const int c = u % A.nch, h = (u / A.nch) % A.H, r = u / (A.nch * A.H);
-                attention_unit(A, l, r, h, c, step, red);
+                if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq)) goto leave;
             }
-            if (b < nO * kso) {  // Wo: unit = 8 columns x one k range
-                const int c0 = (b % nO) * 8, k0 = (b / nO) * klo;
-                tile_load<1>(t, A.L[l].wo, nullptr, D, c0 + half_col, k0, min(D, k0 + klo));
-                have = true;
-            }
-            if (!grid_meet(A, meetings, &s_abort)) goto leave;
 
+            FUSED_MARK(4);
             // ---- C: merged attention rows . Wo, partial rows per k range
             for (int u = b; u < nO * kso; u += G) {
                 const int c0 = (u % nO) * 8, kj = u / nO, k0 = kj * klo, k1 = min(D, k0 + klo);
-                merge_attention(A, a, klo, k0, k1);
+                if (!merge_attention(A, a, klo, k0, k1, stamp, pl, stage)) goto leave;
+                FUSED_MARK(5);
                 float acc[1][R][4], res[1];
-                unit_fma<R, 1>(t, have && u == b, A.L[l].wo, nullptr, D, c0 + half_col, k0, k1, a, klo, k0, acc);
+                unit_fma<R, 1>(t, have && u == b, A.Lw[l].wo, nullptr, D, c0 + half_col, k0, k1, a, klo, k0, acc);
+                FUSED_MARK(12);
                 unit_reduce<R, 1>(acc, red, res);
-                if (warp == 0 && lane < R * 8 && (lane >> 3) < n) A.po[((size_t)kj * R + (lane >> 3)) * D + c0 + (lane & 7)] = res[0];
+                FUSED_MARK(13);
+                if (out_lane) st_pair(A.ll_po + ((size_t)kj * R + out_r) * D + c0 + out_c, res[0], stamp);
             }
             have = false;
             if (b < nD) {
-                tile_load<2>(t, A.L[l].w1, A.L[l].w3, F, b * 8 + half_col, 0, D);
+                tile_load<2>(t, A.Lw[l].w1, A.Lw[l].w3, F, b * 8 + half_col, 0, D);
                 have = true;
             }
-            if (!grid_meet(A, meetings, &s_abort)) goto leave;
 
+            FUSED_MARK(6);
             // ---- D: x += attention projection; norm2 + W1, W3 + SwiGLU (sigmoid_kernel / mul_kernel, same file :799-832)
-            add_partials<R>(x, A.po, kso, n, D);
-            rms_norm_rows<R>(x, A.L[l].norm2, a, D, A.eps, red);
+            if (!residual_norm<R>(x, A.ll_po, kso, n, D, stamp, pl, gam, a, A.eps, red)) goto leave;
+            FUSED_MARK(8);
             for (int u = b; u < nD; u += G) {
                 float acc[2][R][4], res[2];
-                unit_fma<R, 2>(t, have && u == b, A.L[l].w1, A.L[l].w3, F, u * 8 + half_col, 0, D, a, D, 0, acc);
+                unit_fma<R, 2>(t, have && u == b, A.Lw[l].w1, A.Lw[l].w3, F, u * 8 + half_col, 0, D, a, D, 0, acc);
                 unit_reduce<R, 2>(acc, red, res);
-                if (warp == 0 && lane < R * 8 && (lane >> 3) < n) {
+                if (out_lane) {
                     const float gv = res[1];
-                    float s;
-                    if (gv >= 20.f) s = 1.f;
-                    else if (gv <= -20.f) s = 0.f;
-                    else s = 1.f / (1.f + expf(-gv));
-                    A.act[(size_t)(lane >> 3) * F + u * 8 + (lane & 7)] = res[0] * (gv * s);
+                    float sg;
+                    if (gv >= 20.f) sg = 1.f;
+                    else if (gv <= -20.f) sg = 0.f;
+                    else sg = 1.f / (1.f + expf(-gv));
+                    st_pair(A.ll_act + (size_t)out_r * F + u * 8 + out_c, res[0] * (gv * sg), stamp);
                 }
             }
             have = false;
             if (b < nO * ks2) {
                 const int c0 = (b % nO) * 8, k0 = (b / nO) * kl2;
-                tile_load<1>(t, A.L[l].w2, nullptr, D, c0 + half_col, k0, min(F, k0 + kl2));
+                tile_load<1>(t, A.Lw[l].w2, nullptr, D, c0 + half_col, k0, min(F, k0 + kl2));
                 have = true;
             }
-            if (!grid_meet(A, meetings, &s_abort)) goto leave;
 
+            gamma_load(gam, l + 1 < A.layers ? A.Lw[l + 1].norm1 : A.norm_final, D);
+            FUSED_MARK(9);
             // ---- E: activation . W2, partial rows per k range
             for (int u = b; u < nO * ks2; u += G) {
-                const int c0 = (u % nO) * 8, kj = u / nO, k0 = kj * kl2, k1 = min(F, k0 + kl2);
-                for (int e = tid; e < n * (k1 - k0); e += kThreads) {
-                    const int r = e / (k1 - k0), k = e % (k1 - k0);
-                    a[r * kl2 + k] = __ldcg(A.act + (size_t)r * F + k0 + k);
+                const int c0 = (u % nO) * 8, kj = u / nO, k0 = kj * kl2, k1 = min(F, k0 + kl2), span2 = (k1 - k0) / 2;
+                for (int e = tid; e < n * span2; e += kThreads) {
+                    const int r = e / span2, k = 2 * (e % span2);
+                    uint4 v[1];
+                    const uint2 *src = A.ll_act + (size_t)r * F + k0 + k;
+                    ll_load<1>(v, 1, stamp, pl, [&](int) { return src; });
+                    a[r * kl2 + k] = __uint_as_float(v[0].x), a[r * kl2 + k + 1] = __uint_as_float(v[0].z);
                 }
-                __syncthreads();
+                if (__syncthreads_or(pl.failed)) goto leave;
+                FUSED_MARK(10);
                 float acc[1][R][4], res[1];
-                unit_fma<R, 1>(t, have && u == b, A.L[l].w2, nullptr, D, c0 + half_col, k0, k1, a, kl2, k0, acc);
+                unit_fma<R, 1>(t, have && u == b, A.Lw[l].w2, nullptr, D, c0 + half_col, k0, k1, a, kl2, k0, acc);
                 unit_reduce<R, 1>(acc, red, res);
-                if (warp == 0 && lane < R * 8 && (lane >> 3) < n) A.pw2[((size_t)kj * R + (lane >> 3)) * D + c0 + (lane & 7)] = res[0];
+                if (out_lane) st_pair(A.ll_pw2 + ((size_t)kj * R + out_r) * D + c0 + out_c, res[0], stamp);
             }
             have = false;
+            FUSED_MARK(11);
             if (l + 1 < A.layers) {
                 if (b < nA) load_A(l + 1, b), have = true;
             } else if (b < nL) {
                 tile_load<1>(t, A.lm_head, nullptr, A.vocab, b * 8 + half_col, 0, D);
                 have = true;
             }
-            if (!grid_meet(A, meetings, &s_abort)) goto leave;
         }
 
         // ---- final norm + LM head; every CTA keeps the best (value, lowest index) of its columns per row
         {
-            add_partials<R>(x, A.pw2, ks2, n, D);
-            rms_norm_rows<R>(x, A.norm_final, a, D, A.eps, red);
+            const unsigned stamp = A.stamp0 + (unsigned)((step + 1) * A.layers);  // the last layer's
+            if (!residual_norm<R>(x, A.ll_pw2, ks2, n, D, stamp, pl, gam, a, A.eps, red)) goto leave;
             float best = -INFINITY;
             int best_i = 0x7fffffff;
             if (!have && b < nL) tile_load<1>(t, A.lm_head, nullptr, A.vocab, b * 8 + half_col, 0, D);
@@ -468,9 +604,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                 unit_fma<R, 1>(t, true, A.lm_head, nullptr, A.vocab, u * 8 + half_col, 0, D, a, D, 0, acc);
                 unit_reduce<R, 1>(acc, red, res);
                 if (u + G < nL) t = tn;
-                if (warp == 0 && lane < R * 8 && (lane >> 3) < n) {
-                    const int col = u * 8 + (lane & 7);
-                    A.logits[(size_t)(lane >> 3) * A.vocab + col] = res[0];
+                if (out_lane) {
+                    const int col = u * 8 + out_c;
+                    A.logits[(size_t)out_r * A.vocab + col] = res[0];
                     if (res[0] > best || (res[0] == best && col < best_i)) best = res[0], best_i = col;
                 }
             }
@@ -482,21 +618,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                     const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
                     if (ov > best || (ov == best && oi < best_i)) best = ov, best_i = oi;
                 }
-                if (lane < R * 8 && (lane & 7) == 0) {
-                    A.cand_v[(size_t)b * R + (lane >> 3)] = best;
-                    A.cand_i[(size_t)b * R + (lane >> 3)] = best_i;
+                if (lane < R * 8 && out_c == 0) {  // (value, stamp), (index, stamp)
+                    uint2 *dst = A.ll_cand + ((size_t)b * R + out_r) * 2;
+                    st_pair(dst, best, stamp);
+                    st_pair(dst + 1, __int_as_float(best_i), stamp);
                 }
             }
             if (step + 1 < A.steps && b < nA) load_A(0, b), have = true;
-            if (!grid_meet(A, meetings, &s_abort)) goto leave;
-            // every CTA picks the tokens itself (the same comparison order everywhere): no further meeting
+            // every CTA picks the tokens itself (the same comparison order everywhere)
             if (warp < n) {
                 float bv = -INFINITY;
                 int bi = 0x7fffffff;
-                for (int g = lane; g < G; g += 32) {
-                    const float v = __ldcg(A.cand_v + (size_t)g * R + warp);
-                    const int i = __ldcg(A.cand_i + (size_t)g * R + warp);
-                    if (v > bv || (v == bv && i < bi)) bv = v, bi = i;
+                for (int g0 = lane; g0 < G; g0 += 32 * kCandBatch) {  // this lane's CTAs, a batch of polls in flight at a time
+                    uint4 v[kCandBatch];
+                    const int cnt = min(kCandBatch, (G - g0 + 31) / 32);
+                    ll_load<kCandBatch>(v, cnt, stamp, pl, [&](int i) { return A.ll_cand + ((size_t)(g0 + 32 * i) * R + warp) * 2; });
+#pragma unroll
+                    for (int i = 0; i < kCandBatch; i++) {
+                        const float cv = __uint_as_float(v[i].x);
+                        const int ci = (int)v[i].z;
+                        if (i < cnt && !pl.failed && (cv > bv || (cv == bv && ci < bi))) bv = cv, bi = ci;
+                    }
                 }
 #pragma unroll
                 for (int off = 16; off >= 1; off >>= 1) {
@@ -510,27 +652,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                     if (b == 0) A.next[(size_t)step * n + warp] = bi;
                 }
             }
-            __syncthreads();
+            if (__syncthreads_or(pl.failed)) goto leave;
             steps_done = step + 1;
             if (A.stop_on_zero && s_tok[0] == 0) break;
         }
     }
 leave:
-    __syncthreads();
-    if (tid == 0) {
-        if (b == 0) *A.steps_done = steps_done;
-        __threadfence();
-        // the last CTA to leave puts the meeting words back for the next launch
-        if (atomicAdd(A.sync_words + 1, 1u) == (unsigned)G - 1u) {
-            A.sync_words[0] = 0u, A.sync_words[1] = 0u, A.sync_words[2] = 0u;
-            __threadfence();
-        }
-    }
+    if (b == 0 && tid == 0) *A.steps_done = steps_done;
 }
 
 template <int R>
 static size_t fused_smem_bytes(const FusedStepArgs &A) {
-    return sizeof(float) * ((size_t)R * A.D + (size_t)R * A.amax + (size_t)kWarps * 2 * 2 * R * 4 + kWarps * PS);
+    return sizeof(float) * ((size_t)R * A.D + (size_t)R * A.amax + (size_t)kWarps * 2 * 2 * R * 4 + kWarps * PS + 3 * DH + kThreads * 4);
 }
 
 template <int R>
@@ -562,6 +695,13 @@ static int32_t launch_rows(Ctx *ctx, FusedStepArgs &A) {
 }
 
 }  // namespace
+
+#ifdef JGPT_B200_DECODE_TRACE
+extern "C" __attribute__((visibility("default"))) int32_t jgpt_debug_fused_trace_read(long long *host, int32_t n_ctas) {
+    JGPT_CUDA_TRY(cudaMemcpyFromSymbol(host, g_fused_trace, sizeof(long long) * (size_t)n_ctas * kTraceMarks));
+    return JGPT_OK;
+}
+#endif
 
 int fused_step_max_rows() { return 4; }
 

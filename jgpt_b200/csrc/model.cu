@@ -66,9 +66,10 @@ struct Model {
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
     // Steps of up to four rows as one cooperative launch (decode_fused.cu; JGPT_B200_FUSED_STEP=0: off).  Sized on first use.
     int fused_step = 1;
-    LayerW *d_layers = nullptr;
-    float *f_floats = nullptr;  // qkv, attention partials, projection partials, activation, candidates
-    int *f_ints = nullptr;      // candidate indices, tokens of a multi-step launch, steps done, meeting words
+    uint2 *f_pairs = nullptr;   // exchange buffers of (value, stamp) pairs: qkv, attention partials, projection partials, ...
+    uint64_t f_pairs_n = 0;
+    uint32_t f_stamp = 0;       // stamps handed out so far; a launch uses f_stamp + 1 ... f_stamp + steps * layers
+    int *f_ints = nullptr;      // tokens of a multi-step launch, steps done, abort word
     int *h_fused = nullptr;     // pinned: [kFusedMaxSteps * 4] tokens + steps done
 };
 constexpr int kFusedMaxSteps = 256;  // greedy steps one launch runs at most
@@ -1057,53 +1058,62 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
 static bool fused_ok(const Model *m, const Pool *p, int n) {
     const size_t smem = sizeof(float) * 4 * ((size_t)m->d_model + (size_t)std::max(m->d_model, m->d_ff)) + 4096;
     return m->fused_step && !m->strict && n >= 1 && n <= fused_step_max_rows() && p->dhead == 16 && m->d_model == m->heads * 16 &&
-           m->d_model % 8 == 0 && m->d_ff % 8 == 0 && m->vocab % 8 == 0 && smem <= 60 * 1024;
+           m->d_model % 8 == 0 && m->d_ff % 8 == 0 && m->vocab % 8 == 0 && smem <= 60 * 1024 && m->layers <= kFusedMaxLayers &&
+           m->d_model <= 1024;
+}
+static size_t fused_pair_count(const Model *m) {
+    const size_t D = m->d_model, F = m->d_ff, H = m->heads, G = m->ctx->sm_count, R = 4;
+    return R * 3 * D + R * H * kFusedMaxChunks * 18 + 2 * (size_t)kFusedMaxKSplit * R * D + R * F + G * R * 2;
 }
 static int32_t ensure_fused(Model *m) {
-    if (m->d_layers) return JGPT_OK;
-    const size_t D = m->d_model, F = m->d_ff, H = m->heads, G = m->ctx->sm_count, R = 4;
-    const size_t nf = R * 3 * D + R * H * kFusedMaxChunks * 18 + 2 * (size_t)kFusedMaxKSplit * R * D + R * F + G * R;
-    const size_t ni = G * R + (size_t)kFusedMaxSteps * R + 4 + 4;
-    JGPT_CUDA_TRY(cudaMalloc(&m->f_floats, sizeof(float) * nf));
-    JGPT_CUDA_TRY(cudaMalloc(&m->f_ints, sizeof(int) * ni));
+    if (m->f_pairs) return JGPT_OK;
+    const size_t R = 4, ni = (size_t)kFusedMaxSteps * R + 4 + 4;
+    m->f_pairs_n = fused_pair_count(m);
+    if (!m->f_ints) JGPT_CUDA_TRY(cudaMalloc(&m->f_ints, sizeof(int) * ni));
     JGPT_CUDA_TRY(cudaMemsetAsync(m->f_ints, 0, sizeof(int) * ni, m->ctx->stream));
-    JGPT_CUDA_TRY(cudaHostAlloc(&m->h_fused, sizeof(int) * ((size_t)kFusedMaxSteps * R + 4), cudaHostAllocDefault));
-    LayerW *dl = nullptr;
-    JGPT_CUDA_TRY(cudaMalloc(&dl, sizeof(LayerW) * m->L.size()));
-    JGPT_CUDA_TRY(cudaMemcpyAsync(dl, m->L.data(), sizeof(LayerW) * m->L.size(), cudaMemcpyHostToDevice, m->ctx->stream));
-    JGPT_CUDA_TRY(cudaStreamSynchronize(m->ctx->stream));
-    m->d_layers = dl;
+    if (!m->h_fused) JGPT_CUDA_TRY(cudaHostAlloc(&m->h_fused, sizeof(int) * ((size_t)kFusedMaxSteps * R + 4), cudaHostAllocDefault));
+    uint2 *pairs = nullptr;
+    JGPT_CUDA_TRY(cudaMalloc(&pairs, sizeof(uint2) * m->f_pairs_n));
+    JGPT_CUDA_TRY(cudaMemsetAsync(pairs, 0, sizeof(uint2) * m->f_pairs_n, m->ctx->stream));  // stamp 0: never data
+    m->f_pairs = pairs;
+    m->f_stamp = 0;
     return JGPT_OK;
 }
+static int *fused_tokens_dev(Model *m) { return m->f_ints; }
+static int *fused_steps_done_dev(Model *m) { return m->f_ints + (size_t)kFusedMaxSteps * 4; }
 // Enqueues `steps` decode steps of the n rows described in m->d_idx (already uploaded).  Tokens go to `next_dev`
 // ([steps][n]); with stop_on_zero (n == 1) the launch ends after a sampled 0.
 static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_zero, int max_len_after, int *next_dev) {
     const size_t D = m->d_model, F = m->d_ff, H = m->heads, G = m->ctx->sm_count, R = 4;
+    const uint32_t need = (uint32_t)steps * (uint32_t)m->layers;
+    if (m->f_stamp > 0xE0000000u - need) {  // stamps about to wrap: start over from clean buffers
+        JGPT_CUDA_TRY(cudaMemsetAsync(m->f_pairs, 0, sizeof(uint2) * m->f_pairs_n, m->ctx->stream));
+        JGPT_CUDA_TRY(cudaMemsetAsync(fused_steps_done_dev(m) + 4, 0, sizeof(int) * 4, m->ctx->stream));
+        m->f_stamp = 0;
+    }
     FusedStepArgs A = {};
-    A.tok = m->tok, A.pos = m->pos, A.norm_final = m->norm_final, A.lm_head = m->lm_head, A.L = m->d_layers;
+    A.tok = m->tok, A.pos = m->pos, A.norm_final = m->norm_final, A.lm_head = m->lm_head;
+    for (int l = 0; l < m->layers; l++) A.Lw[l] = m->L[(size_t)l];
     A.vocab = m->vocab, A.max_seq = m->max_seq, A.D = m->d_model, A.H = m->heads, A.layers = m->layers, A.F = m->d_ff, A.eps = m->eps;
     A.kv = p->kv, A.table = p->d_table, A.rope = p->d_rope, A.n_blocks = p->n_blocks, A.mbs = p->max_blocks_per_seq;
     A.idx = m->d_idx, A.n = n, A.steps = steps, A.stop_on_zero = stop_on_zero;
-    float *f = m->f_floats;
-    A.qkv = f, f += R * 3 * D;
-    A.part = f, f += R * H * kFusedMaxChunks * 18;
-    A.po = f, f += (size_t)kFusedMaxKSplit * R * D;
-    A.pw2 = f, f += (size_t)kFusedMaxKSplit * R * D;
-    A.act = f, f += R * F;
-    A.cand_v = f;
+    uint2 *f = m->f_pairs;
+    A.ll_qkv = f, f += R * 3 * D;
+    A.ll_part = f, f += R * H * kFusedMaxChunks * 18;
+    A.ll_po = f, f += (size_t)kFusedMaxKSplit * R * D;
+    A.ll_pw2 = f, f += (size_t)kFusedMaxKSplit * R * D;
+    A.ll_act = f, f += R * F;
+    A.ll_cand = f;
+    A.stamp0 = m->f_stamp;
+    m->f_stamp += need;
     A.logits = m->logits;
-    int *ip = m->f_ints;
-    A.cand_i = ip, ip += G * R;
-    ip += (size_t)kFusedMaxSteps * R;  // tokens of a multi-step launch (next_dev points here or at d_next)
-    A.steps_done = ip, ip += 4;
-    A.sync_words = reinterpret_cast<unsigned *>(ip);
+    A.steps_done = fused_steps_done_dev(m);
+    A.sync_words = reinterpret_cast<unsigned *>(fused_steps_done_dev(m) + 4);
     A.next = next_dev;
     A.status = m->ctx->d_status;
     fused_step_plan(A, m->ctx->sm_count, max_len_after);
     return launch_decode_fused(m->ctx, A);
 }
-static int *fused_tokens_dev(Model *m) { return m->f_ints + (size_t)m->ctx->sm_count * 4; }
-static int *fused_steps_done_dev(Model *m) { return fused_tokens_dev(m) + (size_t)kFusedMaxSteps * 4; }
 
 }  // namespace jgpt
 
@@ -1235,7 +1245,7 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     drop_weight_images(m);  // and the decode graphs
     cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b), cudaFree(m->d_u), cudaFree(m->d_samp);
     cudaFreeHost(m->h_u);
-    cudaFree(m->d_layers), cudaFree(m->f_floats), cudaFree(m->f_ints), cudaFreeHost(m->h_fused);
+    cudaFree(m->f_pairs), cudaFree(m->f_ints), cudaFreeHost(m->h_fused);
     delete m;
     return JGPT_OK;
 }

@@ -482,7 +482,7 @@ def test_overlapped_launches_inside_the_decode_step_change_nothing(ctx, level, m
     outs = []
     for lv in (0, level):
         monkeypatch.setenv("JGPT_B200_STEP_OVERLAP", str(lv))
-        gm = GPTModel(ctx, 96, 80, 64, 4, 3, 128, rmsNormEps=1e-5)
+        gm = GPTModel(ctx, 96, 80, 64, 4, 3, 128, rmsNormEps=1e-5, maxRows=256)
         gm.setParameters(om.tensors())
         pool = gm.newPool(n_blocks=6 * 5, max_seqs=6)
         try:  # six rows: the multi-launch step (up to four rows run as one fused launch instead)
