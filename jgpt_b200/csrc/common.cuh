@@ -225,6 +225,39 @@ int fused_step_max_rows();
 void fused_step_plan(FusedStepArgs &A, int sm_count, int max_len);
 int32_t launch_decode_fused(Ctx *ctx, FusedStepArgs &A);
 
+// A decode step of a batch (decode_batch.cu): tile products on the tensor cores, a warp per attention unit, the same
+// stamped hand-over between the phases.  Exchange arrays hold (value, stamp) pairs.
+struct BatchStepArgs {
+    const float *tok, *pos, *norm_final, *lm_head;
+    LayerW Lw[kFusedMaxLayers];
+    const float *w13[kFusedMaxLayers];  // W1/W3 interleaved in groups of 16 columns, [D][2 F]
+    int vocab, max_seq, D, H, layers, F;
+    float eps;
+    __half *kv;
+    const int *table;
+    const float2 *rope;
+    int n_blocks, mbs;
+    const int *idx;  // [5][n] ids, position rows, sequence ids, RoPE positions, lengths after the append
+    int n;
+    uint2 *xa, *xb;    // [n][D] residual rows (ping-pong)
+    uint2 *ssa, *ssb;  // [n][D / 32] partial row sums of squares
+    uint2 *qkv;        // [n][3 D]
+    uint2 *att;        // [n][D]
+    uint2 *act;        // [n][F]
+    uint2 *cand;       // [vocab tiles][n][2] best logit of a tile and its index
+    float *part;       // [n][H][nch_max][18] split-sequence partials (plain; merged through tickets)
+    int *tickets;      // [n][H], zero between launches
+    unsigned stamp0;   // stamps of this launch: stamp0 + 1 ... stamp0 + layers + 2
+    unsigned *abort_word;
+    int *status;
+    float *logits;  // [n][vocab]
+    int *next;      // [n]
+    int cb, nch_max, kmax;
+    float scale_log2e;
+};
+void batch_step_plan(BatchStepArgs &A, int sm_count, const int *lens_host);
+int32_t launch_decode_batch(Ctx *ctx, BatchStepArgs &A);
+
 // Kernel launchers (defined in the .cu files)
 int32_t launch_kv_append(Pool *p, int layer, const float *k, const float *v, const int *seq_ids,
                          const int *slot_pos, const int *rope_pos, int n);

@@ -26,6 +26,7 @@
 // launch's tag in the abort word and its CTA leaves; the others see the tag and leave too.  Stamps grow from launch
 // to launch, so whatever an abandoned launch left behind is never mistaken for data.
 #include "common.cuh"
+#include "exchange.cuh"
 #include "ptx.cuh"
 
 #include <algorithm>
@@ -42,23 +43,7 @@ constexpr int kSlices = kThreads / 2;  // k slices of a projection unit: thread 
 constexpr int kTileK = 3 * kSlices;    // k rows one register tile of a unit covers
 constexpr int DH = 16;                 // head size of this path
 constexpr int PS = DH + 2;             // an attention partial: running maximum, sum, DH unnormalised outputs
-constexpr unsigned kPollLimit = 1u << 21;
 constexpr int kCandBatch = 5;          // per-CTA candidates a lane polls at a time when the tokens are picked
-
-__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// Two (value, stamp) pairs.  Each 8-byte half is written with one store, so a half is never seen torn.
-__device__ __forceinline__ uint4 ld_pairs(const uint2 *p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_pair(uint2 *p, float v, unsigned stamp) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(stamp) : "memory");
-}
 
 #ifdef JGPT_B200_DECODE_TRACE
 // Timing build only: per CTA, SM clock at the marks of one layer (the second layer of the launch's last step).
@@ -73,42 +58,6 @@ __device__ long long g_fused_trace[256 * kTraceMarks];
     do {              \
     } while (0)
 #endif
-
-struct Poll {
-    unsigned *abort_word;
-    unsigned tag;  // this launch's value of the abort word
-    int *status;
-    int failed;
-};
-
-// v[i] = the two pairs at addr(i), i < cnt, re-read until both carry `stamp`.  On a timeout or an abort the values
-// come back as zeros and pl.failed is set (the CTA leaves at its next block barrier).
-template <int N, class AddrFn>
-__device__ __forceinline__ void ll_load(uint4 (&v)[N], int cnt, unsigned stamp, Poll &pl, AddrFn addr) {
-#pragma unroll
-    for (int i = 0; i < N; i++) v[i] = i < cnt ? ld_pairs(addr(i)) : make_uint4(0u, stamp, 0u, stamp);
-    unsigned polls = 0;
-    for (;;) {
-        bool ok = true;
-#pragma unroll
-        for (int i = 0; i < N; i++) ok = ok && v[i].y == stamp && v[i].w == stamp;
-        if (ok) return;
-        if ((++polls & 255u) == 0u) {
-            if (ld_relaxed_u32(pl.abort_word) == pl.tag) break;
-            if (polls > kPollLimit) {
-                atomicOr(pl.status, DEV_STATUS_WAIT_TIMEOUT);
-                atomicExch(pl.abort_word, pl.tag);
-                break;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < N; i++)
-            if (i < cnt && !(v[i].y == stamp && v[i].w == stamp)) v[i] = ld_pairs(addr(i));
-    }
-    pl.failed = 1;
-#pragma unroll
-    for (int i = 0; i < N; i++) v[i] = make_uint4(0u, stamp, 0u, stamp);
-}
 
 // Register tile of a projection unit: for up to two matrices, the thread's 4 columns of 3 k rows.
 struct WTile {

@@ -71,7 +71,15 @@ struct Model {
     uint32_t f_stamp = 0;       // stamps handed out so far; a launch uses f_stamp + 1 ... f_stamp + steps * layers
     int *f_ints = nullptr;      // tokens of a multi-step launch, steps done, abort word
     int *h_fused = nullptr;     // pinned: [kFusedMaxSteps * 4] tokens + steps done
+    // The same for batches (decode_batch.cu; JGPT_B200_FUSED_BATCH=1: on): rows 5 .. fused_batch_rows
+    int fused_batch = 0;
+    int fused_batch_rows = 0;   // rows the buffers below are sized for
+    uint2 *fb_pairs = nullptr;
+    uint64_t fb_pairs_n = 0;
+    float *fb_part = nullptr;
+    int *fb_tickets = nullptr;
 };
+constexpr int kFusedBatchMaxRows = 256;
 constexpr int kFusedMaxSteps = 256;  // greedy steps one launch runs at most
 
 static void drop_decode_graphs(Model *m) {
@@ -236,22 +244,6 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN)) gemm_kernel(const float
 // reference runs its cuBLAS GEMMs with) is ~2^-11.  A tile: BM x 32 (row major, stride 36 floats),
 // W tile: 32 x BN (stride BN + 8): both fragment loads are bank-conflict free.  Multi-stage cp.async ring.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    const float rem = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rem));
-}
-__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
 // 128 threads = 4 warps laid out WARPS_M x WARPS_N over the BM x BN tile; needs K % 4 == 0 and N % 4 == 0.
 template <int BM, int BN, int STAGES>
 constexpr size_t gemm_tc_smem_bytes() { return sizeof(float) * (size_t)STAGES * (BM * (32 + 4) + 32 * (BN + 8)); }
@@ -1115,6 +1107,71 @@ static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_ze
     return launch_decode_fused(m->ctx, A);
 }
 
+// ---- the fused step of a batch (decode_batch.cu) ----
+static bool fused_batch_ok(const Model *m, const Pool *p, int n) {
+    return m->fused_batch && !m->strict && n > fused_step_max_rows() && n <= std::min(kFusedBatchMaxRows, m->max_rows) && p->dhead == 16 &&
+           m->d_model == m->heads * 16 && m->d_model % 64 == 0 && m->d_ff % 16 == 0 && m->vocab % 4 == 0 && m->layers <= kFusedMaxLayers &&
+           std::max(m->d_model, m->d_ff) <= 2048;
+}
+static int fused_batch_max_chunks(const Model *m) { return ((m->max_seq + 15) / 16 + 1) / 2; }  // chunks hold >= 2 blocks
+static int32_t ensure_fused_batch(Model *m) {
+    if (m->fb_pairs) return JGPT_OK;
+    const size_t R = (size_t)std::min(kFusedBatchMaxRows, m->max_rows), D = m->d_model, F = m->d_ff, H = m->heads;
+    const size_t parts = (D + 31) / 32, vt = ((size_t)m->vocab + 31) / 32;
+    m->fb_pairs_n = R * (2 * D + 2 * parts + 3 * D + D + F) + vt * R * 2;
+    if (!m->fb_part) JGPT_CUDA_TRY(cudaMalloc(&m->fb_part, sizeof(float) * R * H * (size_t)fused_batch_max_chunks(m) * 18));
+    if (!m->fb_tickets) JGPT_CUDA_TRY(cudaMalloc(&m->fb_tickets, sizeof(int) * (R * H + 4)));
+    JGPT_CUDA_TRY(cudaMemsetAsync(m->fb_tickets, 0, sizeof(int) * (R * H + 4), m->ctx->stream));
+    uint2 *pairs = nullptr;
+    JGPT_CUDA_TRY(cudaMalloc(&pairs, sizeof(uint2) * m->fb_pairs_n));
+    JGPT_CUDA_TRY(cudaMemsetAsync(pairs, 0, sizeof(uint2) * m->fb_pairs_n, m->ctx->stream));  // stamp 0: never data
+    m->fb_pairs = pairs, m->fused_batch_rows = (int)R;
+    return JGPT_OK;
+}
+// Puts the waits' bookkeeping back after a step that reported a failed device check.
+static void fused_batch_reset(Model *m) {
+    if (m->fb_tickets) cudaMemsetAsync(m->fb_tickets, 0, sizeof(int) * ((size_t)m->fused_batch_rows * m->heads + 4), m->ctx->stream);
+}
+static int32_t fused_batch_enqueue(Model *m, Pool *p, int n, const int *lens_host) {
+    const size_t R = (size_t)m->fused_batch_rows, D = m->d_model, F = m->d_ff;
+    const size_t parts = (D + 31) / 32;
+    const uint32_t need = (uint32_t)m->layers + 2u;
+    if (m->f_stamp > 0xE0000000u - need) {  // stamps about to wrap: start over from clean buffers (both step forms share the counter)
+        JGPT_CUDA_TRY(cudaMemsetAsync(m->fb_pairs, 0, sizeof(uint2) * m->fb_pairs_n, m->ctx->stream));
+        if (m->f_pairs) JGPT_CUDA_TRY(cudaMemsetAsync(m->f_pairs, 0, sizeof(uint2) * m->f_pairs_n, m->ctx->stream));
+        m->f_stamp = 0;
+    }
+    BatchStepArgs A = {};
+    A.tok = m->tok, A.pos = m->pos, A.norm_final = m->norm_final, A.lm_head = m->lm_head;
+    for (int l = 0; l < m->layers; l++) {
+        A.Lw[l] = m->L[(size_t)l];
+        int32_t rc = pair_interleaved(m, m->L[(size_t)l].w1, m->L[(size_t)l].w3, m->d_model, m->d_ff, &A.w13[l]);
+        if (rc) return rc;
+    }
+    A.vocab = m->vocab, A.max_seq = m->max_seq, A.D = m->d_model, A.H = m->heads, A.layers = m->layers, A.F = m->d_ff, A.eps = m->eps;
+    A.kv = p->kv, A.table = p->d_table, A.rope = p->d_rope, A.n_blocks = p->n_blocks, A.mbs = p->max_blocks_per_seq;
+    A.idx = m->d_idx, A.n = n;
+    uint2 *f = m->fb_pairs;
+    A.xa = f, f += R * D;
+    A.xb = f, f += R * D;
+    A.ssa = f, f += R * parts;
+    A.ssb = f, f += R * parts;
+    A.qkv = f, f += R * 3 * D;
+    A.att = f, f += R * D;
+    A.act = f, f += R * F;
+    A.cand = f;
+    A.part = m->fb_part, A.tickets = m->fb_tickets;
+    A.stamp0 = m->f_stamp;
+    m->f_stamp += need;
+    A.abort_word = reinterpret_cast<unsigned *>(m->fb_tickets + R * m->heads);
+    A.status = m->ctx->d_status;
+    A.logits = m->logits, A.next = m->d_next;
+    batch_step_plan(A, m->ctx->sm_count, lens_host);
+    JGPT_REQUIRE(A.nch_max <= fused_batch_max_chunks(m), JGPT_ERR_ILLEGAL_STATE, "attention chunks %d exceed the scratch (%d)", A.nch_max,
+                 fused_batch_max_chunks(m));
+    return launch_decode_batch(m->ctx, A);
+}
+
 }  // namespace jgpt
 
 using namespace jgpt;
@@ -1191,6 +1248,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
     m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = by batch size
     m->fused_step = env_int("JGPT_B200_FUSED_STEP", 1);
+    m->fused_batch = env_int("JGPT_B200_FUSED_BATCH", 0);  // measured slower than the multi-launch step so far: opt-in
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
     auto A = [&](float **p, size_t n) { return cudaMalloc(p, sizeof(float) * n); };
     JGPT_CUDA_TRY(A(&m->tok, V * D));
@@ -1246,6 +1304,7 @@ int32_t jgpt_model_destroy(jgpt_model h) {
     cudaFree(m->aimg), cudaFree(m->aimg2), cudaFree(m->ss_a), cudaFree(m->ss_b), cudaFree(m->d_u), cudaFree(m->d_samp);
     cudaFreeHost(m->h_u);
     cudaFree(m->f_pairs), cudaFree(m->f_ints), cudaFreeHost(m->h_fused);
+    cudaFree(m->fb_pairs), cudaFree(m->fb_part), cudaFree(m->fb_tickets);
     delete m;
     return JGPT_OK;
 }
@@ -1573,6 +1632,18 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         }
         JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
         JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
+    } else if (fused_batch_ok(m, p, n)) {  // a batch: one cooperative launch as well (tile products, a warp per attention unit)
+        if ((rc = ensure_fused_batch(m))) return rc;
+        if ((rc = ensure_logits(m, n))) return rc;
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+        if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
+        if ((rc = fused_batch_enqueue(m, p, n, lens))) return rc;
+        if (sampled) {
+            sample_kernel<<<n, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
+            JGPT_CUDA_TRY(cudaGetLastError());
+        }
+        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
     } else if (m->decode_graph_enabled && small_mode(m, n)) {
         // Key: the pool object and its generation (unique per pool, bumped whenever a device buffer the kernels are
         // handed is reallocated), every other buffer address baked into the captured launches, and the pool geometry.
@@ -1635,7 +1706,10 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
     JGPT_CUDA_TRY(cudaStreamSynchronize(st));
     // a kernel of the step recorded a failed self-check: no tokens, no length change
     rc = status_check_after_sync(m->ctx, p, "jgpt_forward_decode");
-    if (rc) return rc;
+    if (rc) {
+        fused_batch_reset(m);
+        return rc;
+    }
     if (next_tokens_host)
         for (int i = 0; i < n; i++) next_tokens_host[i] = m->h_next[i];
     for (int i = 0; i < n; i++) {  // cache.setLength(cacheLenBefore + 1)

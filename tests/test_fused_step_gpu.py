@@ -141,3 +141,63 @@ def test_a_sampled_zero_ends_the_launch(ctx, monkeypatch):
         assert pool.free_blocks() == 8
     finally:
         pool.close(), fused.close(), plain.close(), om.close()
+
+
+@pytest.mark.parametrize("n,geom,std", [(5, GEOM, 0.15), (17, GEOM, 0.15), (40, (96, 320, 64, 4, 2, 128), 0.15),
+                                        (9, (512, 256, 384, 24, 2, 768), 0.05)])
+def test_fused_batch_step_against_the_multi_launch_step_and_the_oracle(ctx, n, geom, std, monkeypatch):
+    """Five rows and up: tile products and a warp per attention unit inside one launch (csrc/decode_batch.cu), against the
+    multi-launch step (JGPT_B200_FUSED_BATCH=0) and the oracle.  Ragged lengths (1 token up to several chunks), steps that
+    cross block and chunk boundaries."""
+    om = O.Model(*geom, eps=1e-5).init_random(seed=6, std=std)
+    V, MS = geom[0], geom[1]
+    with exact_prefill():
+        monkeypatch.setenv("JGPT_B200_FUSED_BATCH", "1")
+        fused = GPTModel(ctx, *geom, rmsNormEps=1e-5, maxRows=2048)
+        monkeypatch.setenv("JGPT_B200_FUSED_BATCH", "0")
+        plain = GPTModel(ctx, *geom, rmsNormEps=1e-5, maxRows=2048)
+        monkeypatch.delenv("JGPT_B200_FUSED_BATCH")
+    fused.setParameters(om.tensors()), plain.setParameters(om.tensors())
+    rng = np.random.default_rng(n)
+    plens = [int(x) for x in rng.integers(1, MS - 12, n)]
+    plens[0], plens[1] = 1, MS - 12
+    prompts = [rng.integers(0, V, p).astype(np.int32) for p in plens]
+    blocks = sum(-(-(p + 12) // 16) for p in plens)
+    pools = [g.newPool(n_blocks=blocks, max_seqs=n) for g in (fused, plain)]
+    n_check = min(n, 6)  # rows followed in the oracle
+    caches = [om.new_cache(kv_fp16=True) for _ in range(n_check)]
+    try:
+        seqs = [[pool.seq_alloc() for _ in range(n)] for pool in pools]
+        toks = None
+        for g, pool, sq in zip((fused, plain), pools, seqs):
+            for i0 in range(0, n, 8):  # prefill in groups that fit the workspace
+                _, t = g.forwardPrefillBatch(pool, sq[i0:i0 + 8], prompts[i0:i0 + 8])
+                toks_g = t if i0 == 0 else np.concatenate([toks_g, t])
+            assert toks is None or np.array_equal(toks, toks_g)
+            toks = toks_g
+        for i in range(n_check):
+            om.forward_prefill(prompts[i], caches[i])
+        lens = np.array(plens, np.int32)
+        for step in range(10):
+            lf, tf = fused.forwardDecodeBatch(pools[0], seqs[0], toks, lens, lens)
+            lp, tp = plain.forwardDecodeBatch(pools[1], seqs[1], toks, lens, lens)
+            assert np.abs(lf - lp).max() < (1e-4 if step == 0 else 2e-3), (step, float(np.abs(lf - lp).max()))
+            for i in range(n_check):
+                want = om.forward_decode(int(toks[i]), caches[i], int(lens[i]), int(lens[i]))
+                assert np.abs(lf[i] - want).max() < 2e-3, (step, i, float(np.abs(lf[i] - want).max()))
+            assert np.array_equal(tf, np.argmax(lf, axis=1))
+            toks, lens = tp, lens + 1
+        for i in (0, 1, n - 1):  # appended payload of the first layer: the multi-launch step's, up to one fp16 ulp
+            planes = []
+            for pool, sq in zip(pools, seqs):
+                kd, vd = ctx.alloc((geom[3], MS, 16)), ctx.alloc((geom[3], MS, 16))
+                pool.gather(0, sq[i], int(lens[i]), MS, kd, vd)
+                planes.append((kd.to_host(), vd.to_host()))
+            for a, b in zip(planes[0], planes[1]):
+                assert np.all(np.abs(a - b) <= np.abs(b) * 2.0 ** -10 + 5e-5), float(np.abs(a - b).max())
+    finally:
+        for pool in pools:
+            pool.close()
+        for c in caches:
+            c.close()
+        fused.close(), plain.close(), om.close()

@@ -299,12 +299,14 @@ def test_graph_replayed_decode_steps_equal_eager_ones_and_follow_weight_updates(
     length-bucket boundaries and for two batch sizes; after a weight update the old graphs must be gone."""
     V, MS, D, H, L, F = 96, 320, 64, 4, 2, 128
     om = O.Model(V, MS, D, H, L, F, eps=1e-5).init_random(seed=11, std=0.15)
-    gm_graph = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=1024)
-    os.environ["JGPT_B200_DECODE_GRAPH"] = "0"
+    os.environ["JGPT_B200_FUSED_BATCH"] = "0"  # the multi-launch step is what is replayed as a graph
     try:
+        gm_graph = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=1024)
+        os.environ["JGPT_B200_DECODE_GRAPH"] = "0"
         gm_eager = GPTModel(ctx, V, MS, D, H, L, F, rmsNormEps=1e-5, maxRows=1024)
     finally:
-        os.environ.pop("JGPT_B200_DECODE_GRAPH")
+        os.environ.pop("JGPT_B200_DECODE_GRAPH", None)
+        os.environ.pop("JGPT_B200_FUSED_BATCH")
     gm_graph.setParameters(om.tensors()), gm_eager.setParameters(om.tensors())
     pools = [g.newPool(n_blocks=6 * MS // 16, max_seqs=6) for g in (gm_graph, gm_eager)]
     try:  # 6 and 5 rows: above the row count that runs as one fused launch, which is not replayed as a graph
@@ -480,6 +482,7 @@ def test_overlapped_launches_inside_the_decode_step_change_nothing(ctx, level, m
     payload are bit-identical to the ordinary step, eager and replayed as a graph."""
     om = O.Model(96, 80, 64, 4, 3, 128, eps=1e-5).init_random(seed=4, std=0.15)
     outs = []
+    monkeypatch.setenv("JGPT_B200_FUSED_BATCH", "0")  # the multi-launch step is the one with overlapping launches
     for lv in (0, level):
         monkeypatch.setenv("JGPT_B200_STEP_OVERLAP", str(lv))
         gm = GPTModel(ctx, 96, 80, 64, 4, 3, 128, rmsNormEps=1e-5, maxRows=256)
