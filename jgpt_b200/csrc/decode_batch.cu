@@ -389,23 +389,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
     for (int l = 0; l < A.layers; l++) {
         const unsigned s_in = A.stamp0 + 1u + (unsigned)l, st = s_in + 1u;  // the layer's input x, what the layer writes
         const LayerW &Y = A.Lw[l];
-        BATCH_MARK(l == 1, 0);
         // ---- A: RMSNorm + Q,K,V  ->  qkv [n][3D]
         {
             const int nt_n = D / BN;  // column tiles per matrix
             for (int u = b; u < mt_n * 3 * nt_n; u += G) {
                 const int mt = u / (3 * nt_n), zt = u % (3 * nt_n), z = zt / nt_n, n0 = (zt % nt_n) * BN, m0 = mt * BM;
                 const float *W = z == 0 ? Y.wq : (z == 1 ? Y.wk : Y.wv);
-                BATCH_MARK(l == 1 && u == b, 9);
+                BATCH_MARK(l == 1 && u == b, 0);
                 w_prefetch(S, W, D, n0, D, Y.norm1);
-                BATCH_MARK(l == 1 && u == b, 10);
                 slab_load(S, A.xa, D, m0, n, s_in, pl);
-                BATCH_MARK(l == 1 && u == b, 11);
                 inv_rms_load(S, A.ssa, parts, D, A.eps, m0, n, s_in, pl);
                 if (__syncthreads_or(pl.failed)) BATCH_BAIL();
-                BATCH_MARK(l == 1 && u == b, 12);
+                BATCH_MARK(l == 1 && u == b, 1);
                 tile_mma<true>(S, W, D, n0, D);
-                BATCH_MARK(l == 1 && u == b, 13);
                 const int m = m0 + er;
                 if (m < n) {
                     uint2 *dst = A.qkv + (size_t)m * 3 * D + (size_t)z * D + n0 + ec;
@@ -413,30 +409,32 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
                     st_pair(dst + 1, red_sum(S, er, ec + 1), st);
                 }
                 __syncthreads();
-                BATCH_MARK(l == 1 && u == b, 14);
+                BATCH_MARK(l == 1 && u == b, 2);
             }
         }
-        BATCH_MARK(l == 1, 1);
         // ---- B: append + attention  ->  att [n][D]
         {
             const int units = n * A.nch_max * A.H;
+            BATCH_MARK(l == 1, 3);
             for (int u = b * kWarps + warp; u < units; u += G * kWarps) {
                 const int h = u % A.H, c = (u / A.H) % A.nch_max, row = u / (A.H * A.nch_max);
                 attention_warp(A, l, row, h, c, st, pl);
             }
+            BATCH_MARK(l == 1, 4);
             if (__syncthreads_or(pl.failed)) BATCH_BAIL();
         }
-        BATCH_MARK(l == 1, 2);
         // ---- C: Wo + residual  ->  xb [n][D], ssb
         {
             const int nt_n = D / BN;
             for (int u = b; u < mt_n * nt_n; u += G) {
                 const int mt = u / nt_n, n0 = (u % nt_n) * BN, m0 = mt * BM, m = m0 + er;
+                BATCH_MARK(l == 1 && u == b, 6);
                 w_prefetch(S, Y.wo, D, n0, D);
                 uint4 rsd[1];
                 ll_load<1>(rsd, 1, s_in, pl, [&](int) { return A.xa + (size_t)min(m, n - 1) * D + n0 + ec; });
                 slab_load(S, A.att, D, m0, n, st, pl);
                 if (__syncthreads_or(pl.failed)) BATCH_BAIL();
+                BATCH_MARK(l == 1 && u == b, 7);
                 tile_mma<false>(S, Y.wo, D, n0, D);
                 const float v0 = red_sum(S, er, ec) + __uint_as_float(rsd[0].x), v1 = red_sum(S, er, ec + 1) + __uint_as_float(rsd[0].z);
                 float sq = m < n ? v0 * v0 + v1 * v1 : 0.f;
@@ -448,18 +446,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
                     if ((tid & 15) == 0) st_pair(A.ssb + (size_t)m * parts + n0 / BN, sq, st);
                 }
                 __syncthreads();
+                BATCH_MARK(l == 1 && u == b, 8);
             }
         }
-        BATCH_MARK(l == 1, 3);
         // ---- D: RMSNorm + W1,W3 + SwiGLU (W1/W3 interleaved in groups of 16 columns)  ->  act [n][F]
         {
             const int nt_n = 2 * F / BN;
             for (int u = b; u < mt_n * nt_n; u += G) {
                 const int mt = u / nt_n, nt = u % nt_n, n0 = nt * BN, m0 = mt * BM;
+                BATCH_MARK(l == 1 && u == b, 9);
                 w_prefetch(S, A.w13[l], 2 * F, n0, D, Y.norm2);
                 slab_load(S, A.xb, D, m0, n, st, pl);
                 inv_rms_load(S, A.ssb, parts, D, A.eps, m0, n, st, pl);
                 if (__syncthreads_or(pl.failed)) BATCH_BAIL();
+                BATCH_MARK(l == 1 && u == b, 10);
                 tile_mma<true>(S, A.w13[l], 2 * F, n0, D);
                 const int r = tid >> 4, c = tid & 15, m = m0 + r;
                 if (m < n) {
@@ -471,19 +471,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
                     st_pair(A.act + (size_t)m * F + nt * 16 + c, hv * (gv * sg), st);
                 }
                 __syncthreads();
+                BATCH_MARK(l == 1 && u == b, 11);
             }
         }
-        BATCH_MARK(l == 1, 4);
         // ---- E: W2 + residual  ->  xa [n][D], ssa (the next layer's input)
         {
             const int nt_n = D / BN;
             for (int u = b; u < mt_n * nt_n; u += G) {
                 const int mt = u / nt_n, n0 = (u % nt_n) * BN, m0 = mt * BM, m = m0 + er;
+                BATCH_MARK(l == 1 && u == b, 12);
                 w_prefetch(S, Y.w2, D, n0, F);
                 uint4 rsd[1];
                 ll_load<1>(rsd, 1, st, pl, [&](int) { return A.xb + (size_t)min(m, n - 1) * D + n0 + ec; });
                 slab_load(S, A.act, F, m0, n, st, pl);
                 if (__syncthreads_or(pl.failed)) BATCH_BAIL();
+                BATCH_MARK(l == 1 && u == b, 13);
                 tile_mma<false>(S, Y.w2, D, n0, F);
                 const float v0 = red_sum(S, er, ec) + __uint_as_float(rsd[0].x), v1 = red_sum(S, er, ec + 1) + __uint_as_float(rsd[0].z);
                 float sq = m < n ? v0 * v0 + v1 * v1 : 0.f;
@@ -495,12 +497,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
                     if ((tid & 15) == 0) st_pair(A.ssa + (size_t)m * parts + n0 / BN, sq, st);
                 }
                 __syncthreads();
+                BATCH_MARK(l == 1 && u == b, 14);
             }
         }
-        BATCH_MARK(l == 1, 5);
     }
 
-    BATCH_MARK(true, 6);
     // ---- final norm + LM head: logits, and per (column tile, row) the best logit with its index ----
     const unsigned s_last = A.stamp0 + 1u + (unsigned)A.layers, s_out = s_last + 1u;
     const int vt_n = (V + BN - 1) / BN;
@@ -536,7 +537,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
         }
         __syncthreads();
     }
-    BATCH_MARK(true, 7);
     // ---- argmax over the column tiles: one warp per row ----
     for (int r = b * kWarps + warp; r < n; r += G * kWarps) {
         float bv = -INFINITY;
@@ -561,7 +561,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
         if (bi == 0x7fffffff) bi = 0;
         if (lane == 0) A.next[r] = bi;
     }
-    BATCH_MARK(true, 8);
 }
 
 size_t batch_smem_bytes(int kmax) {

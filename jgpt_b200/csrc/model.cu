@@ -394,6 +394,13 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     const float *__restrict__ W = z == 0 ? B.W[0] : (z == 1 ? B.W[1] : B.W[2]);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    // norm weights into shared memory up front (weights: no need to wait for the previous kernel): read from global
+    // inside the k loop they put an L2 round trip into every one of its iterations
+    constexpr int kGammaSmem = 1024;
+    __shared__ float s_gamma[NORM ? kGammaSmem : 1];
+    const bool gamma_staged = NORM && K <= kGammaSmem;
+    if (gamma_staged)
+        for (int k = tid; k < K; k += 256) s_gamma[k] = F.gamma[k];
     if (F.pdl & 1) griddep_wait();
     if (F.pdl & 2) griddep_launch_dependents();  // the whole grid is resident: the next launch cannot get in its way
 
@@ -435,6 +442,14 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         if (s < nk) load_tiles(s, s * BK);
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    // the residual elements this thread adds in the epilogue, requested now so that they do not cost a round trip then
+    const float *Rz = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
+    float rpre[2 * MT];
+#pragma unroll
+    for (int i = 0; i < 2 * MT; i++) {
+        const int e = tid + 256 * i, m = m0 + (e >> 5), n = n0 + (e & 31);
+        rpre[i] = (EPI != 2 && Rz && m < M && n < N) ? Rz[(size_t)m * N + n] : 0.f;
+    }
     __shared__ float s_inv[BM];
     if (NORM && tid < BM) {
         const int m = m0 + tid;
@@ -459,7 +474,8 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         float g0 = 0.f, g1 = 0.f;
         if (NORM) {
             const int k = kt * BK + ks + t;
-            g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
+            if (gamma_staged) g0 = k < K ? s_gamma[k] : 0.f, g1 = k + 4 < K ? s_gamma[k + 4] : 0.f;
+            else g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < MT; i++) {
@@ -517,15 +533,16 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             C[(size_t)m * Fo + n] = h * (gv * sg);
         }
     }
-    for (int e = tid; EPI != 2 && e < BM * BN; e += 256) {  // one warp = one row of the tile per iteration
-        const int r = e >> 5, c = e & 31, m = m0 + r, n = n0 + c;
+#pragma unroll
+    for (int i = 0; EPI != 2 && i < 2 * MT; i++) {  // one warp = one row of the tile per iteration
+        const int e = tid + 256 * i, r = e >> 5, c = e & 31, m = m0 + r, n = n0 + c;
         const bool ok = m < M && n < N;
         float v = 0.f;
         if (ok) {
             v = red[0][r][c];
 #pragma unroll
             for (int w = 1; w < 8; w++) v += red[w][r][c];
-            if (R) v += R[(size_t)m * N + n];
+            if (R) v += rpre[i];
             C[(size_t)m * N + n] = v;
         }
         if (EPI == 1) {
