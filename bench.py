@@ -470,7 +470,7 @@ def run_gpu(args, rank, world, local_rank):
 
             uid2 = rendezvous_unique_id(rank, world, f"{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}_cb")
         ranks.barrier()
-        cb = W.run_contbatch(ctx, rank, world, unique_id=uid2)
+        cb = W.run_contbatch(ctx, rank, world, unique_id=uid2, gather_depth=args.gather_depth)
         cb_s = ranks.max(cb["seconds"])
         extras["contbatch"] = {"what": cb["workload"], "generated_tokens": cb["generated_tokens"], "seconds": cb_s,
                                "tokens_per_s": cb["generated_tokens"] / cb_s, "steps_rank0": cb["steps"],
@@ -562,6 +562,8 @@ def run_secondary(args, rank, world, local_rank):
         line["overlap_2"] = W.run_phases(ctx, pool, seqs, BATCH, LAYERS, D, CTX_LEN, overlap=2)
         line["overlap_0"] = W.run_phases(ctx, pool, seqs, BATCH, LAYERS, D, CTX_LEN, overlap=0)
         pool.close()
+    elif args.workload == "fusedphases":
+        line.update(W.run_fused_phases(ctx))
     elif args.workload == "contbatch":
         uid = None
         if world > 1:
@@ -569,7 +571,7 @@ def run_secondary(args, rank, world, local_rank):
 
             uid = rendezvous_unique_id(rank, world, f"{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}_cb")
         ranks.barrier()
-        r = W.run_contbatch(ctx, rank, world, unique_id=uid)
+        r = W.run_contbatch(ctx, rank, world, unique_id=uid, gather_depth=args.gather_depth)
         sec = ranks.max(r["seconds"])
         r["seconds_max_over_ranks"], r["tokens_per_s"] = sec, r["generated_tokens"] / sec
         line.update(r)
@@ -604,7 +606,8 @@ def main():
     ap.add_argument("--per-layer", action="store_true", help="with --quick: one launch per layer instead of one per step")
     ap.add_argument("--launch-overlap", type=int, default=2, help="with --quick --per-layer: 0 ordinary launches, 1 / 2 overlapped")
     ap.add_argument("--batch", type=int, default=64, help="sequences per step for --workload decodestep")
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore", "phases"],
+    ap.add_argument("--gather-depth", type=int, default=4, help="continuous batching: steps a rank may run ahead of the token-id gather")
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore", "phases", "fusedphases"],
                     help="microbench (default) is the headline KV-append + decode-attention step; the others are the "
                          "remaining named configurations (reported, not the contract line)")
     args = ap.parse_args()

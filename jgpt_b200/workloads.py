@@ -8,6 +8,7 @@ import time
 
 import numpy as np
 
+from . import binding as B
 from .kv_cache import KvPool
 from .model import GPTModel
 from .runtime import Event
@@ -380,6 +381,44 @@ def run_phases(ctx, pool, seqs, batch, layers, d_model, ctx_len, overlap=2):
             "per_cta_median_us": {"barriers_ready": float(np.median(ph[:, 0])), "first_slab_consumed": float(np.median(ph[:, 1])),
                                   "block_loop_done": float(np.median(ph[:, 2])), "exit": float(np.median(ph[:, 3]))}})
     return res
+
+
+def run_fused_phases(ctx, prompt_len=900, new_tokens=33):
+    """Where the time of one layer of the one-launch decode step (1-4 rows) goes: needs the library built by
+    ``python -m jgpt_b200.build --trace`` (loaded through JGPT_B200_LIB).  Generates ``new_tokens`` greedy tokens after a
+    prompt (one launch for all steps after the first) and reads every CTA's SM-cycle marks of the second layer of the
+    last step: medians over the CTAs that have a unit in the phase."""
+    import ctypes as C
+
+    lib = ctx._lib
+    if not hasattr(lib, "jgpt_debug_fused_trace_read"):
+        raise RuntimeError("this library was not built with --trace (python -m jgpt_b200.build --trace; JGPT_B200_LIB=...)")
+    model = make_model(ctx, max_rows=1024)
+    try:
+        prompt = np.random.default_rng(1).integers(1, VOCAB, prompt_len).astype(np.int32)
+        best = 1e9
+        for _ in range(3):
+            t0 = time.perf_counter()
+            model.generateGpuKv(prompt, new_tokens)
+            best = min(best, time.perf_counter() - t0)
+        buf = np.zeros((256, 16), np.int64)  # the trace array's size; CTAs that do not exist leave their rows zero
+        B.check(lib.jgpt_debug_fused_trace_read(buf.ctypes.data_as(C.c_void_p), 256))
+        buf = buf[buf.any(axis=1)]
+    finally:
+        model.close()
+    marks = [0, 2, 1, 7, 3, 4, 5, 12, 13, 6, 8, 9, 10, 11]
+    names = ["A: wait for the W2 partials + norm", "A: Q,K,V products", "A: sum of the k slices", "A: store + prefetch of Wo",
+             "B: attention (incl. the wait for q)", "C: wait for the partials + merge", "C: Wo products", "C: sum of the k slices",
+             "C: store + prefetch of W1/W3", "D: wait for the Wo partials + norm", "D: W1/W3 + SwiGLU + store", "E: wait for the activation",
+             "E: W2 + store"]
+    d = np.diff(buf[:, marks], axis=1).astype(np.float64)
+    out = {"workload": f"one-launch decode step, JGPT-35M, batch 1, context ~{prompt_len + new_tokens}: SM-cycle marks of one layer",
+           "generate_ms": best * 1e3, "layer_cycles_median": float(np.median(buf[:, 11] - buf[:, 0])), "segments_cycles_median": {}}
+    for i, nm in enumerate(names):
+        col = d[:, i]
+        col = col[(col > 0) & (col < 1e7)]  # CTAs without a unit in the phase leave a mark unset
+        out["segments_cycles_median"][nm] = float(np.median(col)) if col.size else None
+    return out
 
 
 def run_longctx(ctx, rank, world, n_seqs_total=512, steps=20, warmup=3):
