@@ -608,17 +608,21 @@ int32_t launch_decode_batch(Ctx *ctx, BatchStepArgs &A) {
         if (!ready.count(ctx->device)) {
             int coop = 0, per_sm = 0;
             JGPT_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device));
-            JGPT_REQUIRE(coop, JGPT_ERR_CUDA, "device %d has no cooperative launch", ctx->device);
+            JGPT_REQUIRE(coop, JGPT_ERR_UNSUPPORTED, "device %d has no cooperative launch", ctx->device);
             JGPT_CUDA_TRY(cudaFuncSetAttribute(decode_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
             JGPT_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_batch_kernel, kThreads, 160 * 1024));
-            JGPT_REQUIRE(per_sm >= 1, JGPT_ERR_CUDA, "the batched fused decode step does not fit an SM");
+            JGPT_REQUIRE(per_sm >= 1, JGPT_ERR_UNSUPPORTED, "the batched fused decode step does not fit an SM");
             ready.insert(ctx->device);
         }
     }
     JGPT_REQUIRE(smem <= 160 * 1024, JGPT_ERR_INVALID_ARGUMENT, "model too wide for the batched fused decode step");
     void *args[1] = {&A};
-    JGPT_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(decode_batch_kernel), dim3((unsigned)ctx->sm_count), dim3(kThreads),
-                                              args, smem, ctx->stream));
+    const cudaError_t le = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(decode_batch_kernel), dim3((unsigned)ctx->sm_count), dim3(kThreads),
+                                              args, smem, ctx->stream);
+    if (le != cudaSuccess) {  // e.g. the grid cannot be resident at once on what this process may use of the device
+        cudaGetLastError();
+        return fail(JGPT_ERR_UNSUPPORTED, "cooperative launch refused: %s", cudaGetErrorString(le));
+    }
     return JGPT_OK;
 }
 

@@ -626,10 +626,10 @@ static int32_t launch_rows(Ctx *ctx, FusedStepArgs &A) {
         if (!ready.count(ctx->device)) {
             int coop = 0, per_sm = 0;
             JGPT_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device));
-            JGPT_REQUIRE(coop, JGPT_ERR_CUDA, "device %d has no cooperative launch", ctx->device);
+            JGPT_REQUIRE(coop, JGPT_ERR_UNSUPPORTED, "device %d has no cooperative launch", ctx->device);
             JGPT_CUDA_TRY(cudaFuncSetAttribute(decode_step_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
             JGPT_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<R>, kThreads, 64 * 1024));
-            JGPT_REQUIRE(per_sm >= 1, JGPT_ERR_CUDA, "the fused decode step does not fit an SM");
+            JGPT_REQUIRE(per_sm >= 1, JGPT_ERR_UNSUPPORTED, "the fused decode step does not fit an SM");
             grid_for[ctx->device & 63] = ctx->sm_count;
             ready.insert(ctx->device);
         }
@@ -638,8 +638,12 @@ static int32_t launch_rows(Ctx *ctx, FusedStepArgs &A) {
     const int G = grid_for[ctx->device & 63];
     JGPT_REQUIRE(G == A.grid, JGPT_ERR_ILLEGAL_STATE, "fused decode step sized for %d CTAs, device runs %d", A.grid, G);
     void *args[1] = {&A};
-    JGPT_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(decode_step_kernel<R>), dim3((unsigned)G), dim3(kThreads), args,
-                                              smem, ctx->stream));
+    const cudaError_t le = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(decode_step_kernel<R>), dim3((unsigned)G), dim3(kThreads), args,
+                                              smem, ctx->stream);
+    if (le != cudaSuccess) {  // e.g. the grid cannot be resident at once on what this process may use of the device
+        cudaGetLastError();
+        return fail(JGPT_ERR_UNSUPPORTED, "cooperative launch refused: %s", cudaGetErrorString(le));
+    }
     return JGPT_OK;
 }
 
@@ -677,6 +681,8 @@ void fused_step_plan(FusedStepArgs &A, int sm_count, int max_len) {
 }
 
 int32_t launch_decode_fused(Ctx *ctx, FusedStepArgs &A) {
+    // host-side fault injection for the tests: behave as a device that refuses the cooperative launch
+    if (env_int("JGPT_B200_FUSED_REFUSE", 0)) return fail(JGPT_ERR_UNSUPPORTED, "cooperative launch refused (injected)");
     JGPT_REQUIRE(A.n >= 1 && A.n <= fused_step_max_rows() && A.steps >= 1, JGPT_ERR_INVALID_ARGUMENT, "fused decode step: %d rows, %d steps", A.n,
                  A.steps);
     JGPT_REQUIRE(A.D == A.H * DH && A.D % 8 == 0 && A.F % 8 == 0 && A.vocab % 8 == 0, JGPT_ERR_INVALID_ARGUMENT,

@@ -1637,30 +1637,32 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         return JGPT_OK;
     };
     Model::DecodeGraph *slot = nullptr;
-    if (fused_ok(m, p, n)) {  // a handful of rows: the whole step is one cooperative launch
-        if ((rc = ensure_fused(m))) return rc;
+    // One cooperative launch for the whole step where that form exists and is switched on.  A device that cannot keep the
+    // grid resident (fewer SMs than the context was sized for: MPS with a thread percentage, a green context) refuses the
+    // launch: the form is switched off for this model and the step below runs as separate launches.
+    bool one_launch = false;
+    const int form = fused_ok(m, p, n) ? 1 : (fused_batch_ok(m, p, n) ? 2 : 0);
+    if (form) {
+        if ((rc = form == 1 ? ensure_fused(m) : ensure_fused_batch(m))) return rc;
         if ((rc = ensure_logits(m, n))) return rc;
         JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
         if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
-        if ((rc = fused_enqueue(m, p, n, 1, 0, max_len, m->d_next))) return rc;
-        if (sampled) {
-            sample_kernel<<<n, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
-            JGPT_CUDA_TRY(cudaGetLastError());
+        rc = form == 1 ? fused_enqueue(m, p, n, 1, 0, max_len, m->d_next) : fused_batch_enqueue(m, p, n, lens);
+        if (rc == JGPT_ERR_UNSUPPORTED) {
+            (form == 1 ? m->fused_step : m->fused_batch) = 0;
+        } else if (rc) {
+            return rc;
+        } else {
+            if (sampled) {
+                sample_kernel<<<n, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
+                JGPT_CUDA_TRY(cudaGetLastError());
+            }
+            JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+            JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
+            one_launch = true;
         }
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
-        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
-    } else if (fused_batch_ok(m, p, n)) {  // a batch: one cooperative launch as well (tile products, a warp per attention unit)
-        if ((rc = ensure_fused_batch(m))) return rc;
-        if ((rc = ensure_logits(m, n))) return rc;
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
-        if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
-        if ((rc = fused_batch_enqueue(m, p, n, lens))) return rc;
-        if (sampled) {
-            sample_kernel<<<n, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
-            JGPT_CUDA_TRY(cudaGetLastError());
-        }
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
-        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
+    }
+    if (one_launch) {
     } else if (m->decode_graph_enabled && small_mode(m, n)) {
         // Key: the pool object and its generation (unique per pool, bumped whenever a device buffer the kernels are
         // handed is reallocated), every other buffer address baked into the captured launches, and the pool geometry.
@@ -1837,6 +1839,10 @@ static bool fused_greedy_steps(Model *m, Pool *p, jgpt_kvpool poolh, int32_t seq
     };
     *rc = run();
     const int32_t trc = pool_trim_reservation(p, seq, p->seqs[(size_t)seq].len);
+    if (*rc == JGPT_ERR_UNSUPPORTED) {  // the device refused the cooperative launch: nothing ran; the one-step path takes over
+        m->fused_step = 0, *rc = JGPT_OK;
+        return false;
+    }
     if (*rc == JGPT_OK) *rc = trc;
     return true;
 }

@@ -201,3 +201,35 @@ def test_fused_batch_step_against_the_multi_launch_step_and_the_oracle(ctx, n, g
         for c in caches:
             c.close()
         fused.close(), plain.close(), om.close()
+
+
+def test_a_refused_cooperative_launch_falls_back_to_the_multi_launch_step(ctx, monkeypatch):
+    """A device that cannot keep one CTA per SM resident (MPS with a thread percentage, a green context) refuses the
+    cooperative launch.  Injected on the host (JGPT_B200_FUSED_REFUSE=1): the call must still succeed, through the
+    multi-launch step, bit for bit; generation likewise, with the allocator left clean."""
+    om, fused, plain = _three(ctx, GEOM, 4, 0.15, monkeypatch)
+    pools = [g.newPool(n_blocks=10, max_seqs=2) for g in (fused, plain)]
+    try:
+        prompt = np.array([(i * 7 + 3) % GEOM[0] for i in range(20)], np.int32)
+        monkeypatch.setenv("JGPT_B200_FUSED_REFUSE", "1")
+        outs = []
+        for g, pool in zip((fused, plain), pools):
+            s = pool.seq_alloc()
+            _, t = g.forwardPrefillBatch(pool, [s], [prompt])
+            lg, nx = g.forwardDecodeBatch(pool, [s], t, [20], [20])
+            outs.append((lg, nx))
+            pool.seq_free(s)
+        assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+        a = fused.generateGpuKv(prompt, 30, pool=pools[0])
+        b = plain.generateGpuKv(prompt, 30, pool=pools[1])
+        assert np.array_equal(a, b) and pools[0].free_blocks() == 10
+        monkeypatch.delenv("JGPT_B200_FUSED_REFUSE")
+        # the form stays off for this model after a refusal: still the multi-launch answers
+        s = pools[0].seq_alloc()
+        _, t = fused.forwardPrefillBatch(pools[0], [s], [prompt])
+        lg, _ = fused.forwardDecodeBatch(pools[0], [s], t, [20], [20])
+        assert np.array_equal(lg, outs[1][0])
+    finally:
+        for pool in pools:
+            pool.close()
+        fused.close(), plain.close(), om.close()
