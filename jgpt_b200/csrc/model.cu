@@ -1932,6 +1932,14 @@ int32_t jgpt_generate_greedy_rolling(jgpt_model h, jgpt_kvpool poolh, const int3
                 if (rc) break;
             }
             const int32_t prev = out_host[S + j - 1], len_before = p->seqs[(size_t)seq].len, rope = S + j - 1;
+            // the steps up to the next dropped block in one launch (at most a block's worth once the window rolls)
+            const int T = std::min(std::min(max_new - j, cap - len_before), std::min(p->max_positions - rope, kFusedMaxSteps));
+            int done = 0;
+            if (T >= 2 && fused_ok(m, p, 1) && fused_greedy_steps(m, p, poolh, seq, prev, len_before, rope, T, out_host + S + j, &done, &rc)) {
+                if (rc) break;
+                n += done, j += done - 1, tok = out_host[S + j];
+                continue;
+            }
             rc = jgpt_forward_decode(h, poolh, &seq, &prev, &len_before, &rope, 1, nullptr, &tok);
             if (rc) break;
             out_host[S + j] = tok, n++;
