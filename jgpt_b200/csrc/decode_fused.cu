@@ -49,9 +49,15 @@ constexpr int kCandBatch = 5;          // per-CTA candidates a lane polls at a t
 // Timing build only: per CTA, SM clock at the marks of one layer (the second layer of the launch's last step).
 constexpr int kTraceMarks = 16;
 __device__ long long g_fused_trace[256 * kTraceMarks];
+__device__ long long g_fused_trace_ns[256 * kTraceMarks];  // the same marks on the global timer (comparable across SMs)
 #define FUSED_MARK(i)                                                                            \
     do {                                                                                         \
-        if (tracing && threadIdx.x == 0) g_fused_trace[blockIdx.x * kTraceMarks + (i)] = clock64(); \
+        if (tracing && threadIdx.x == 0) {                                                       \
+            long long gt_;                                                                       \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));                              \
+            g_fused_trace[blockIdx.x * kTraceMarks + (i)] = clock64();                           \
+            g_fused_trace_ns[blockIdx.x * kTraceMarks + (i)] = gt_;                              \
+        }                                                                                        \
     } while (0)
 #else
 #define FUSED_MARK(i) \
@@ -212,7 +218,7 @@ __device__ __forceinline__ bool residual_norm(float *x, const uint2 *p, int ks, 
 // One (row, head, chunk) of the attention: RoPE on q, the new token appended by the chunk that owns its slot, a
 // partial (maximum, sum, outputs) of this chunk's tokens left in `part`.  `sq` = 3 * DH floats of shared memory.
 __device__ __forceinline__ bool attention_unit(const FusedStepArgs &A, int layer, int r, int h, int c, int step, unsigned stamp, Poll &pl,
-                                               float *red, float *sq) {
+                                               float *red, float *sq, bool trace_on = false) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = A.n;
     const int seq = A.idx[2 * n + r], rp = A.idx[3 * n + r] + step, len = A.idx[4 * n + r] + step;
@@ -247,14 +253,23 @@ __device__ __forceinline__ bool attention_unit(const FusedStepArgs &A, int layer
     float2 rope[DH / 2];
 #pragma unroll
     for (int j = 0; j < DH / 2; j++) rope[j] = __ldg(cs + j);
-    // this head's q, k, v of the row: 3 x 8 pairs
-    if (tid < 3 * DH / 2) {
+    // this head's q, k, v of the row: 3 x 8 pairs, polled by the LAST warp: it has no cache rows in flight unless the chunk
+    // is longer than 224 tokens (a warp's wait for its poll may also wait for that warp's older loads from HBM)
+    if (tid >= kThreads - 32 && tid < kThreads - 32 + 3 * DH / 2) {
+        const int pt = tid - (kThreads - 32);
         uint4 v[1];
-        const uint2 *src = A.ll_qkv + (size_t)r * 3 * A.D + (size_t)(tid / (DH / 2)) * A.D + h * DH + 2 * (tid % (DH / 2));
+        const uint2 *src = A.ll_qkv + (size_t)r * 3 * A.D + (size_t)(pt / (DH / 2)) * A.D + h * DH + 2 * (pt % (DH / 2));
         ll_load<1>(v, 1, stamp, pl, [&](int) { return src; });
-        sq[2 * tid] = __uint_as_float(v[0].x), sq[2 * tid + 1] = __uint_as_float(v[0].z);
+        sq[2 * pt] = __uint_as_float(v[0].x), sq[2 * pt + 1] = __uint_as_float(v[0].z);
     }
     if (__syncthreads_or(pl.failed)) return false;
+#ifdef JGPT_B200_DECODE_TRACE
+    if (threadIdx.x == 0 && trace_on) {
+        long long gt_;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));
+        g_fused_trace_ns[blockIdx.x * kTraceMarks + 14] = gt_;
+    }
+#endif
     float q[DH];
 #pragma unroll
     for (int j = 0; j < DH / 2; j++) {
@@ -304,6 +319,13 @@ __device__ __forceinline__ bool attention_unit(const FusedStepArgs &A, int layer
 #pragma unroll
         for (int d = 0; d < DH; d++) o[d] = fmaf(pe, __half2float(vh[d]), o[d]);
     }
+#ifdef JGPT_B200_DECODE_TRACE
+    if (threadIdx.x == 0 && trace_on) {
+        long long gt_;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));
+        g_fused_trace_ns[blockIdx.x * kTraceMarks + 15] = gt_;
+    }
+#endif
     // merge: lanes of a warp, then the warps
     float M = m;
 #pragma unroll
@@ -354,36 +376,70 @@ __device__ __forceinline__ bool attention_unit(const FusedStepArgs &A, int layer
     return true;
 }
 
-// Merged attention output for model columns [k0, k1) (whole heads) of rows < n into a[r * lda + (k - k0)].  One thread
-// per (pair of adjacent dimensions, chunk) fetches that chunk's (maximum, sum) and its two outputs; the chunks meet in
-// shared memory (`stage`, 4 floats per item).
+// Merged attention output for model columns [k0, k1) (whole heads) of rows < n into a[r * lda + (k - k0)].
+// A pair of adjacent dimensions of one row is merged by 4 / R threads.  The chunks form four classes (chunk mod 4, at
+// most two chunks each); a thread owns R classes, fetches their (maximum, sum) and outputs in one wait, the threads
+// of a pair exchange maxima and then the weighted sums per class through shared memory, and the classes are added in the
+// order 0, 1, 2, 3 - the same association whatever R is, so a row's result does not depend on the size of the batch.
+// All loops have compile-time bounds: the weights are independent exp2 evaluations, not a chain.
+// `stage`: kThreads float4 (maxima) followed by 4 * (kThreads / (4 / R)) float4 (class sums).
+static_assert(kFusedMaxChunks == 8, "the merge keeps two chunks per class");
+template <int R>
 __device__ __forceinline__ bool merge_attention(const FusedStepArgs &A, float *a, int lda, int k0, int k1, unsigned stamp, Poll &pl,
                                                float *stage) {
-    const int span2 = (k1 - k0) / 2, items = A.n * span2 * A.nch;
-    const int per = (kThreads / A.nch) * A.nch;  // items of a pass: whole groups of chunks
-    for (int base = 0; base < items; base += per) {
-        const int it = (int)threadIdx.x < per ? base + (int)threadIdx.x : items;
-        if (it < items) {
-            const int c = it % A.nch, e = it / A.nch, r = e / span2, k = k0 + 2 * (e % span2), h = k / DH, d = k % DH;
-            const uint2 *pp = A.ll_part + (((size_t)r * A.H + h) * A.nch + c) * PS;
-            uint4 v[2];
-            ll_load<2>(v, 2, stamp, pl, [&](int i) { return pp + (i ? 2 + d : 0); });
-            reinterpret_cast<float4 *>(stage)[threadIdx.x] =
-                make_float4(__uint_as_float(v[0].x), __uint_as_float(v[0].z), __uint_as_float(v[1].x), __uint_as_float(v[1].z));
-        }
+    constexpr int GROUPS = 4 / R, PT = kThreads / GROUPS;  // threads per pair, pairs per pass
+    const int span2 = (k1 - k0) / 2, pairs = A.n * span2, nch = A.nch;
+    const int g = threadIdx.x / PT, pe = threadIdx.x % PT;
+    float4 *mx4 = reinterpret_cast<float4 *>(stage), *cls4 = mx4 + kThreads;  // cls4[class * PT + pair]
+    for (int e0 = 0; e0 < pairs; e0 += PT) {
+        const int e = e0 + pe;
+        const bool live = e < pairs;
+        int r = 0, k = k0;
+        if (live) r = e / span2, k = k0 + 2 * (e % span2);
+        const int h = k / DH, d = k % DH;
+        const uint2 *pp = A.ll_part + (((size_t)r * A.H + h) * nch) * PS;
+        // entry i: class g + GROUPS * (i / 4), its chunk (i / 2) % 2 (class, class + 4), (maximum, sum) or the two outputs
+        uint4 v[4 * R];
+        auto chunk_of = [&](int i) { return g + GROUPS * (i >> 2) + 4 * ((i >> 1) & 1); };
+        ll_load<4 * R>(v, live ? 4 * R : 0, stamp, pl, [&](int i) {
+            const int c = min(chunk_of(i), nch - 1);  // classes beyond the launch's chunks re-read the last chunk; never used
+            return pp + c * PS + ((i & 1) ? 2 + d : 0);
+        });
+        float m_loc = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4 * R; i += 2)
+            if (chunk_of(i) < nch) m_loc = fmaxf(m_loc, __uint_as_float(v[i].x));
+        mx4[threadIdx.x].x = m_loc;
         if (__syncthreads_or(pl.failed)) return false;
-        if (it < items && it % A.nch == 0) {
-            const int e = it / A.nch, r = e / span2, k = k0 + 2 * (e % span2);
-            const float4 *st = reinterpret_cast<const float4 *>(stage) + threadIdx.x;
-            float Mx = -INFINITY, L = 0.f, acc0 = 0.f, acc1 = 0.f;
-            for (int c = 0; c < A.nch; c++) Mx = fmaxf(Mx, st[c].x);
-            for (int c = 0; c < A.nch; c++) {
-                const float4 pc = st[c];
-                const float w = pc.x == -INFINITY ? 0.f : exp2f(pc.x - Mx);
-                L = fmaf(pc.y, w, L), acc0 = fmaf(pc.z, w, acc0), acc1 = fmaf(pc.w, w, acc1);
+        float Mx = -INFINITY;
+#pragma unroll
+        for (int gg = 0; gg < GROUPS; gg++) Mx = fmaxf(Mx, mx4[gg * PT + pe].x);
+#pragma unroll
+        for (int vi = 0; vi < R; vi++) {  // this thread's classes
+            float L = 0.f, acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int i = 4 * vi + 2 * half;
+                if (chunk_of(i) < nch) {
+                    const float mc = __uint_as_float(v[i].x);
+                    const float w = mc == -INFINITY ? 0.f : exp2f(mc - Mx);
+                    L = fmaf(__uint_as_float(v[i].z), w, L);
+                    acc0 = fmaf(__uint_as_float(v[i + 1].x), w, acc0);
+                    acc1 = fmaf(__uint_as_float(v[i + 1].z), w, acc1);
+                }
             }
-            const float inv = 1.f / fmaxf(L, 1e-12f);
-            a[r * lda + (k - k0)] = acc0 * inv, a[r * lda + (k - k0) + 1] = acc1 * inv;
+            cls4[(g + GROUPS * vi) * PT + pe] = make_float4(0.f, L, acc0, acc1);
+        }
+        __syncthreads();
+        if (g == 0 && live) {
+            float4 t = cls4[pe];
+#pragma unroll
+            for (int cl = 1; cl < 4; cl++) {
+                const float4 o = cls4[cl * PT + pe];
+                t.y += o.y, t.z += o.z, t.w += o.w;
+            }
+            const float inv = 1.f / fmaxf(t.y, 1e-12f);
+            a[r * lda + (k - k0)] = t.z * inv, a[r * lda + (k - k0) + 1] = t.w * inv;
         }
         __syncthreads();
     }
@@ -464,14 +520,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
             // ---- B: append + attention partials
             for (int u = b; u < n * A.H * A.nch; u += G) {
                 const int c = u % A.nch, h = (u / A.nch) % A.H, r = u / (A.nch * A.H);
+#ifdef JGPT_B200_DECODE_TRACE
+                if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq, tracing)) goto leave;
+#else
                 if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq)) goto leave;
+#endif
             }
 
             FUSED_MARK(4);
             // ---- C: merged attention rows . Wo, partial rows per k range
             for (int u = b; u < nO * kso; u += G) {
                 const int c0 = (u % nO) * 8, kj = u / nO, k0 = kj * klo, k1 = min(D, k0 + klo);
-                if (!merge_attention(A, a, klo, k0, k1, stamp, pl, stage)) goto leave;
+                                if (!merge_attention<R>(A, a, klo, k0, k1, stamp, pl, stage)) goto leave;
                 FUSED_MARK(5);
                 float acc[1][R][4], res[1];
                 unit_fma<R, 1>(t, have && u == b, A.Lw[l].wo, nullptr, D, c0 + half_col, k0, k1, a, klo, k0, acc);
@@ -612,7 +672,7 @@ leave:
 
 template <int R>
 static size_t fused_smem_bytes(const FusedStepArgs &A) {
-    return sizeof(float) * ((size_t)R * A.D + (size_t)R * A.amax + (size_t)kWarps * 2 * 2 * R * 4 + kWarps * PS + 3 * DH + kThreads * 4);
+    return sizeof(float) * ((size_t)R * A.D + (size_t)R * A.amax + (size_t)kWarps * 2 * 2 * R * 4 + kWarps * PS + 3 * DH + kThreads * 4 + 4 * kThreads * 4);
 }
 
 template <int R>
@@ -652,6 +712,10 @@ static int32_t launch_rows(Ctx *ctx, FusedStepArgs &A) {
 #ifdef JGPT_B200_DECODE_TRACE
 extern "C" __attribute__((visibility("default"))) int32_t jgpt_debug_fused_trace_read(long long *host, int32_t n_ctas) {
     JGPT_CUDA_TRY(cudaMemcpyFromSymbol(host, g_fused_trace, sizeof(long long) * (size_t)n_ctas * kTraceMarks));
+    return JGPT_OK;
+}
+extern "C" __attribute__((visibility("default"))) int32_t jgpt_debug_fused_trace_read_ns(long long *host, int32_t n_ctas) {
+    JGPT_CUDA_TRY(cudaMemcpyFromSymbol(host, g_fused_trace_ns, sizeof(long long) * (size_t)n_ctas * kTraceMarks));
     return JGPT_OK;
 }
 #endif

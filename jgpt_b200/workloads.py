@@ -405,6 +405,9 @@ def run_fused_phases(ctx, prompt_len=900, new_tokens=33):
         buf = np.zeros((256, 16), np.int64)  # the trace array's size; CTAs that do not exist leave their rows zero
         B.check(lib.jgpt_debug_fused_trace_read(buf.ctypes.data_as(C.c_void_p), 256))
         buf = buf[buf.any(axis=1)]
+        ns = np.zeros((256, 16), np.int64)  # the same marks on the global timer: comparable across CTAs (0.256 us steps)
+        B.check(lib.jgpt_debug_fused_trace_read_ns(ns.ctypes.data_as(C.c_void_p), 256))
+        ns = ns[ns.any(axis=1)]
     finally:
         model.close()
     marks = [0, 2, 1, 7, 3, 4, 5, 12, 13, 6, 8, 9, 10, 11]
@@ -419,6 +422,16 @@ def run_fused_phases(ctx, prompt_len=900, new_tokens=33):
         col = d[:, i]
         col = col[(col > 0) & (col < 1e7)]  # CTAs without a unit in the phase leave a mark unset
         out["segments_cycles_median"][nm] = float(np.median(col)) if col.size else None
+    # when, over all CTAs, each point of the layer is reached (us after the first CTA starts the layer)
+    t0 = ns[:, 0].min()
+    points = [(0, "previous layer's W2 results stored"), (2, "A: inputs complete, norm done"), (3, "A: Q,K,V stored"),
+              (4, "B: attention partial stored"), (5, "C: partials complete, merged"), (6, "C: Wo results stored"),
+              (8, "D: inputs complete, norm done"), (9, "D: activation stored"), (10, "E: activation slice complete"), (11, "E: W2 results stored")]
+    out["timeline_us_min_median_max"] = {}
+    for mk, nm in points:
+        col = ns[:, mk].astype(np.float64)
+        col = (col[col > 0] - t0) / 1e3
+        out["timeline_us_min_median_max"][nm] = [float(col.min()), float(np.median(col)), float(col.max())]
     return out
 
 
