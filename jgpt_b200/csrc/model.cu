@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(256) sample_kernel(const float *__restrict__ l
                                                      int top_k, const float *__restrict__ u01, int *__restrict__ out) {
     __shared__ float bv[8];
     __shared__ int bi[8];
-    __shared__ float s_thr_v, s_mx, s_sum;
+    __shared__ float s_thr_v, s_mx;
     __shared__ int s_thr_i;
     const float *row = logits + (size_t)blockIdx.x * V;
     float *z = work + (size_t)blockIdx.x * V;
@@ -666,7 +666,6 @@ __global__ void __launch_bounds__(256) sample_kernel(const float *__restrict__ l
     if (tid == 0) {
         float sum = 0.f;
         for (int i = 0; i < V; i++) sum += z[i];
-        s_sum = sum;
         const float u = u01[blockIdx.x];
         float cum = 0.f;
         int tok = V - 1;
@@ -1096,7 +1095,7 @@ static int *fused_steps_done_dev(Model *m) { return m->f_ints + (size_t)kFusedMa
 // Enqueues `steps` decode steps of the n rows described in m->d_idx (already uploaded).  Tokens go to `next_dev`
 // ([steps][n]); with stop_on_zero (n == 1) the launch ends after a sampled 0.
 static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_zero, int max_len_after, int *next_dev) {
-    const size_t D = m->d_model, F = m->d_ff, H = m->heads, G = m->ctx->sm_count, R = 4;
+    const size_t D = m->d_model, F = m->d_ff, H = m->heads, R = 4;
     const uint32_t need = (uint32_t)steps * (uint32_t)m->layers;
     if (m->f_stamp > 0xE0000000u - need) {  // stamps about to wrap: start over from clean buffers
         JGPT_CUDA_TRY(cudaMemsetAsync(m->f_pairs, 0, sizeof(uint2) * m->f_pairs_n, m->ctx->stream));
