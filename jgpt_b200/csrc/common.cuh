@@ -218,7 +218,7 @@ struct FusedStepArgs {
     unsigned *sync_words;  // [1] abort word: holds stamp0 + 1 of a launch that gave up
     int *status;
     // plan
-    int grid, nch, cb, ks_o, kl_o, ks_2, kl_2, amax;
+    int grid, nch, cb, ks_o, kl_o, ks_2, kl_2, amax, lm_stage;
     float scale_log2e;
 };
 int fused_step_max_rows();

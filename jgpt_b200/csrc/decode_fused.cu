@@ -47,7 +47,7 @@ constexpr int kCandBatch = 5;          // per-CTA candidates a lane polls at a t
 
 #ifdef JGPT_B200_DECODE_TRACE
 // Timing build only: per CTA, SM clock at the marks of one layer (the second layer of the launch's last step).
-constexpr int kTraceMarks = 16;
+constexpr int kTraceMarks = 24;
 __device__ long long g_fused_trace[256 * kTraceMarks];
 __device__ long long g_fused_trace_ns[256 * kTraceMarks];  // the same marks on the global timer (comparable across SMs)
 #define FUSED_MARK(i)                                                                            \
@@ -454,6 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
     float *red = a + R * A.amax;      // reductions
     float *sq = red + kWarps * 2 * 2 * R * 4 + kWarps * PS;  // q, k, v of one head
     float *stage = sq + 3 * DH;                              // [256][4] chunk partials on their way to be merged
+    float *lm_w = stage + kThreads * 4 + 4 * kThreads * 4;  // [lm_stage][D][8] this CTA's first LM-head column blocks
     __shared__ int s_tok[R];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, G = gridDim.x, n = A.n, D = A.D, F = A.F;
@@ -516,6 +517,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
             }
 
             gamma_load(gam, A.Lw[l].norm2, D);
+            if (l == A.layers - 1) {  // the LM head's weights for this CTA's first column blocks: into shared memory, well ahead
+                for (int j = 0; j < A.lm_stage && b + j * G < nL; j++) {
+                    const float *src = A.lm_head + (size_t)(b + j * G) * 8;
+                    float *dst = lm_w + (size_t)j * D * 8;
+                    for (int e = tid; e < D * 2; e += kThreads) cp_async16(dst + e * 4, src + (size_t)(e >> 1) * A.vocab + (e & 1) * 4, true);
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
             FUSED_MARK(3);
             // ---- B: append + attention partials
             for (int u = b; u < n * A.H * A.nch; u += G) {
@@ -593,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
             FUSED_MARK(11);
             if (l + 1 < A.layers) {
                 if (b < nA) load_A(l + 1, b), have = true;
-            } else if (b < nL) {
+            } else if (b < nL && A.lm_stage == 0) {
                 tile_load<1>(t, A.lm_head, nullptr, A.vocab, b * 8 + half_col, 0, D);
                 have = true;
             }
@@ -602,17 +611,45 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
         // ---- final norm + LM head; every CTA keeps the best (value, lowest index) of its columns per row
         {
             const unsigned stamp = A.stamp0 + (unsigned)((step + 1) * A.layers);  // the last layer's
+#ifdef JGPT_B200_DECODE_TRACE
+            const bool tracing = step == A.steps - 1;
+#endif
+            FUSED_MARK(16);
             if (!residual_norm<R>(x, A.ll_pw2, ks2, n, D, stamp, pl, gam, a, A.eps, red)) goto leave;
+            FUSED_MARK(17);
             float best = -INFINITY;
             int best_i = 0x7fffffff;
-            if (!have && b < nL) tile_load<1>(t, A.lm_head, nullptr, A.vocab, b * 8 + half_col, 0, D);
-            for (int u = b; u < nL; u += G) {
-                WTile tn;  // the next unit's tile is on its way while this one is multiplied and reduced
-                if (u + G < nL) tile_load<1>(tn, A.lm_head, nullptr, A.vocab, (u + G) * 8 + half_col, 0, D);
+            if (A.lm_stage > 0) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncthreads();
+            }
+            const int u_reg0 = b + A.lm_stage * G;  // first unit whose weights come through registers
+            if (!have && u_reg0 < nL) tile_load<1>(t, A.lm_head, nullptr, A.vocab, u_reg0 * 8 + half_col, 0, D);
+            int j = 0;
+            for (int u = b; u < nL; u += G, j++) {
                 float acc[1][R][4], res[1];
-                unit_fma<R, 1>(t, true, A.lm_head, nullptr, A.vocab, u * 8 + half_col, 0, D, a, D, 0, acc);
+                WTile tn;  // beyond the staged blocks: the next unit's tile is on its way while this one is multiplied and reduced
+                if (j < A.lm_stage) {  // weights in shared memory: [k][8 columns]
+                    const float *wu = lm_w + (size_t)j * D * 8 + half_col;
+#pragma unroll
+                    for (int r = 0; r < R; r++)
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; q4++) acc[0][r][q4] = 0.f;
+                    for (int k = tid >> 1; k < D; k += kSlices) {
+                        const float4 w = *reinterpret_cast<const float4 *>(wu + (size_t)k * 8);
+#pragma unroll
+                        for (int r = 0; r < R; r++) {
+                            const float av = a[r * D + k];
+                            acc[0][r][0] = fmaf(av, w.x, acc[0][r][0]), acc[0][r][1] = fmaf(av, w.y, acc[0][r][1]);
+                            acc[0][r][2] = fmaf(av, w.z, acc[0][r][2]), acc[0][r][3] = fmaf(av, w.w, acc[0][r][3]);
+                        }
+                    }
+                } else {
+                    if (u + G < nL) tile_load<1>(tn, A.lm_head, nullptr, A.vocab, (u + G) * 8 + half_col, 0, D);
+                    unit_fma<R, 1>(t, true, A.lm_head, nullptr, A.vocab, u * 8 + half_col, 0, D, a, D, 0, acc);
+                }
                 unit_reduce<R, 1>(acc, red, res);
-                if (u + G < nL) t = tn;
+                if (j >= A.lm_stage && u + G < nL) t = tn;
                 if (out_lane) {
                     const int col = u * 8 + out_c;
                     A.logits[(size_t)out_r * A.vocab + col] = res[0];
@@ -633,6 +670,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                     st_pair(dst + 1, __int_as_float(best_i), stamp);
                 }
             }
+            FUSED_MARK(18);
             if (step + 1 < A.steps && b < nA) load_A(0, b), have = true;
             // every CTA picks the tokens itself (the same comparison order everywhere)
             if (warp < n) {
@@ -662,17 +700,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                 }
             }
             if (__syncthreads_or(pl.failed)) goto leave;
+            FUSED_MARK(19);
             steps_done = step + 1;
             if (A.stop_on_zero && s_tok[0] == 0) break;
         }
     }
 leave:
+    asm volatile("cp.async.wait_all;" ::: "memory");  // nothing may still be copying into this CTA's shared memory
     if (b == 0 && tid == 0) *A.steps_done = steps_done;
 }
 
 template <int R>
 static size_t fused_smem_bytes(const FusedStepArgs &A) {
-    return sizeof(float) * ((size_t)R * A.D + (size_t)R * A.amax + (size_t)kWarps * 2 * 2 * R * 4 + kWarps * PS + 3 * DH + kThreads * 4 + 4 * kThreads * 4);
+    return sizeof(float) * ((size_t)R * A.D + (size_t)R * A.amax + (size_t)kWarps * 2 * 2 * R * 4 + kWarps * PS + 3 * DH + kThreads * 4 + 4 * kThreads * 4 + (size_t)A.lm_stage * A.D * 8);
 }
 
 template <int R>
@@ -687,14 +727,14 @@ static int32_t launch_rows(Ctx *ctx, FusedStepArgs &A) {
             int coop = 0, per_sm = 0;
             JGPT_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device));
             JGPT_REQUIRE(coop, JGPT_ERR_UNSUPPORTED, "device %d has no cooperative launch", ctx->device);
-            JGPT_CUDA_TRY(cudaFuncSetAttribute(decode_step_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-            JGPT_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<R>, kThreads, 64 * 1024));
+            JGPT_CUDA_TRY(cudaFuncSetAttribute(decode_step_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+            JGPT_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel<R>, kThreads, 160 * 1024));
             JGPT_REQUIRE(per_sm >= 1, JGPT_ERR_UNSUPPORTED, "the fused decode step does not fit an SM");
             grid_for[ctx->device & 63] = ctx->sm_count;
             ready.insert(ctx->device);
         }
     }
-    JGPT_REQUIRE(smem <= 64 * 1024, JGPT_ERR_INVALID_ARGUMENT, "model too wide for the fused decode step");
+    JGPT_REQUIRE(smem <= 160 * 1024, JGPT_ERR_INVALID_ARGUMENT, "model too wide for the fused decode step");
     const int G = grid_for[ctx->device & 63];
     JGPT_REQUIRE(G == A.grid, JGPT_ERR_ILLEGAL_STATE, "fused decode step sized for %d CTAs, device runs %d", A.grid, G);
     void *args[1] = {&A};
@@ -742,6 +782,9 @@ void fused_step_plan(FusedStepArgs &A, int sm_count, int max_len) {
     const int nbk = std::min(max_blocks, (max_len + 15) / 16);
     A.nch = std::max(1, (nbk + A.cb - 1) / A.cb);
     A.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
+    // LM head: as many of a CTA's column blocks as fit in 96 KB of shared memory are staged there during the last layer
+    const int per_cta = (A.vocab / 8 + sm_count - 1) / sm_count;
+    A.lm_stage = std::max(0, std::min(per_cta, (int)(96 * 1024 / (sizeof(float) * 8 * (size_t)A.D))));
 }
 
 int32_t launch_decode_fused(Ctx *ctx, FusedStepArgs &A) {

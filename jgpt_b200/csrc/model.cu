@@ -1067,9 +1067,9 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
 
 // ---- the fused step (decode_fused.cu) ----
 static bool fused_ok(const Model *m, const Pool *p, int n) {
-    const size_t smem = sizeof(float) * 4 * ((size_t)m->d_model + (size_t)std::max(m->d_model, m->d_ff)) + 28672;
+    const size_t smem = sizeof(float) * 4 * ((size_t)m->d_model + (size_t)std::max(m->d_model, m->d_ff)) + 28672 + 96 * 1024;
     return m->fused_step && !m->strict && n >= 1 && n <= fused_step_max_rows() && p->dhead == 16 && m->d_model == m->heads * 16 &&
-           m->d_model % 8 == 0 && m->d_ff % 8 == 0 && m->vocab % 8 == 0 && smem <= 60 * 1024 && m->layers <= kFusedMaxLayers &&
+           m->d_model % 8 == 0 && m->d_ff % 8 == 0 && m->vocab % 8 == 0 && smem <= 156 * 1024 && m->layers <= kFusedMaxLayers &&
            m->d_model <= 1024;
 }
 static size_t fused_pair_count(const Model *m) {

@@ -402,10 +402,10 @@ def run_fused_phases(ctx, prompt_len=900, new_tokens=33):
             t0 = time.perf_counter()
             model.generateGpuKv(prompt, new_tokens)
             best = min(best, time.perf_counter() - t0)
-        buf = np.zeros((256, 16), np.int64)  # the trace array's size; CTAs that do not exist leave their rows zero
+        buf = np.zeros((256, 24), np.int64)  # the trace array's size; CTAs that do not exist leave their rows zero
         B.check(lib.jgpt_debug_fused_trace_read(buf.ctypes.data_as(C.c_void_p), 256))
         buf = buf[buf.any(axis=1)]
-        ns = np.zeros((256, 16), np.int64)  # the same marks on the global timer: comparable across CTAs (0.256 us steps)
+        ns = np.zeros((256, 24), np.int64)  # the same marks on the global timer: comparable across CTAs (0.256 us steps)
         B.check(lib.jgpt_debug_fused_trace_read_ns(ns.ctypes.data_as(C.c_void_p), 256))
         ns = ns[ns.any(axis=1)]
     finally:
@@ -432,6 +432,15 @@ def run_fused_phases(ctx, prompt_len=900, new_tokens=33):
         col = ns[:, mk].astype(np.float64)
         col = (col[col > 0] - t0) / 1e3
         out["timeline_us_min_median_max"][nm] = [float(col.min()), float(np.median(col)), float(col.max())]
+    # the step's tail: final norm + LM head (1000 units of 8 columns over the CTAs) + argmax
+    t0 = ns[:, 16].min()
+    points = [(16, "last layer's W2 results stored"), (17, "final norm done"), (18, "logits and per-CTA candidates stored"),
+              (19, "tokens picked")]
+    out["tail_timeline_us_min_median_max"] = {}
+    for mk, nm in points:
+        col = ns[:, mk].astype(np.float64)
+        col = (col[col > 0] - t0) / 1e3
+        out["tail_timeline_us_min_median_max"][nm] = [float(col.min()), float(np.median(col)), float(col.max())]
     return out
 
 
