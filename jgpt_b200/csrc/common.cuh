@@ -245,7 +245,7 @@ struct BatchStepArgs {
     uint2 *att;        // [n][D]
     uint2 *act;        // [n][F]
     uint2 *cand;       // [vocab tiles][n][2] best logit of a tile and its index
-    float *part;       // [n][H][nch_max][18] split-sequence partials (plain; merged through tickets)
+    uint2 *part;       // [n][H][nch_max][18] split-sequence partials (stamped pairs; a ticket elects the warp that merges)
     int *tickets;      // [n][H], zero between launches
     unsigned stamp0;   // stamps of this launch: stamp0 + 1 ... stamp0 + layers + 2
     unsigned *abort_word;

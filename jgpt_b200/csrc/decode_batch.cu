@@ -38,6 +38,7 @@ constexpr int kWarps = 8;
 constexpr int DH = 16, PS = DH + 2;
 constexpr int BM = 16, BN = 32, BK = 64, STAGES = 4, WS = BN + 8;
 constexpr int kSlabBatch = 12;  // 16-byte reads of the activation slab a thread keeps in flight
+constexpr int kAttnGroup = 8;  // KV blocks (1 KiB each) a warp requests before it consumes them: 8 warps x 8 KiB in flight per SM
 
 // Leaving early (a wait gave up): nothing may still be copying into this CTA's shared memory.
 #define BATCH_BAIL()                                        \
@@ -48,7 +49,7 @@ constexpr int kSlabBatch = 12;  // 16-byte reads of the activation slab a thread
 
 #ifdef JGPT_B200_DECODE_TRACE
 // Timing build only: per CTA, the global timer (ns) at the phase boundaries of the second layer and of the LM head.
-constexpr int kBatchMarks = 16;
+constexpr int kBatchMarks = 24;
 __device__ long long g_batch_trace[256 * kBatchMarks];
 __device__ __forceinline__ long long global_ns() {
     long long t;
@@ -198,7 +199,7 @@ __device__ __forceinline__ float red_sum(const Shared &S, int r, int c) {
 }
 
 // ---- one warp: (row, head, chunk) of the attention ----
-__device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer, int row, int h, int c, unsigned stamp, Poll &pl) {
+__device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer, int row, int h, int c, unsigned stamp, Poll &pl, bool tr = false) {
     const int lane = threadIdx.x & 31, t = lane & 15;
     const bool vlane = lane >= 16;
     const int n = A.n;
@@ -207,6 +208,7 @@ __device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer
     if (c >= nch) return;
     const int b0 = c * A.cb, b1 = min(nbk, b0 + A.cb);
     const bool owner = c == nch - 1;  // the chunk that holds slot len - 1
+    BATCH_MARK(tr, 16);
     // block table entries of the chunk (cb <= 32) and the RoPE row: neither depends on this step's activations
     const int my_phys = (b0 + lane < b1) ? __ldcg(A.table + (size_t)seq * A.mbs + b0 + lane) : -1;
     float2 rope[DH / 2];
@@ -220,6 +222,7 @@ __device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer
         ll_load<1>(v, 1, stamp, pl, [&](int) { return src; });
         in0 = __uint_as_float(v[0].x), in1 = __uint_as_float(v[0].z);
     }
+    BATCH_MARK(tr, 17);
     float q[DH];
 #pragma unroll
     for (int j = 0; j < DH / 2; j++) {
@@ -242,7 +245,7 @@ __device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer
 #pragma unroll
     for (int d = 0; d < DH; d++) o[d] = 0.f;
     const size_t layer_base = (size_t)layer * A.n_blocks;
-    constexpr int U = 4;  // KV blocks in flight per warp
+    constexpr int U = kAttnGroup;  // KV blocks in flight per warp
     for (int bb = b0; bb < b1; bb += U) {
         __align__(16) __half rowv[U][DH];
         bool live[U];
@@ -298,6 +301,7 @@ __device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer
         }
     }
     // merge the 16 token lanes (both halves of the warp hold the same m and l)
+    BATCH_MARK(tr, 18);
     float M = m;
 #pragma unroll
     for (int off = 8; off >= 1; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
@@ -318,32 +322,50 @@ __device__ __forceinline__ void attention_warp(const BatchStepArgs &A, int layer
             }
     }
     uint2 *out = A.att + (size_t)row * A.D + h * DH;
+    BATCH_MARK(tr, 19);
     if (nch == 1) {
         if (vlane) st_pair(out + t, o[0] / fmaxf(l, 1e-12f), stamp);
         return;
     }
-    float *pp = A.part + (((size_t)row * A.H + h) * A.nch_max + c) * PS;
-    if (lane == 0) pp[0] = M, pp[1] = l;
-    if (vlane) pp[2 + t] = o[0];
-    __threadfence();
-    __syncwarp();
+    // The chunk's partial goes out as stamped pairs, so no fence is needed: a ticket (relaxed) only elects the warp that
+    // merges; that warp reads every chunk's pairs until they carry the stamp.
+    uint2 *pp = A.part + (((size_t)row * A.H + h) * A.nch_max + c) * PS;
+    if (lane == 0) st_pair(pp, M, stamp), st_pair(pp + 1, l, stamp);
+    if (vlane) st_pair(pp + 2 + t, o[0], stamp);
     int ticket = 0;
     if (lane == 0) ticket = atomicAdd(A.tickets + (size_t)row * A.H + h, 1);
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    BATCH_MARK(tr, 20);
     if (ticket != nch - 1) return;
     if (lane == 0) A.tickets[(size_t)row * A.H + h] = 0;  // for the next layer
-    __threadfence();
-    const float *p0 = A.part + (((size_t)row * A.H + h) * A.nch_max) * PS;
-    float Mx = -INFINITY;
-    for (int cc = 0; cc < nch; cc++) Mx = fmaxf(Mx, __ldcg(p0 + cc * PS));
-    float L = 0.f, acc = 0.f;
-    for (int cc = 0; cc < nch; cc++) {
-        const float mc = __ldcg(p0 + cc * PS);
-        const float w = mc == -INFINITY ? 0.f : exp2f(mc - Mx);
-        L = fmaf(__ldcg(p0 + cc * PS + 1), w, L);
-        acc = fmaf(__ldcg(p0 + cc * PS + 2 + t), w, acc);
+    // lane L merges chunk L's 18 values (nch <= 32): one wait for all of them, then warp reductions
+    const uint2 *p0 = A.part + (((size_t)row * A.H + h) * A.nch_max + min(lane, nch - 1)) * PS;
+    uint4 v[PS / 2];
+    ll_load<PS / 2>(v, PS / 2, stamp, pl, [&](int i) { return p0 + 2 * i; });
+    const bool mine = lane < nch;
+    const float mc = mine ? __uint_as_float(v[0].x) : -INFINITY;
+    float Mx = mc;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) Mx = fmaxf(Mx, __shfl_xor_sync(0xffffffffu, Mx, off));
+    const float w = (mine && mc != -INFINITY) ? exp2f(mc - Mx) : 0.f;
+    float L = __uint_as_float(v[0].z) * w;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+    float od[DH];
+#pragma unroll
+    for (int i = 1; i < PS / 2; i++) od[2 * i - 2] = __uint_as_float(v[i].x) * w, od[2 * i - 1] = __uint_as_float(v[i].z) * w;
+#pragma unroll
+    for (int width = DH / 2, off = 16; width >= 1; width >>= 1, off >>= 1) {  // lane L ends with dimension L >> 1
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < DH / 2; i++)
+            if (i < width) {
+                const float keep = upper ? od[i + width] : od[i], give = upper ? od[i] : od[i + width];
+                od[i] = keep + __shfl_xor_sync(0xffffffffu, give, off);
+            }
     }
-    if (vlane) st_pair(out + t, acc / fmaxf(L, 1e-12f), stamp);
+    od[0] += __shfl_xor_sync(0xffffffffu, od[0], 1);
+    if ((lane & 1) == 0) st_pair(out + (lane >> 1), od[0] / fmaxf(L, 1e-12f), stamp);
 }
 
 __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchStepArgs A) {
@@ -418,7 +440,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_batch_kernel(const BatchSt
             BATCH_MARK(l == 1, 3);
             for (int u = b * kWarps + warp; u < units; u += G * kWarps) {
                 const int h = u % A.H, c = (u / A.H) % A.nch_max, row = u / (A.H * A.nch_max);
+#ifdef JGPT_B200_DECODE_TRACE
+                attention_warp(A, l, row, h, c, st, pl, l == 1 && u == b * kWarps && threadIdx.x == 0);
+#else
                 attention_warp(A, l, row, h, c, st, pl);
+#endif
             }
             BATCH_MARK(l == 1, 4);
             if (__syncthreads_or(pl.failed)) BATCH_BAIL();
@@ -586,11 +612,12 @@ void batch_step_plan(BatchStepArgs &A, int sm_count, const int *lens_host) {
     int best_cb = std::min(32, max_blocks);
     double best_cost = 1e30;
     for (int cb = 2; cb <= 32; cb++) {
-        // cost model: rounds of the busiest warp x (blocks per unit + a fixed cost per unit of ~3 blocks)
+        // cost model (us): rounds of the busiest warp x (one memory round trip per group of kAttnGroup blocks + ~1.3 per unit
+        // for the table entry, q, the merge and the ticket)
         long units = 0;
         for (int i = 0; i < A.n; i++) units += (long)(((lens_host[i] + 15) / 16 + cb - 1) / cb) * A.H;
         const long rounds = (units + warps - 1) / warps;
-        const double cost = (double)rounds * (cb + 3);
+        const double cost = (double)rounds * ((cb + kAttnGroup - 1) / kAttnGroup * 1.0 + 1.3);
         if (cost < best_cost) best_cost = cost, best_cb = cb;
     }
     A.cb = best_cb;

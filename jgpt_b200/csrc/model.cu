@@ -79,7 +79,7 @@ struct Model {
     int fused_batch_rows = 0;   // rows the buffers below are sized for
     uint2 *fb_pairs = nullptr;
     uint64_t fb_pairs_n = 0;
-    float *fb_part = nullptr;
+    uint2 *fb_part = nullptr;
     int *fb_tickets = nullptr;
 };
 constexpr int kFusedBatchMaxRows = 256;
@@ -1138,7 +1138,11 @@ static int32_t ensure_fused_batch(Model *m) {
     const size_t R = (size_t)std::min(kFusedBatchMaxRows, m->max_rows), D = m->d_model, F = m->d_ff, H = m->heads;
     const size_t parts = (D + 31) / 32, vt = ((size_t)m->vocab + 31) / 32;
     m->fb_pairs_n = R * (2 * D + 2 * parts + 3 * D + D + F) + vt * R * 2;
-    if (!m->fb_part) JGPT_CUDA_TRY(cudaMalloc(&m->fb_part, sizeof(float) * R * H * (size_t)fused_batch_max_chunks(m) * 18));
+    if (!m->fb_part) {
+        const size_t np = R * H * (size_t)fused_batch_max_chunks(m) * 18;
+        JGPT_CUDA_TRY(cudaMalloc(&m->fb_part, sizeof(uint2) * np));
+        JGPT_CUDA_TRY(cudaMemsetAsync(m->fb_part, 0, sizeof(uint2) * np, m->ctx->stream));  // stamp 0: never data
+    }
     if (!m->fb_tickets) JGPT_CUDA_TRY(cudaMalloc(&m->fb_tickets, sizeof(int) * (R * H + 4)));
     JGPT_CUDA_TRY(cudaMemsetAsync(m->fb_tickets, 0, sizeof(int) * (R * H + 4), m->ctx->stream));
     uint2 *pairs = nullptr;
@@ -1157,6 +1161,7 @@ static int32_t fused_batch_enqueue(Model *m, Pool *p, int n, const int *lens_hos
     const uint32_t need = (uint32_t)m->layers + 2u;
     if (m->f_stamp > 0xE0000000u - need) {  // stamps about to wrap: start over from clean buffers (both step forms share the counter)
         JGPT_CUDA_TRY(cudaMemsetAsync(m->fb_pairs, 0, sizeof(uint2) * m->fb_pairs_n, m->ctx->stream));
+        JGPT_CUDA_TRY(cudaMemsetAsync(m->fb_part, 0, sizeof(uint2) * (size_t)m->fused_batch_rows * m->heads * fused_batch_max_chunks(m) * 18, m->ctx->stream));
         if (m->f_pairs) JGPT_CUDA_TRY(cudaMemsetAsync(m->f_pairs, 0, sizeof(uint2) * m->f_pairs_n, m->ctx->stream));
         m->f_stamp = 0;
     }
@@ -1186,7 +1191,7 @@ static int32_t fused_batch_enqueue(Model *m, Pool *p, int n, const int *lens_hos
     A.status = m->ctx->d_status;
     A.logits = m->logits, A.next = m->d_next;
     batch_step_plan(A, m->ctx->sm_count, lens_host);
-    JGPT_REQUIRE(A.nch_max <= fused_batch_max_chunks(m), JGPT_ERR_ILLEGAL_STATE, "attention chunks %d exceed the scratch (%d)", A.nch_max,
+    JGPT_REQUIRE(A.nch_max <= std::min(32, fused_batch_max_chunks(m)), JGPT_ERR_ILLEGAL_STATE, "attention chunks %d exceed the scratch (%d)", A.nch_max,
                  fused_batch_max_chunks(m));
     return launch_decode_batch(m->ctx, A);
 }
