@@ -219,6 +219,7 @@ struct FusedStepArgs {
     int *status;
     // plan
     int grid, nch, cb, ks_o, kl_o, ks_2, kl_2, amax, lm_stage;
+    int test_withhold;  // tests only: one CTA withholds a result (JGPT_B200_FUSED_TEST_WITHHOLD=1)
     float scale_log2e;
 };
 int fused_step_max_rows();

@@ -507,7 +507,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                 FUSED_MARK(1);
                 unit_reduce<R, 1>(acc, red, res);
                 FUSED_MARK(7);
-                if (out_lane) st_pair(A.ll_qkv + (size_t)out_r * 3 * D + z * D + c0 + out_c, res[0], stamp);
+                // test hook (host-side fault injection): CTA 0 withholds its first layer's result, so the units that
+                // need it run into their bounded wait and the launch reports WAIT_TIMEOUT
+                if (out_lane && !(A.test_withhold && b == 0 && l == 0))
+                    st_pair(A.ll_qkv + (size_t)out_r * 3 * D + z * D + c0 + out_c, res[0], stamp);
             }
             have = false;
             if (b < nO * kso) {  // Wo: unit = 8 columns x one k range; on its way while the attention runs

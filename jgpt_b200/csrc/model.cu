@@ -1123,6 +1123,7 @@ static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_ze
     A.next = next_dev;
     A.status = m->ctx->d_status;
     fused_step_plan(A, m->ctx->sm_count, max_len_after);
+    A.test_withhold = env_int("JGPT_B200_FUSED_TEST_WITHHOLD", 0);
     return launch_decode_fused(m->ctx, A);
 }
 

@@ -233,3 +233,39 @@ def test_a_refused_cooperative_launch_falls_back_to_the_multi_launch_step(ctx, m
         for pool in pools:
             pool.close()
         fused.close(), plain.close(), om.close()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_works(ctx, monkeypatch):
+    """Every wait inside the one-launch step is bounded.  A test hook lets one CTA withhold a result (nothing faults,
+    nothing spins for ever): the units that need it give up after their poll limit (~0.5 s), the launch reports
+    wait-timeout through the status word, the call fails without tokens or a length change - and the next call, with
+    fresh stamps, runs as if nothing had happened."""
+    from jgpt_b200 import JgptError
+
+    om, fused, plain = _three(ctx, GEOM, 4, 0.15, monkeypatch)
+    pools = [g.newPool(n_blocks=6, max_seqs=1) for g in (fused, plain)]
+    try:
+        prompt = np.array([(i * 7 + 3) % GEOM[0] for i in range(20)], np.int32)
+        seqs, toks = [], None
+        for g, pool in zip((fused, plain), pools):
+            s = pool.seq_alloc()
+            _, toks = g.forwardPrefillBatch(pool, [s], [prompt])
+            seqs.append(s)
+        monkeypatch.setenv("JGPT_B200_FUSED_TEST_WITHHOLD", "1")
+        with pytest.raises(JgptError, match="wait-timeout"):
+            fused.forwardDecodeBatch(pools[0], [seqs[0]], toks, [20], [20])
+        assert pools[0].length(seqs[0]) == 20
+        monkeypatch.delenv("JGPT_B200_FUSED_TEST_WITHHOLD")
+        lf, tf = fused.forwardDecodeBatch(pools[0], [seqs[0]], toks, [20], [20])
+        lp, tp = plain.forwardDecodeBatch(pools[1], [seqs[1]], toks, [20], [20])
+        assert np.abs(lf - lp).max() < 1e-4 and np.array_equal(tf, tp)
+        # generation after an aborted multi-step launch as well
+        monkeypatch.setenv("JGPT_B200_FUSED_TEST_WITHHOLD", "1")
+        with pytest.raises(JgptError, match="wait-timeout"):
+            fused.generateGpuKv(prompt, 12)
+        monkeypatch.delenv("JGPT_B200_FUSED_TEST_WITHHOLD")
+        assert np.array_equal(fused.generateGpuKv(prompt, 12), plain.generateGpuKv(prompt, 12))
+    finally:
+        for pool in pools:
+            pool.close()
+        fused.close(), plain.close(), om.close()
