@@ -202,7 +202,8 @@ struct FusedStepArgs {
     const float2 *rope;
     int n_blocks, mbs;
     // rows: idx = [5][n] token ids, position rows (unused here), sequence ids, RoPE positions, lengths after the append
-    const int *idx;
+    const int *idx;       // device copy, or nullptr: then idx_inline holds them (no upload before a per-token call)
+    int idx_inline[20];
     int n, steps, stop_on_zero;
     // exchange buffers: (value, stamp) pairs, rows padded to the kernel's row count (4 at most)
     uint2 *ll_qkv;   // [rows][3 D]
@@ -215,6 +216,7 @@ struct FusedStepArgs {
     float *logits;   // [n][vocab]
     int *next;       // [steps][n] tokens picked
     int *steps_done;
+    int *next_host, *steps_done_host;  // the same in mapped page-locked host memory (nullptr: not wanted)
     unsigned *sync_words;  // [1] abort word: holds stamp0 + 1 of a launch that gave up
     int *status;
     // plan

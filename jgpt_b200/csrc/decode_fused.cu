@@ -218,10 +218,10 @@ __device__ __forceinline__ bool residual_norm(float *x, const uint2 *p, int ks, 
 // One (row, head, chunk) of the attention: RoPE on q, the new token appended by the chunk that owns its slot, a
 // partial (maximum, sum, outputs) of this chunk's tokens left in `part`.  `sq` = 3 * DH floats of shared memory.
 __device__ __forceinline__ bool attention_unit(const FusedStepArgs &A, int layer, int r, int h, int c, int step, unsigned stamp, Poll &pl,
-                                               float *red, float *sq, bool trace_on = false) {
+                                               float *red, float *sq, const int *idx, bool trace_on = false) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = A.n;
-    const int seq = A.idx[2 * n + r], rp = A.idx[3 * n + r] + step, len = A.idx[4 * n + r] + step;
+    const int seq = idx[2 * n + r], rp = idx[3 * n + r] + step, len = idx[4 * n + r] + step;
     const int nbk = (len + 15) >> 4;
     const int b0 = c * A.cb, b1 = min(nbk, b0 + A.cb);  // a row shorter than the launch's longest leaves chunks empty
     const int t0 = b0 * 16, t1 = min(len, b1 * 16);
@@ -456,9 +456,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
     float *stage = sq + 3 * DH;                              // [256][4] chunk partials on their way to be merged
     float *lm_w = stage + kThreads * 4 + 4 * kThreads * 4;  // [lm_stage][D][8] this CTA's first LM-head column blocks
     __shared__ int s_tok[R];
+    __shared__ int s_idx[5 * 4];  // the rows' descriptors: out of the launch parameters (a per-token call) or device memory
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, G = gridDim.x, n = A.n, D = A.D, F = A.F;
     const int half_col = (tid & 1) * 4;
+    if (tid < 5 * A.n) s_idx[tid] = A.idx ? A.idx[tid] : A.idx_inline[tid];
     for (int e = tid; e < R * D; e += kThreads) x[e] = 0.f;
     for (int e = tid; e < R * A.amax; e += kThreads) a[e] = 0.f;
     __syncthreads();
@@ -483,8 +485,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
         // ---- embedding + learned position row (embedding_token_fwd_kernel + add_position_embedding_broadcast_kernel)
         for (int e = tid; e < n * D; e += kThreads) {
             const int r = e / D, j = e % D;
-            const int id = step == 0 ? A.idx[r] : s_tok[r];
-            const int pr = (A.idx[3 * n + r] + step) % A.max_seq;
+            const int id = step == 0 ? s_idx[r] : s_tok[r];
+            const int pr = (s_idx[3 * n + r] + step) % A.max_seq;
             x[e] = __ldg(A.tok + (size_t)id * D + j) + __ldg(A.pos + (size_t)pr * D + j);
         }
         __syncthreads();
@@ -533,9 +535,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
             for (int u = b; u < n * A.H * A.nch; u += G) {
                 const int c = u % A.nch, h = (u / A.nch) % A.H, r = u / (A.nch * A.H);
 #ifdef JGPT_B200_DECODE_TRACE
-                if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq, tracing)) goto leave;
+                if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq, s_idx, tracing)) goto leave;
 #else
-                if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq)) goto leave;
+                if (!attention_unit(A, l, r, h, c, step, stamp, pl, red, sq, s_idx)) goto leave;
 #endif
             }
 
@@ -699,7 +701,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
                 if (bi == 0x7fffffff) bi = 0;  // nothing compared greater than -inf: index 0, as argmax_kernel answers
                 if (lane == 0) {
                     s_tok[warp] = bi;
-                    if (b == 0) A.next[(size_t)step * n + warp] = bi;
+                    if (b == 0) {
+                        A.next[(size_t)step * n + warp] = bi;
+                        if (A.next_host) A.next_host[(size_t)step * n + warp] = bi;  // mapped host memory: no copy after the launch
+                    }
                 }
             }
             if (__syncthreads_or(pl.failed)) goto leave;
@@ -710,7 +715,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_step_kernel(const FusedSte
     }
 leave:
     asm volatile("cp.async.wait_all;" ::: "memory");  // nothing may still be copying into this CTA's shared memory
-    if (b == 0 && tid == 0) *A.steps_done = steps_done;
+    if (b == 0 && tid == 0) {
+        *A.steps_done = steps_done;
+        if (A.steps_done_host) *A.steps_done_host = steps_done;
+    }
 }
 
 template <int R>

@@ -74,6 +74,7 @@ struct Model {
     uint32_t f_stamp = 0;       // stamps handed out so far; a launch uses f_stamp + 1 ... f_stamp + steps * layers
     int *f_ints = nullptr;      // tokens of a multi-step launch, steps done, abort word
     int *h_fused = nullptr;     // pinned: [kFusedMaxSteps * 4] tokens + steps done
+    int *hd_fused = nullptr, *hd_next = nullptr;  // device-side addresses of h_fused and h_next: the kernel writes its results there itself
     // The same for batches (decode_batch.cu; JGPT_B200_FUSED_BATCH=1: on): rows 5 .. fused_batch_rows
     int fused_batch = 0;
     int fused_batch_rows = 0;   // rows the buffers below are sized for
@@ -1086,6 +1087,8 @@ static int32_t ensure_fused(Model *m) {
     uint2 *pairs = nullptr;
     JGPT_CUDA_TRY(cudaMalloc(&pairs, sizeof(uint2) * m->f_pairs_n));
     JGPT_CUDA_TRY(cudaMemsetAsync(pairs, 0, sizeof(uint2) * m->f_pairs_n, m->ctx->stream));  // stamp 0: never data
+    JGPT_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&m->hd_fused), m->h_fused, 0));
+    JGPT_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&m->hd_next), m->h_next, 0));
     m->f_pairs = pairs;
     m->f_stamp = 0;
     return JGPT_OK;
@@ -1094,7 +1097,10 @@ static int *fused_tokens_dev(Model *m) { return m->f_ints; }
 static int *fused_steps_done_dev(Model *m) { return m->f_ints + (size_t)kFusedMaxSteps * 4; }
 // Enqueues `steps` decode steps of the n rows described in m->d_idx (already uploaded).  Tokens go to `next_dev`
 // ([steps][n]); with stop_on_zero (n == 1) the launch ends after a sampled 0.
-static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_zero, int max_len_after, int *next_dev) {
+// idx_host: the rows' descriptors ([5][n], travel in the launch parameters: no upload).  next_host / done_host: mapped
+// host addresses the kernel also writes the tokens and the step count to (nullptr: not wanted).
+static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_zero, int max_len_after, int *next_dev, const int *idx_host,
+                             int *next_host, int *done_host) {
     const size_t D = m->d_model, F = m->d_ff, H = m->heads, R = 4;
     const uint32_t need = (uint32_t)steps * (uint32_t)m->layers;
     if (m->f_stamp > 0xE0000000u - need) {  // stamps about to wrap: start over from clean buffers
@@ -1107,7 +1113,9 @@ static int32_t fused_enqueue(Model *m, Pool *p, int n, int steps, int stop_on_ze
     for (int l = 0; l < m->layers; l++) A.Lw[l] = m->L[(size_t)l];
     A.vocab = m->vocab, A.max_seq = m->max_seq, A.D = m->d_model, A.H = m->heads, A.layers = m->layers, A.F = m->d_ff, A.eps = m->eps;
     A.kv = p->kv, A.table = p->d_table, A.rope = p->d_rope, A.n_blocks = p->n_blocks, A.mbs = p->max_blocks_per_seq;
-    A.idx = m->d_idx, A.n = n, A.steps = steps, A.stop_on_zero = stop_on_zero;
+    A.idx = nullptr, A.n = n, A.steps = steps, A.stop_on_zero = stop_on_zero;
+    for (int i = 0; i < 5 * n; i++) A.idx_inline[i] = idx_host[i];
+    A.next_host = next_host, A.steps_done_host = done_host;
     uint2 *f = m->f_pairs;
     A.ll_qkv = f, f += R * 3 * D;
     A.ll_part = f, f += R * H * kFusedMaxChunks * 18;
@@ -1690,9 +1698,11 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
     if (form) {
         if ((rc = form == 1 ? ensure_fused(m) : ensure_fused_batch(m))) return rc;
         if ((rc = ensure_logits(m, n))) return rc;
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+        // the small form takes the rows' descriptors in its launch parameters and writes greedy tokens to h_next itself
+        if (form == 2) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
         if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
-        rc = form == 1 ? fused_enqueue(m, p, n, 1, 0, max_len, m->d_next) : fused_batch_enqueue(m, p, n, lens);
+        rc = form == 1 ? fused_enqueue(m, p, n, 1, 0, max_len, m->d_next, m->h_idx, sampled ? nullptr : m->hd_next, nullptr)
+                       : fused_batch_enqueue(m, p, n, lens);
         if (rc == JGPT_ERR_UNSUPPORTED) {
             (form == 1 ? m->fused_step : m->fused_batch) = 0;
         } else if (rc) {
@@ -1702,7 +1712,7 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
                 sample_kernel<<<n, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
                 JGPT_CUDA_TRY(cudaGetLastError());
             }
-            JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+            if (form == 2 || sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
             JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
             one_launch = true;
         }
@@ -1869,10 +1879,9 @@ static bool fused_greedy_steps(Model *m, Pool *p, jgpt_kvpool poolh, int32_t seq
         if ((r2 = ensure_logits(m, 1))) return r2;
         int *ids = m->h_idx;  // packed [5][1]
         ids[0] = first_id, ids[1] = rope % m->max_seq, ids[2] = seq, ids[3] = rope, ids[4] = len_before + 1;
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5, cudaMemcpyHostToDevice, st));
-        if ((r2 = fused_enqueue(m, p, 1, T, 1, len_before + T, fused_tokens_dev(m)))) return r2;
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_fused, fused_tokens_dev(m), sizeof(int) * (size_t)T, cudaMemcpyDeviceToHost, st));
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_fused + (size_t)kFusedMaxSteps * 4, fused_steps_done_dev(m), sizeof(int), cudaMemcpyDeviceToHost, st));
+        m->h_fused[(size_t)kFusedMaxSteps * 4] = 0;  // the kernel writes the tokens and the step count into h_fused itself
+        if ((r2 = fused_enqueue(m, p, 1, T, 1, len_before + T, fused_tokens_dev(m), m->h_idx, m->hd_fused, m->hd_fused + (size_t)kFusedMaxSteps * 4)))
+            return r2;
         JGPT_CUDA_TRY(status_enqueue_read(m->ctx));
         JGPT_CUDA_TRY(cudaStreamSynchronize(st));
         if ((r2 = status_check_after_sync(m->ctx, p, "jgpt_generate_greedy"))) return r2;
