@@ -109,13 +109,17 @@ Registry<Comm> &comm_registry() {
 int32_t nccl_settle(Comm *c, ncclResult_t first, const char *what, int timeout_ms) {
     NcclApi &api = nccl_api();
     ncclResult_t state = first;
-    const auto deadline = Clock::now() + std::chrono::milliseconds(timeout_ms);
+    const auto start = Clock::now();
+    const auto deadline = start + std::chrono::milliseconds(timeout_ms);
+    const auto spin_until = start + std::chrono::microseconds(200);
     while (state == ncclInProgress) {
         if (Clock::now() > deadline) {
             c->broken = true;
             return fail(JGPT_ERR_TIMEOUT, "%s: still in progress after %d ms (a peer rank is late or gone)", what, timeout_ms);
         }
-        std::this_thread::sleep_for(std::chrono::microseconds(50));
+        // A call on a healthy communicator settles within microseconds: ask without sleeping for the first
+        // 200 us (a sleep costs about 0.1 ms of timer slack per step), then back off.
+        if (Clock::now() > spin_until) std::this_thread::sleep_for(std::chrono::microseconds(50));
         const ncclResult_t q = api.CommGetAsyncError(c->nccl, &state);
         if (q != ncclSuccess) state = q;
     }
