@@ -17,6 +17,9 @@
 
 #include <algorithm>
 #include <chrono>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 namespace jgpt {
 
@@ -929,6 +932,46 @@ extern "C" __attribute__((visibility("default"))) int jgpt_debug_decode_trace(lo
 }
 #endif
 
+// Clusters of `c` CTAs of the scalar dhead-16.. decode kernel (this block size and ring) that the device holds at once,
+// as cudaOccupancyMaxActiveClusters reports it; cached per shape.  On B200 with 416 threads and a 72 KiB ring:
+// 296 single CTAs, but 93 / 71 / 56 / 45 / 37 / 33 clusters of 3 / 4 / 5 / 6 / 7 / 8 (a cluster stays inside one GPC).
+// 0 when the query fails (the caller then plans without clusters).
+static int cluster_capacity(Pool *p, bool fused, int threads, size_t smem, int c) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, int, int, size_t, int, int>, int> cache;
+    const auto key = std::make_tuple(p->ctx->device, p->dhead, (int)fused, smem, threads, c);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) return it->second;
+    }
+    void (*kern)(const DecodeParams) = nullptr;
+    int variant = -1;
+    switch (p->dhead) {
+        case 4: kern = fused ? attn_decode_kernel<4, true, false> : attn_decode_kernel<4, false, false>, variant = 0; break;
+        case 8: kern = fused ? attn_decode_kernel<8, true, false> : attn_decode_kernel<8, false, false>, variant = 4; break;
+        case 16: kern = fused ? attn_decode_kernel<16, true, false> : attn_decode_kernel<16, false, false>, variant = 8; break;
+        case 32: kern = fused ? attn_decode_kernel<32, true, false> : attn_decode_kernel<32, false, false>, variant = 12; break;
+        default: return 0;
+    }
+    int n = 0;
+    if (decode_opt_in_smem(kern, variant + (fused ? 1 : 0), p->ctx->device) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)c, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+        cfg.gridDim = dim3((unsigned)c * 64), cfg.blockDim = dim3((unsigned)threads), cfg.dynamicSmemBytes = smem;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    cache[key] = n;
+    return n;
+}
+
 // Split-K chunk length of a launch with `base` (layer, sequence, head group) triples of up to max_blocks KV blocks.
 // Two CTAs fit on an SM.  When the triples alone fill those slots the launch runs in several waves anyway and
 // 32-block chunks keep the per-item set-up small.  Otherwise every sequence is cut into as many chunks as still
@@ -968,10 +1011,35 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     const int per_sm = p->persistent > 0 ? p->persistent : 2;
     const long long slots = (long long)per_sm * p->ctx->sm_count;
     const bool dynamic = p->persistent > 0;
-    P.chunk_blocks = p->chunk_blocks > 0 ? p->chunk_blocks : pick_chunk_blocks(p, (long long)n_layers * n * P.n_hg, max_blocks);
+    P.stages = p->stages > 0 ? p->stages : (overlapped_single ? 3 : 4);
+    const int n_cons = ((kBlockTokens * P.HG + 31) / 32) * 32;
+    const int threads = n_cons + 32;
+    const size_t stage_bytes = (size_t)P.HG * 2 * kBlockTokens * DH * 2;
+    const size_t smem = stage_bytes * P.stages;
+    const bool may_cluster = p->cluster_merge && !dynamic && !p->decode_mma;
+    if (p->chunk_blocks > 0) {
+        P.chunk_blocks = p->chunk_blocks;
+    } else if (overlapped_single && may_cluster) {
+        // The per-layer launch of the model's decode step: the chunks of a sequence are one cluster, so the launch is one
+        // wave only while the device holds `base` clusters of that size at once -- fewer CTAs than two per SM (see
+        // cluster_capacity; clusters beyond it wait for a whole CTA time).  Most chunks of at least 4 blocks that stay
+        // 1/16 under that number (a launch at the exact limit measured slower than the next smaller cluster).  JGPT-35M
+        // step, ms per step before / after: 40 rows 0.591 / 0.509, 48 rows 0.614 / 0.512, 96 rows 0.775 / 0.672;
+        // up to 29 rows ten chunks merged through global scratch became eight in a cluster (16 rows: 0.430 / 0.413).
+        const long long base = (long long)n * P.n_hg;
+        int c = 1;
+        for (int t = std::min(8, (max_blocks + 3) / 4); t >= 2; t--)
+            if (16 * base <= 15ll * cluster_capacity(p, k_new != nullptr, threads, smem, t)) {
+                c = t;
+                break;
+            }
+        c = std::max(c, (max_blocks + 31) / 32);  // a chunk holds at most 32 blocks
+        P.chunk_blocks = std::min(32, std::max(4, (max_blocks + c - 1) / c));
+    } else {
+        P.chunk_blocks = pick_chunk_blocks(p, (long long)n_layers * n * P.n_hg, max_blocks);
+    }
     P.max_len = max_blocks * kBlockTokens;
     P.max_chunks = std::max(1, (max_blocks + P.chunk_blocks - 1) / P.chunk_blocks);
-    P.stages = p->stages > 0 ? p->stages : (overlapped_single ? 3 : 4);
     P.overlap = ov;
     P.stream_hint = p->stream_hint;
     P.scale_log2e = (1.0f / sqrtf((float)DH)) * 1.4426950408889634f;
@@ -983,7 +1051,7 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
     // Only for launches of a wave or two: there the merge's global round trips are a visible part of the launch (per-layer
     // launch at batch 64 / context 1024: 24.1 -> 22.7 us).  A launch of many waves hides them behind other CTAs' copies,
     // and co-scheduling pairs of CTAs costs it more than it saves (12-layer launch: 198 us without, 202 us with).
-    P.cluster = (p->cluster_merge && !dynamic && !p->decode_mma && P.max_chunks >= 2 && P.max_chunks <= 8 &&
+    P.cluster = (may_cluster && P.max_chunks >= 2 && P.max_chunks <= 8 &&
                  items <= 4ll * p->ctx->sm_count) ? 1 : 0;
     if (P.max_chunks > 1 && !P.cluster) {
         int32_t rc = pool_ensure_split_scratch(p, (uint64_t)n_layers * n * P.max_chunks * p->heads * (DH + 2),
@@ -1002,10 +1070,6 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
         g_decode_trace = d_trace, g_decode_trace_items = P.n_items;
     }
 #endif
-    const int n_cons = ((kBlockTokens * P.HG + 31) / 32) * 32;
-    const int threads = n_cons + 32;
-    const size_t stage_bytes = (size_t)P.HG * 2 * kBlockTokens * DH * 2;
-    const size_t smem = stage_bytes * P.stages;
     int grid = P.n_items;
     if (dynamic && (long long)P.n_items > slots) {
         grid = (int)slots;

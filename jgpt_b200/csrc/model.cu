@@ -405,10 +405,27 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     const bool gamma_staged = NORM && K <= kGammaSmem;
     if (gamma_staged)
         for (int k = tid; k < K; k += 256) s_gamma[k] = F.gamma[k];
-    if (F.pdl & 1) griddep_wait();
+    // weight tiles do not depend on the previous kernel either: a launch that moved in early requests the first
+    // STAGES - 1 of them before it waits (they join the first committed group below)
+    const int w_k = tid >> 3, w_c = (tid & 7) * 4;  // second chunk: k + 32
+    const bool w_col_ok = n0 + w_c < N;
+    const float *w_src = W + (size_t)w_k * N + (w_col_ok ? n0 + w_c : 0);
+    auto load_w = [&](int buf, int k0) {
+        const bool k1 = w_col_ok && k0 + w_k < K, k2 = w_col_ok && k0 + w_k + 32 < K;
+        cp_async16(&Ws[buf][w_k][w_c], k1 ? w_src + (size_t)k0 * N : W, k1);
+        cp_async16(&Ws[buf][w_k + 32][w_c], k2 ? w_src + (size_t)(k0 + 32) * N : W, k2);
+    };
+    const int nk = (K + BK - 1) / BK;
+    const bool early_w = (F.pdl & 1) != 0;
+    if (early_w) {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; s++)
+            if (s < nk) load_w(s, s * BK);
+        griddep_wait();
+    }
     if (F.pdl & 2) griddep_launch_dependents();  // the whole grid is resident: the next launch cannot get in its way
 
-    // this thread's copy slots: MT 16-byte chunks of A (rows a_r, a_r + 16), two of W per k tile
+    // this thread's copy slots of A: MT 16-byte chunks (rows a_r, a_r + 16)
     const int a_r = tid >> 4, a_c = (tid & 15) * 4;
     bool a_row_ok[MT];
     const float *a_src[MT];
@@ -417,18 +434,16 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         a_row_ok[i] = m0 + a_r + 16 * i < M;
         a_src[i] = A + (size_t)(a_row_ok[i] ? (rowsel ? rowsel[m0 + a_r + 16 * i] : m0 + a_r + 16 * i) : 0) * K + a_c;
     }
-    const int w_k = tid >> 3, w_c = (tid & 7) * 4;  // second chunk: k + 32
-    const bool w_col_ok = n0 + w_c < N;
-    const float *w_src = W + (size_t)w_k * N + (w_col_ok ? n0 + w_c : 0);
-    auto load_tiles = [&](int buf, int k0) {
+    auto load_a = [&](int buf, int k0) {
 #pragma unroll
         for (int i = 0; i < MT; i++) {
             const bool ak = a_row_ok[i] && k0 + a_c < K;
             cp_async16(&As[buf][a_r + 16 * i][a_c], ak ? a_src[i] + k0 : A, ak);
         }
-        const bool k1 = w_col_ok && k0 + w_k < K, k2 = w_col_ok && k0 + w_k + 32 < K;
-        cp_async16(&Ws[buf][w_k][w_c], k1 ? w_src + (size_t)k0 * N : W, k1);
-        cp_async16(&Ws[buf][w_k + 32][w_c], k2 ? w_src + (size_t)(k0 + 32) * N : W, k2);
+    };
+    auto load_tiles = [&](int buf, int k0) {
+        load_a(buf, k0);
+        load_w(buf, k0);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
@@ -440,11 +455,13 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
 #pragma unroll
             for (int e = 0; e < 4; e++) acc[i][j][e] = 0.f, cor[i][j][e] = 0.f;
 
-    const int nk = (K + BK - 1) / BK;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
-        if (s < nk) load_tiles(s, s * BK);
-        else asm volatile("cp.async.commit_group;" ::: "memory");
+        if (s < nk) {
+            load_a(s, s * BK);
+            if (!early_w) load_w(s, s * BK);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
     // the residual elements this thread adds in the epilogue, requested now so that they do not cost a round trip then
     const float *Rz = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
@@ -925,8 +942,9 @@ static bool small_mode(const Model *m, int rows) {
     return !m->strict && rows <= 512 && m->d_model % 4 == 0 && m->d_ff % 16 == 0 && m->vocab % 4 == 0 &&
            !(m->umma_min_rows > 0 && rows >= m->umma_min_rows);
 }
-static int32_t pair_interleaved(Model *m, const float *W1, const float *W3, int K, int Fo, const float **out) {
+static int32_t pair_interleaved(Model *m, const float *W1, const float *W3, int K, int Fo, const float **out, bool *fresh = nullptr) {
     auto it = m->w13i.find(W1);
+    if (fresh) *fresh = it == m->w13i.end();
     if (it == m->w13i.end()) {
         float *buf = nullptr;
         JGPT_CUDA_TRY(cudaMalloc(&buf, sizeof(float) * (size_t)K * 2 * Fo));
@@ -949,7 +967,11 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(256), cfg.stream = m->ctx->stream, cfg.attrs = attr, cfg.numAttrs = (fuse.pdl & 1) ? 1 : 0;
-    if (M >= small_rows_for_wide_tiles()) {
+    // 32-row tiles also where the 16-row grid would no longer be resident at once (three CTAs per SM) while the 32-row
+    // grid is: a few CTAs left for a second wave cost a whole tile time (W1,W3 from 145 rows on: 160 rows 1.01 ms per step)
+    const long long resident = 3ll * m->ctx->sm_count, col_tiles = (long long)((N + 31) / 32) * nb;
+    const bool spills = col_tiles * ((M + 15) / 16) > resident && col_tiles * ((M + 31) / 32) <= resident;
+    if (M >= small_rows_for_wide_tiles() || spills) {
         cfg.gridDim = dim3((N + 31) / 32, (M + 31) / 32, nb), cfg.dynamicSmemBytes = gemm_small_smem_bytes<4, 2>();
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 2>, A, B, M, K, N, rowsel, fuse));
     } else {
@@ -988,11 +1010,12 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         if ((rc = small_launch<false, 1>(m, m->att, rows, D, D, 1, Wo, Cx, Rx, nullptr,
                                          SmallFuse{nullptr, nullptr, m->ss_b, 0, 0.f, (ov >= 2 ? 1 : 0) | (ov >= 3 ? 2 : 0)}))) return rc;
         const float *pair = nullptr;
-        if ((rc = pair_interleaved(m, y.w1, y.w3, D, F, &pair))) return rc;
+        bool fresh = false;  // just written by a kernel on this stream: that launch must not read weights ahead of its wait
+        if ((rc = pair_interleaved(m, y.w1, y.w3, D, F, &pair, &fresh))) return rc;
         const float *Wp[1] = {pair};
         float *Ch[1] = {m->h1};
         if ((rc = small_launch<true, 2>(m, m->x, rows, D, 2 * F, 1, Wp, Ch, nullptr, nullptr,
-                                        SmallFuse{y.norm2, m->ss_b, nullptr, parts, m->eps, ov >= 3 ? 3 : 0}))) return rc;
+                                        SmallFuse{y.norm2, m->ss_b, nullptr, parts, m->eps, ov >= 3 ? (fresh ? 2 : 3) : 0}))) return rc;
         const float *W2[1] = {y.w2};
         if ((rc = small_launch<false, 1>(m, m->h1, rows, F, D, 1, W2, Cx, Rx, nullptr,
                                          SmallFuse{nullptr, nullptr, m->ss_a, 0, 0.f, ov >= 3 ? 3 : 0}))) return rc;
