@@ -51,6 +51,7 @@ struct DecodeParams {
     int *counters;  // [0] next item, [1] CTAs that have finished (the last one resets both)
 #ifdef JGPT_B200_DECODE_TRACE
     long long *trace;  // experiments only: 8 timestamps per CTA (never compiled into the shipped library)
+    Timeline timeline;
 #endif
 };
 
@@ -181,6 +182,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     const int tid = threadIdx.x;
 #ifdef JGPT_B200_DECODE_TRACE
     long long tr_gt0 = 0, tr_c0 = clock64(), tr_c1 = 0, tr_c2 = 0, tr_c3 = 0, tr_c4 = 0;
+    timeline_in(P.timeline);
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tr_gt0));
 #endif
     const int n_cons = ((BT * P.HG + 31) / 32) * 32;  // consumer threads (padded to whole warps)
@@ -212,6 +214,9 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     // With overlap 2 the scalar consumers wait later still: right before they read q (see below).
     const bool late_wait = P.overlap == 2 && !MMA;
     if (P.overlap && !(P.overlap == 2 && is_producer) && !(late_wait && !is_producer)) griddep_wait();
+#ifdef JGPT_B200_DECODE_TRACE
+    if (!late_wait) timeline_at(P.timeline, 1);
+#endif
     bool waited = !late_wait || is_producer;
     uint32_t it = 0;  // KV blocks processed so far by this CTA (producer and consumers count alike)
     int stage = 0;    // it % NS, kept incrementally (no integer division in the block loop)
@@ -363,6 +368,9 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
             // RoPE position -- has been fetched above; q, k_new, v_new and every store come after the wait.
             griddep_wait();
             waited = true;
+#ifdef JGPT_B200_DECODE_TRACE
+            timeline_at(P.timeline, 1);
+#endif
         }
 
         if (b0 >= b1 || !seq_ok) {
@@ -824,6 +832,7 @@ __global__ void __launch_bounds__(max_head_group<DH>() * kBlockTokens + 32, 2) a
     __syncthreads();
 #ifdef JGPT_B200_DECODE_TRACE
     tr_c4 = clock64();
+    timeline_at(P.timeline, 2);
     if (tid == 0 && P.trace) {
         long long gt1;
         unsigned smid;
@@ -1065,6 +1074,7 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
         static int launch_no = 0;
         if (!d_trace) cudaMalloc(&d_trace, sizeof(long long) * 8 * 65536);
         // two halves used in turn: the last two launches can be compared (where did the second start / the first end)
+        if (n_layers == 1) P.timeline = timeline_next();
         P.trace = P.n_items <= 32768 ? d_trace + (size_t)(launch_no & 1) * 8 * 32768 : nullptr;
         launch_no++;
         g_decode_trace = d_trace, g_decode_trace_items = P.n_items;

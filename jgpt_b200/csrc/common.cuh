@@ -273,4 +273,32 @@ int32_t launch_attn_prefill(Pool *p, int layer, const float *q, const float *k, 
                             const int *seq_ids_host, const int *seq_starts_host, const int *rope_offsets_host,
                             int n_seqs, float *out, float *out_image = nullptr, bool skip_append = false, int fast_mode = -1);
 
+#ifdef JGPT_B200_DECODE_TRACE
+// Step timeline (trace builds only, never in the shipped library): per launch of the multi-launch decode step, the
+// global-timer ns of {first CTA in, last CTA past its wait for the previous kernel, last CTA out}.
+struct Timeline {
+    unsigned long long *buf;  // device, 4 words per slot
+    int slot;
+};
+Timeline timeline_next();  // the next slot of the step being enqueued (model.cu)
+__device__ __forceinline__ unsigned long long timeline_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void timeline_in(const Timeline &T) {
+    if (T.buf && threadIdx.x == 0) {
+        atomicMin(T.buf + 4 * T.slot, timeline_now());
+        // which SM each of the launch's first 256 CTAs ran on (after the 256 slots of four words)
+        const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        if (cta < 256) T.buf[4 * 256 + 256 * T.slot + cta] = smid + 1;
+    }
+}
+__device__ __forceinline__ void timeline_at(const Timeline &T, int which) {
+    if (T.buf && threadIdx.x == 0) atomicMax(T.buf + 4 * T.slot + which, timeline_now());
+}
+#endif
+
 }  // namespace jgpt

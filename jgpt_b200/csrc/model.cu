@@ -65,7 +65,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
-    int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = by batch size)
+    int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = the default, 3)
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
     // Steps of up to four rows as one cooperative launch (decode_fused.cu; JGPT_B200_FUSED_STEP=0: off).  Sized on first use.
     int fused_step = 1;
@@ -383,6 +383,9 @@ struct SmallFuse {
     // previous kernel on the stream finished: wait for that kernel before touching memory.  bit 1: let the NEXT
     // launch on the stream move in early (it waits for this kernel itself before it reads this kernel's output).
     int pdl = 0;
+#ifdef JGPT_B200_DECODE_TRACE
+    Timeline timeline;
+#endif
 };
 
 // MT = 2: 32-row tiles (two MMA row blocks per warp share every weight fragment) for the larger decode batches.
@@ -403,6 +406,9 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     constexpr int kGammaSmem = 1024;
     __shared__ float s_gamma[NORM ? kGammaSmem : 1];
     const bool gamma_staged = NORM && K <= kGammaSmem;
+#ifdef JGPT_B200_DECODE_TRACE
+    timeline_in(F.timeline);
+#endif
     if (gamma_staged)
         for (int k = tid; k < K; k += 256) s_gamma[k] = F.gamma[k];
     // weight tiles do not depend on the previous kernel either: a launch that moved in early requests the first
@@ -423,6 +429,9 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             if (s < nk) load_w(s, s * BK);
         griddep_wait();
     }
+#ifdef JGPT_B200_DECODE_TRACE
+    timeline_at(F.timeline, 1);
+#endif
     if (F.pdl & 2) griddep_launch_dependents();  // the whole grid is resident: the next launch cannot get in its way
 
     // this thread's copy slots of A: MT 16-byte chunks (rows a_r, a_r + 16)
@@ -573,6 +582,9 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             if (lane == 0 && m < M) F.ss_out[(size_t)m * gridDim.x + blockIdx.x] = sq;
         }
     }
+#ifdef JGPT_B200_DECODE_TRACE
+    timeline_at(F.timeline, 2);
+#endif
 }
 
 // W1, W3 [K, Fo] -> [K, 2 Fo] with groups of 16 columns alternating (what EPI 2 expects).
@@ -708,13 +720,19 @@ static int small_rows_for_wide_tiles() {
     return v;
 }
 
+// A launch of at most one CTA per SM that moves in early (programmatic dependent launch) asks for this much shared
+// memory, more than half an SM's, so that no two of its CTAs share an SM: placed while the previous kernel still holds
+// most SMs, the 48 CTAs of a Wo / W2 product otherwise land three to an SM on the few SMs with room (measured: on 24 SMs)
+// and take 7 us after their wait instead of 3.5 us.
+constexpr int kSoloSmemBytes = 115 * 1024;
+
 // The larger tile configurations need more than 48 KiB of dynamic shared memory: once per device.
 static cudaError_t opt_in_shared_memory(const Ctx *ctx) {
     static bool opted[64] = {};
     if (opted[ctx->device & 63]) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)gemm_tc_smem_bytes<64, 64, 3>());
-    const int sb = (int)gemm_small_smem_bytes<4, 1>(), sb2 = (int)gemm_small_smem_bytes<4, 2>();
+    const int sb = std::max((int)gemm_small_smem_bytes<4, 1>(), kSoloSmemBytes), sb2 = std::max((int)gemm_small_smem_bytes<4, 2>(), kSoloSmemBytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
@@ -935,6 +953,18 @@ static int32_t run_layers_umma(Model *m, int rows, const PagedAppendArgs *paged,
     return JGPT_OK;
 }
 
+#ifdef JGPT_B200_DECODE_TRACE
+static unsigned long long *g_timeline_buf = nullptr;
+static int g_timeline_slot = 0;
+constexpr int kTimelineSlots = 256;
+Timeline timeline_next() {
+    if (!g_timeline_buf && cudaMalloc(&g_timeline_buf, sizeof(unsigned long long) * (4 + 256) * kTimelineSlots) != cudaSuccess) return Timeline{};
+    Timeline T{};
+    T.buf = g_timeline_buf, T.slot = g_timeline_slot < kTimelineSlots ? g_timeline_slot++ : kTimelineSlots - 1;
+    return T;
+}
+#endif
+
 // Decode-sized steps: every projection on gemm_tc_small_kernel with RMSNorm folded into the consumer (the producer
 // of x leaves partial row sums of squares) and SwiGLU into the W1/W3 product: 4 projection launches + attention per
 // layer instead of 7 launches + attention.
@@ -958,7 +988,7 @@ static int32_t pair_interleaved(Model *m, const float *W1, const float *W3, int 
 }
 template <bool NORM, int EPI>
 static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
-                            const float *const *R, const int *rowsel, const SmallFuse &fuse) {
+                            const float *const *R, const int *rowsel, const SmallFuse &fuse_in) {
     JGPT_CUDA_TRY(opt_in_shared_memory(m->ctx));
     GemmBatch B;
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
@@ -966,30 +996,47 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+#ifdef JGPT_B200_DECODE_TRACE
+    SmallFuse fuse = fuse_in;
+    fuse.timeline = timeline_next();
+#else
+    const SmallFuse &fuse = fuse_in;
+#endif
     cfg.blockDim = dim3(256), cfg.stream = m->ctx->stream, cfg.attrs = attr, cfg.numAttrs = (fuse.pdl & 1) ? 1 : 0;
     // 32-row tiles also where the 16-row grid would no longer be resident at once (three CTAs per SM) while the 32-row
     // grid is: a few CTAs left for a second wave cost a whole tile time (W1,W3 from 145 rows on: 160 rows 1.01 ms per step)
     const long long resident = 3ll * m->ctx->sm_count, col_tiles = (long long)((N + 31) / 32) * nb;
     const bool spills = col_tiles * ((M + 15) / 16) > resident && col_tiles * ((M + 31) / 32) <= resident;
-    if (M >= small_rows_for_wide_tiles() || spills) {
-        cfg.gridDim = dim3((N + 31) / 32, (M + 31) / 32, nb), cfg.dynamicSmemBytes = gemm_small_smem_bytes<4, 2>();
+    const bool wide = M >= small_rows_for_wide_tiles() || spills;
+    const bool solo = (fuse.pdl & 1) && col_tiles * ((M + (wide ? 31 : 15)) / (wide ? 32 : 16)) <= m->ctx->sm_count;
+    if (wide) {
+        cfg.gridDim = dim3((N + 31) / 32, (M + 31) / 32, nb);
+        cfg.dynamicSmemBytes = solo ? std::max<size_t>(gemm_small_smem_bytes<4, 2>(), kSoloSmemBytes) : gemm_small_smem_bytes<4, 2>();
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 2>, A, B, M, K, N, rowsel, fuse));
     } else {
-        cfg.gridDim = dim3((N + 31) / 32, (M + 15) / 16, nb), cfg.dynamicSmemBytes = gemm_small_smem_bytes<4, 1>();
+        cfg.gridDim = dim3((N + 31) / 32, (M + 15) / 16, nb);
+        cfg.dynamicSmemBytes = solo ? std::max<size_t>(gemm_small_smem_bytes<4, 1>(), kSoloSmemBytes) : gemm_small_smem_bytes<4, 1>();
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 1>, A, B, M, K, N, rowsel, fuse));
     }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
 }
 
-// How far the launches of a decode step overlap.  Measured on the JGPT-35M shapes (ms per step at batch 1 / 64 / 256):
-// level 0: 0.475 / 0.625 / 1.270; 1: 0.455 / 0.610 / 1.257; 2: 0.447 / 0.653 / 1.295; 3: 0.444 / 0.677 / 1.353 --
-// with a handful of rows every kernel is a latency chain and letting each move in early pays; with full batches the
-// early CTAs only take room from the kernel that is still working.
-static int step_overlap_level(const Model *m, int rows) { return m->step_overlap >= 0 ? m->step_overlap : (rows <= 16 ? 3 : 1); }
+// How far the launches of a decode step overlap (levels: see run_layers_small).  Measured on the JGPT-35M shapes, ms
+// per step at batch 8 / 64 / 256: level 0: 0.45 / 0.59 / 1.26; 1: 0.42 / 0.574 / 1.256; 2: 0.41 / 0.566 / 1.247;
+// 3: 0.375 / 0.535 / 1.21.  Level 3 only pays since early-launched projections of at most one CTA per SM keep an SM
+// to themselves (kSoloSmemBytes) and request their weight tiles before they wait; before that it lost from 24 rows on
+// (batch 64: 0.62 ms) because the early CTAs of Wo and W2 were packed three to an SM.
+static int step_overlap_level(const Model *m, int rows) {
+    (void)rows;
+    return m->step_overlap >= 0 ? m->step_overlap : 3;
+}
 
 template <class AttnFn>
 static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
+#ifdef JGPT_B200_DECODE_TRACE
+    g_timeline_slot = 0;
+#endif
     const int D = m->d_model, F = m->d_ff, parts = (D + 31) / 32;
     for (int l = 0; l < m->layers; l++) {
         const LayerW &y = m->L[(size_t)l];
@@ -1232,6 +1279,33 @@ static int32_t fused_batch_enqueue(Model *m, Pool *p, int n, const int *lens_hos
 
 using namespace jgpt;
 
+#ifdef JGPT_B200_DECODE_TRACE
+// Trace builds only: the step timeline (4 words per launch slot: first CTA in, last wait passed, last CTA out, unused).
+extern "C" __attribute__((visibility("default"))) int32_t jgpt_debug_timeline_reset() {
+    if (!g_timeline_buf) return 0;
+    cudaDeviceSynchronize();
+    std::vector<unsigned long long> init((size_t)4 * kTimelineSlots, 0ull);
+    for (int i = 0; i < kTimelineSlots; i++) init[(size_t)4 * i] = ~0ull;
+    cudaMemcpy(g_timeline_buf, init.data(), sizeof(unsigned long long) * init.size(), cudaMemcpyHostToDevice);
+    cudaMemset(g_timeline_buf + 4 * kTimelineSlots, 0, sizeof(unsigned long long) * 256 * kTimelineSlots);
+    return g_timeline_slot;
+}
+extern "C" __attribute__((visibility("default"))) int32_t jgpt_debug_timeline_read(unsigned long long *host, int32_t slots) {
+    if (!g_timeline_buf) return 0;
+    cudaDeviceSynchronize();
+    const int n = std::min(slots, kTimelineSlots);
+    cudaMemcpy(host, g_timeline_buf, sizeof(unsigned long long) * 4 * (size_t)n, cudaMemcpyDeviceToHost);
+    return g_timeline_slot;
+}
+extern "C" __attribute__((visibility("default"))) int32_t jgpt_debug_timeline_read_sms(unsigned long long *host, int32_t slots) {
+    if (!g_timeline_buf) return 0;
+    cudaDeviceSynchronize();
+    const int n = std::min(slots, kTimelineSlots);
+    cudaMemcpy(host, g_timeline_buf + 4 * kTimelineSlots, sizeof(unsigned long long) * 256 * (size_t)n, cudaMemcpyDeviceToHost);
+    return g_timeline_slot;
+}
+#endif
+
 #define GET_MODEL(m, h)                                         \
     Model *m = model_registry().get(h);                         \
     JGPT_REQUIRE(m, JGPT_ERR_BAD_HANDLE, "bad model handle");   \
@@ -1302,7 +1376,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
-    m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = by batch size
+    m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = the default level
     m->fused_step = env_int("JGPT_B200_FUSED_STEP", 1);
     m->fused_batch = env_int("JGPT_B200_FUSED_BATCH", 0);  // measured slower than the multi-launch step so far: opt-in
     const size_t D = d_model, F = d_ff, V = vocab, R = max_rows;
