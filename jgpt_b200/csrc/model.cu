@@ -606,9 +606,16 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     const float *row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int j = threadIdx.x; j < V; j += blockDim.x) {
-        const float v = row[j];
-        if (v > best || (v == best && j < idx)) best = v, idx = j;
+    // eight loads in flight per thread: one load per iteration made the row a chain of V / 256 L2 round trips
+    for (int j0 = threadIdx.x; j0 < V; j0 += 8 * 256) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = j0 + 256 * u < V ? row[j0 + 256 * u] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int j = j0 + 256 * u;
+            if (j < V && (v[u] > best || (v[u] == best && j < idx))) best = v[u], idx = j;
+        }
     }
     if (idx == 0x7fffffff) idx = 0;  // all NaN / -inf: the reference starts from index 0
 #pragma unroll
