@@ -584,6 +584,8 @@ def run_secondary(args, rank, world, local_rank):
         pool.close()
     elif args.workload == "fusedphases":
         line.update(W.run_fused_phases(ctx))
+    elif args.workload == "steptimeline":
+        line.update(W.run_step_timeline(ctx, batch=args.batch))
     elif args.workload == "contbatch":
         uid = None
         if world > 1:
@@ -627,7 +629,7 @@ def main():
     ap.add_argument("--launch-overlap", type=int, default=2, help="with --quick --per-layer: 0 ordinary launches, 1 / 2 overlapped")
     ap.add_argument("--batch", type=int, default=64, help="sequences per step for --workload decodestep")
     ap.add_argument("--gather-depth", type=int, default=4, help="continuous batching: steps a rank may run ahead of the token-id gather")
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore", "phases", "fusedphases"],
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "decode35m", "decodestep", "prefill", "contbatch", "longctx", "kvstore", "phases", "fusedphases", "steptimeline"],
                     help="microbench (default) is the headline KV-append + decode-attention step; the others are the "
                          "remaining named configurations (reported, not the contract line)")
     args = ap.parse_args()

@@ -444,6 +444,69 @@ def run_fused_phases(ctx, prompt_len=900, new_tokens=33):
     return out
 
 
+def run_step_timeline(ctx, batch=64, ctx_len=512):
+    """When each launch of one multi-launch decode step runs: needs the library built by ``python -m jgpt_b200.build
+    --trace`` (loaded through JGPT_B200_LIB).  Every projection and attention kernel of that build records, on the global
+    timer, when its first CTA came in, when its last CTA was past the wait for the previous kernel and when its last CTA
+    left, and which SM each of its first 256 CTAs ran on.  Reported per kind of launch (medians over layers 1..):
+    ``early_us`` = how long before the previous kernel's end the first CTA came in (negative: a gap), ``busy_us`` = from
+    the later of (own start, previous kernel's end) to the own end, and how the CTAs were spread over the SMs."""
+    import ctypes as C
+
+    lib = ctx._lib
+    if not hasattr(lib, "jgpt_debug_timeline_read"):
+        raise RuntimeError("this library was not built with --trace (python -m jgpt_b200.build --trace; JGPT_B200_LIB=...)")
+    model = make_model(ctx, max_rows=8192)
+    pool = model.newPool(n_blocks=batch * (-(-(ctx_len + 64) // 16)), max_seqs=batch)
+    rng = np.random.default_rng(0)
+    seqs = [pool.seq_alloc() for _ in range(batch)]
+    prompts = [rng.integers(0, VOCAB, ctx_len).astype(np.int32) for _ in range(batch)]
+    per_call = max(1, 8192 // ctx_len)
+    try:
+        toks = np.zeros(batch, np.int32)
+        for i in range(0, batch, per_call):
+            _, toks[i:i + per_call] = model.forwardPrefillBatch(pool, seqs[i:i + per_call], prompts[i:i + per_call])
+        lens = np.full(batch, ctx_len, np.int32)
+        for _ in range(10):
+            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            lens += 1
+        ctx.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(20):
+            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            lens += 1
+        ms = (time.perf_counter() - t0) / 20 * 1e3
+        lib.jgpt_debug_timeline_reset()
+        model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+        buf = np.zeros((256, 4), np.uint64)
+        n = int(lib.jgpt_debug_timeline_read(buf.ctypes.data_as(C.c_void_p), 256))
+        sms = np.zeros((256, 256), np.uint64)
+        lib.jgpt_debug_timeline_read_sms(sms.ctypes.data_as(C.c_void_p), 256)
+    finally:
+        pool.close(), model.close()
+    t = buf[:n].astype(np.int64)
+    kinds = ["Q,K,V", "attention", "Wo", "W1/W3", "W2"]
+    n_layer_launches = n - 1  # the last one is the LM head
+    rows = {}
+    for i in range(n):
+        kind = kinds[i % 5] if i < n_layer_launches else "LM head"
+        start, end = t[i, 0], t[i, 2]
+        prev_end = t[i - 1, 2] if i else start
+        ids = sms[i][sms[i] > 0].astype(np.int64) - 1
+        per_sm = np.bincount(ids, minlength=1)
+        if i >= 5 or kind == "LM head":
+            rows.setdefault(kind, []).append(((prev_end - start) / 1e3, (end - max(prev_end, start)) / 1e3, int(ids.size),
+                                              int(np.sum(per_sm > 0)), int(per_sm.max()) if ids.size else 0))
+    out = {"workload": f"timeline of one multi-launch decode step, JGPT-35M, batch {batch}, context {ctx_len}+ (trace build)",
+           "ms_per_step_trace_build": ms, "launches_recorded": n,
+           "first_start_to_last_end_us": float((t[n - 1, 2] - t[0, 0]) / 1e3), "per_launch_kind": {}}
+    for kind, v in rows.items():
+        a = np.asarray(v, np.float64)
+        out["per_launch_kind"][kind] = {"launches": len(v), "early_us_median": float(np.median(a[:, 0])), "busy_us_median": float(np.median(a[:, 1])),
+                                        "ctas_recorded": int(a[-1, 2]), "sms_used": int(a[-1, 3]), "max_ctas_on_one_sm": int(a[-1, 4])}
+    return out
+
+
 def run_longctx(ctx, rank, world, n_seqs_total=512, steps=20, warmup=3):
     """Decode attention + append at long context: 512 sequences (seed 3) with lengths U[1024, 8192], RoPE positions
     to 8192, dealt in contiguous shards to the ranks; one fused 12-layer launch per step."""
