@@ -65,6 +65,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
+    int w_resident = 1;  // projections of the decode step keep their CTA's weight slice in shared memory when the grid allows (JGPT_B200_W_RESIDENT=0: off)
     int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = the default, 3)
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
     // Steps of up to four rows as one cooperative launch (decode_fused.cu; JGPT_B200_FUSED_STEP=0: off).  Sized on first use.
@@ -383,6 +384,9 @@ struct SmallFuse {
     // previous kernel on the stream finished: wait for that kernel before touching memory.  bit 1: let the NEXT
     // launch on the stream move in early (it waits for this kernel itself before it reads this kernel's output).
     int pdl = 0;
+    // 1: the launch's shared memory holds this CTA's whole weight slice (every k tile its own stage, none reused):
+    // all of it is requested at the top of the kernel -- one trip to memory instead of one per STAGES - 1 tiles.
+    int w_resident = 0;
 #ifdef JGPT_B200_DECODE_TRACE
     Timeline timeline;
 #endif
@@ -422,13 +426,16 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         cp_async16(&Ws[buf][w_k + 32][w_c], k2 ? w_src + (size_t)(k0 + 32) * N : W, k2);
     };
     const int nk = (K + BK - 1) / BK;
-    const bool early_w = (F.pdl & 1) != 0;
-    if (early_w) {
+    const bool w_resident = F.w_resident != 0;
+    const bool early_w = (F.pdl & 1) != 0 || w_resident;
+    if (w_resident) {
+        for (int kt = 0; kt < nk; kt++) load_w(kt, kt * BK);
+    } else if (early_w) {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; s++)
             if (s < nk) load_w(s, s * BK);
-        griddep_wait();
     }
+    if (F.pdl & 1) griddep_wait();
 #ifdef JGPT_B200_DECODE_TRACE
     timeline_at(F.timeline, 1);
 #endif
@@ -452,7 +459,7 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     };
     auto load_tiles = [&](int buf, int k0) {
         load_a(buf, k0);
-        load_w(buf, k0);
+        if (!w_resident) load_w(buf, k0);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
@@ -495,7 +502,7 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     }
     const int ks = warp * 8;
     for (int kt = 0; kt < nk; kt++) {
-        const int buf = kt % STAGES;
+        const int buf = kt % STAGES, wbuf = w_resident ? kt : buf;
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
         __syncthreads();  // tile kt (and s_inv) visible to all; everyone is done with the buffer refilled below (read at kt-1)
         if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
@@ -524,8 +531,8 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         for (int j = 0; j < 4; j++) {
             const int c = j * 8 + g;
             uint32_t bh0, bl0, bh1, bl1;
-            split_tf32(Ws[buf][ks + t][c], bh0, bl0);
-            split_tf32(Ws[buf][ks + t + 4][c], bh1, bl1);
+            split_tf32(Ws[wbuf][ks + t][c], bh0, bl0);
+            split_tf32(Ws[wbuf][ks + t + 4][c], bh1, bl1);
 #pragma unroll
             for (int i = 0; i < MT; i++) {
                 mma_tf32(cor[i][j], al[i], bh0, bh1);
@@ -732,6 +739,8 @@ static int small_rows_for_wide_tiles() {
 // most SMs, the 48 CTAs of a Wo / W2 product otherwise land three to an SM on the few SMs with room (measured: on 24 SMs)
 // and take 7 us after their wait instead of 3.5 us.
 constexpr int kSoloSmemBytes = 115 * 1024;
+constexpr int kSmallMaxSmemBytes = 219 * 1024;  // dynamic shared memory limit asked for the projection kernels: 227 KiB per CTA less their static arrays
+constexpr size_t kSmemPerSm = 228 * 1024;       // of which 1 KiB per resident CTA is the system's
 
 // The larger tile configurations need more than 48 KiB of dynamic shared memory: once per device.
 static cudaError_t opt_in_shared_memory(const Ctx *ctx) {
@@ -739,7 +748,7 @@ static cudaError_t opt_in_shared_memory(const Ctx *ctx) {
     if (opted[ctx->device & 63]) return cudaSuccess;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<64, 64, 2, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)gemm_tc_smem_bytes<64, 64, 3>());
-    const int sb = std::max((int)gemm_small_smem_bytes<4, 1>(), kSoloSmemBytes), sb2 = std::max((int)gemm_small_smem_bytes<4, 2>(), kSoloSmemBytes);
+    const int sb = kSmallMaxSmemBytes, sb2 = kSmallMaxSmemBytes;  // ring, solo padding or the whole weight slice (small_launch)
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, false, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_small_kernel<4, true, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb);
@@ -1003,11 +1012,9 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-#ifdef JGPT_B200_DECODE_TRACE
     SmallFuse fuse = fuse_in;
+#ifdef JGPT_B200_DECODE_TRACE
     fuse.timeline = timeline_next();
-#else
-    const SmallFuse &fuse = fuse_in;
 #endif
     cfg.blockDim = dim3(256), cfg.stream = m->ctx->stream, cfg.attrs = attr, cfg.numAttrs = (fuse.pdl & 1) ? 1 : 0;
     // 32-row tiles also where the 16-row grid would no longer be resident at once (three CTAs per SM) while the 32-row
@@ -1016,13 +1023,24 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     const bool spills = col_tiles * ((M + 15) / 16) > resident && col_tiles * ((M + 31) / 32) <= resident;
     const bool wide = M >= small_rows_for_wide_tiles() || spills;
     const bool solo = (fuse.pdl & 1) && col_tiles * ((M + (wide ? 31 : 15)) / (wide ? 32 : 16)) <= m->ctx->sm_count;
+    // The CTA's whole weight slice in shared memory (SmallFuse::w_resident) where the launch is still resident at once
+    // with that much shared memory per CTA.  The step's weights do not stay in L2 from one step to the next, so a
+    // ring of four k tiles pays a trip to HBM per three tiles (W2, K = 768: 0.43 us per tile); with the slice
+    // requested at the top - before the wait for the previous kernel - it is one trip, hidden when the launch moved in early.
+    const int bm = wide ? 32 : 16;
+    const long long ctas = col_tiles * ((M + bm - 1) / bm);
+    const size_t ring = wide ? gemm_small_smem_bytes<4, 2>() : gemm_small_smem_bytes<4, 1>();
+    const size_t slice = sizeof(float) * (4 * (size_t)bm * (kSmallBK + 4) + (size_t)((K + kSmallBK - 1) / kSmallBK) * kSmallBK * (32 + 8));
+    const long long by_regs = wide ? 2 : 3;  // 128 / 80 registers per thread
+    const long long per_sm = std::min<long long>(by_regs, (long long)(kSmemPerSm / (slice + 1024)));
+    if (m->w_resident && slice <= kSmallMaxSmemBytes && per_sm >= 1 && ctas <= per_sm * m->ctx->sm_count) fuse.w_resident = 1;
+    cfg.dynamicSmemBytes = fuse.w_resident ? std::max(slice, ring) : ring;
+    if (solo) cfg.dynamicSmemBytes = std::max<size_t>(cfg.dynamicSmemBytes, kSoloSmemBytes);
     if (wide) {
         cfg.gridDim = dim3((N + 31) / 32, (M + 31) / 32, nb);
-        cfg.dynamicSmemBytes = solo ? std::max<size_t>(gemm_small_smem_bytes<4, 2>(), kSoloSmemBytes) : gemm_small_smem_bytes<4, 2>();
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 2>, A, B, M, K, N, rowsel, fuse));
     } else {
         cfg.gridDim = dim3((N + 31) / 32, (M + 15) / 16, nb);
-        cfg.dynamicSmemBytes = solo ? std::max<size_t>(gemm_small_smem_bytes<4, 1>(), kSoloSmemBytes) : gemm_small_smem_bytes<4, 1>();
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 1>, A, B, M, K, N, rowsel, fuse));
     }
     JGPT_CUDA_TRY(cudaGetLastError());
@@ -1383,6 +1401,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->umma_min_rows = env_int("JGPT_B200_UMMA_MIN_ROWS", 513);
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
+    m->w_resident = env_int("JGPT_B200_W_RESIDENT", 1);
     m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = the default level
     m->fused_step = env_int("JGPT_B200_FUSED_STEP", 1);
     m->fused_batch = env_int("JGPT_B200_FUSED_BATCH", 0);  // measured slower than the multi-launch step so far: opt-in
