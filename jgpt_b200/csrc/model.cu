@@ -543,6 +543,9 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();  // the stage buffers are dead: reuse them for the eight partial tiles
+#ifdef JGPT_B200_DECODE_TRACE
+    timeline_at(F.timeline, 3);
+#endif
     float (*red)[BM][BN + 1] = reinterpret_cast<float (*)[BM][BN + 1]>(gemm_smem);
 #pragma unroll
     for (int i = 0; i < MT; i++)

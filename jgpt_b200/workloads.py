@@ -450,7 +450,8 @@ def run_step_timeline(ctx, batch=64, ctx_len=512):
     timer, when its first CTA came in, when its last CTA was past the wait for the previous kernel and when its last CTA
     left, and which SM each of its first 256 CTAs ran on.  Reported per kind of launch (medians over layers 1..):
     ``early_us`` = how long before the previous kernel's end the first CTA came in (negative: a gap), ``busy_us`` = from
-    the later of (own start, previous kernel's end) to the own end, and how the CTAs were spread over the SMs."""
+    the later of (own start, previous kernel's end) to the own end, how the CTAs were spread over the SMs, and for the
+    projections the split of their time at the end of the k loop (last CTA)."""
     import ctypes as C
 
     lib = ctx._lib
@@ -496,14 +497,17 @@ def run_step_timeline(ctx, batch=64, ctx_len=512):
         per_sm = np.bincount(ids, minlength=1)
         if i >= 5 or kind == "LM head":
             rows.setdefault(kind, []).append(((prev_end - start) / 1e3, (end - max(prev_end, start)) / 1e3, int(ids.size),
-                                              int(np.sum(per_sm > 0)), int(per_sm.max()) if ids.size else 0))
+                                              int(np.sum(per_sm > 0)), int(per_sm.max()) if ids.size else 0,
+                                              (t[i, 1] - prev_end) / 1e3, (t[i, 3] - t[i, 1]) / 1e3 if t[i, 3] else 0.0, (end - t[i, 3]) / 1e3 if t[i, 3] else 0.0))
     out = {"workload": f"timeline of one multi-launch decode step, JGPT-35M, batch {batch}, context {ctx_len}+ (trace build)",
            "ms_per_step_trace_build": ms, "launches_recorded": n,
            "first_start_to_last_end_us": float((t[n - 1, 2] - t[0, 0]) / 1e3), "per_launch_kind": {}}
     for kind, v in rows.items():
         a = np.asarray(v, np.float64)
         out["per_launch_kind"][kind] = {"launches": len(v), "early_us_median": float(np.median(a[:, 0])), "busy_us_median": float(np.median(a[:, 1])),
-                                        "ctas_recorded": int(a[-1, 2]), "sms_used": int(a[-1, 3]), "max_ctas_on_one_sm": int(a[-1, 4])}
+                                        "ctas_recorded": int(a[-1, 2]), "sms_used": int(a[-1, 3]), "max_ctas_on_one_sm": int(a[-1, 4]),
+                                        "wait_passed_after_prev_end_us": float(np.median(a[:, 5])), "wait_to_k_loop_end_us": float(np.median(a[:, 6])),
+                                        "k_loop_end_to_end_us": float(np.median(a[:, 7]))}
     return out
 
 
