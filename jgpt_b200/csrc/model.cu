@@ -65,6 +65,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
+    int k_split = 1;  // Wo / W2 of a step with few rows as pairs of CTAs that split the k range (JGPT_B200_K_SPLIT=0: off)
     int w_resident = 1;  // projections of the decode step keep their CTA's weight slice in shared memory when the grid allows (JGPT_B200_W_RESIDENT=0: off)
     int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = the default, 3)
     int prefill_fast = 1;  // single-fp16 q / p operands in the d_head-16 prefill attention (JGPT_B200_PREFILL_EXACT=1: off)
@@ -387,6 +388,10 @@ struct SmallFuse {
     // 1: the launch's shared memory holds this CTA's whole weight slice (every k tile its own stage, none reused):
     // all of it is requested at the top of the kernel -- one trip to memory instead of one per STAGES - 1 tiles.
     int w_resident = 0;
+    // 2 (EPI 1 only): the launch is made of clusters of two CTAs along x that share one output tile; each runs half of the
+    // k tiles, the second hands its sums to the first through shared memory, the first adds them to its own (k halves in
+    // order), then the residual, and stores.  For the Wo / W2 products of a step with few rows: 48 CTAs on 148 SMs otherwise.
+    int k_split = 1;
 #ifdef JGPT_B200_DECODE_TRACE
     Timeline timeline;
 #endif
@@ -404,7 +409,9 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     const int z = blockIdx.z;  // selects below: indexing B would copy it to local memory
     const float *__restrict__ W = z == 0 ? B.W[0] : (z == 1 ? B.W[1] : B.W[2]);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_split = (EPI == 1 && F.k_split == 2) ? 2 : 1;
+    const int k_part = k_split == 2 ? (int)(blockIdx.x & 1) : 0, col_tile = k_split == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = col_tile * BN;
     // norm weights into shared memory up front (weights: no need to wait for the previous kernel): read from global
     // inside the k loop they put an L2 round trip into every one of its iterations
     constexpr int kGammaSmem = 1024;
@@ -425,15 +432,17 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         cp_async16(&Ws[buf][w_k][w_c], k1 ? w_src + (size_t)k0 * N : W, k1);
         cp_async16(&Ws[buf][w_k + 32][w_c], k2 ? w_src + (size_t)(k0 + 32) * N : W, k2);
     };
-    const int nk = (K + BK - 1) / BK;
+    const int nk_all = (K + BK - 1) / BK;
+    const int kt_first = k_part * nk_all / k_split, nk = (k_part + 1) * nk_all / k_split - kt_first;  // this CTA's k tiles
+    const int kbase = kt_first * BK;
     const bool w_resident = F.w_resident != 0;
     const bool early_w = (F.pdl & 1) != 0 || w_resident;
     if (w_resident) {
-        for (int kt = 0; kt < nk; kt++) load_w(kt, kt * BK);
+        for (int kt = 0; kt < nk; kt++) load_w(kt, kbase + kt * BK);
     } else if (early_w) {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; s++)
-            if (s < nk) load_w(s, s * BK);
+            if (s < nk) load_w(s, kbase + s * BK);
     }
     if (F.pdl & 1) griddep_wait();
 #ifdef JGPT_B200_DECODE_TRACE
@@ -474,8 +483,8 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (s < nk) {
-            load_a(s, s * BK);
-            if (!early_w) load_w(s, s * BK);
+            load_a(s, kbase + s * BK);
+            if (!early_w) load_w(s, kbase + s * BK);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -485,9 +494,10 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
 #pragma unroll
     for (int i = 0; i < 2 * MT; i++) {
         const int e = tid + 256 * i, m = m0 + (e >> 5), n = n0 + (e & 31);
-        rpre[i] = (EPI != 2 && Rz && m < M && n < N) ? Rz[(size_t)m * N + n] : 0.f;
+        rpre[i] = (EPI != 2 && Rz && k_part == 0 && m < M && n < N) ? Rz[(size_t)m * N + n] : 0.f;
     }
     __shared__ float s_inv[BM];
+    __shared__ float s_xch[EPI == 1 ? BM * BN : 1];  // k_split: the partner CTA's sums land here (never part of the tile ring)
     if (NORM && tid < BM) {
         const int m = m0 + tid;
         float inv = 0.f;
@@ -505,12 +515,12 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         const int buf = kt % STAGES, wbuf = w_resident ? kt : buf;
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
         __syncthreads();  // tile kt (and s_inv) visible to all; everyone is done with the buffer refilled below (read at kt-1)
-        if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, (kt + STAGES - 1) * BK);
+        if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, kbase + (kt + STAGES - 1) * BK);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         uint32_t ah[MT][4], al[MT][4];
         float g0 = 0.f, g1 = 0.f;
         if (NORM) {
-            const int k = kt * BK + ks + t;
+            const int k = kbase + kt * BK + ks + t;
             if (gamma_staged) g0 = k < K ? s_gamma[k] : 0.f, g1 = k + 4 < K ? s_gamma[k + 4] : 0.f;
             else g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
         }
@@ -561,7 +571,7 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     float *C = z == 0 ? B.C[0] : (z == 1 ? B.C[1] : B.C[2]);
     const float *R = z == 0 ? B.R[0] : (z == 1 ? B.R[1] : B.R[2]);
     for (int e = tid; EPI == 2 && e < BM * 16; e += 256) {
-        const int r = e >> 4, c = e & 15, m = m0 + r, n = blockIdx.x * 16 + c, Fo = N / 2;
+        const int r = e >> 4, c = e & 15, m = m0 + r, n = col_tile * 16 + c, Fo = N / 2;
         if (m < M && n < Fo) {
             float h = red[0][r][c], gv = red[0][r][16 + c];
 #pragma unroll
@@ -573,15 +583,39 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             C[(size_t)m * Fo + n] = h * (gv * sg);
         }
     }
+    float vsum[2 * MT];
 #pragma unroll
     for (int i = 0; EPI != 2 && i < 2 * MT; i++) {  // one warp = one row of the tile per iteration
+        const int e = tid + 256 * i, r = e >> 5, c = e & 31;
+        float v = red[0][r][c];
+#pragma unroll
+        for (int w = 1; w < 8; w++) v += red[w][r][c];
+        vsum[i] = v;
+    }
+    if (EPI == 1 && k_split == 2) {
+        // the second CTA of the pair puts its sums into the first one's shared memory (behind the partial tiles) and is done
+        float *xch = s_xch;
+        if (k_part == 1) {
+#pragma unroll
+            for (int i = 0; i < 2 * MT; i++) st_cluster_f32(xch + tid + 256 * i, 0u, vsum[i]);
+        }
+        cluster_sync();
+        if (k_part == 1) {
+#ifdef JGPT_B200_DECODE_TRACE
+            timeline_at(F.timeline, 2);
+#endif
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * MT; i++) vsum[i] += xch[tid + 256 * i];
+    }
+#pragma unroll
+    for (int i = 0; EPI != 2 && i < 2 * MT; i++) {
         const int e = tid + 256 * i, r = e >> 5, c = e & 31, m = m0 + r, n = n0 + c;
         const bool ok = m < M && n < N;
         float v = 0.f;
         if (ok) {
-            v = red[0][r][c];
-#pragma unroll
-            for (int w = 1; w < 8; w++) v += red[w][r][c];
+            v = vsum[i];
             if (R) v += rpre[i];
             C[(size_t)m * N + n] = v;
         }
@@ -589,7 +623,7 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             float sq = v * v;
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-            if (lane == 0 && m < M) F.ss_out[(size_t)m * gridDim.x + blockIdx.x] = sq;
+            if (lane == 0 && m < M) F.ss_out[(size_t)m * (gridDim.x / k_split) + col_tile] = sq;
         }
     }
 #ifdef JGPT_B200_DECODE_TRACE
@@ -1012,38 +1046,53 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     GemmBatch B;
     for (int z = 0; z < 3; z++) B.W[z] = z < nb ? W[z] : nullptr, B.C[z] = z < nb ? C[z] : nullptr, B.R[z] = (z < nb && R) ? R[z] : nullptr;
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
     SmallFuse fuse = fuse_in;
+    if (fuse.pdl & 1) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
 #ifdef JGPT_B200_DECODE_TRACE
     fuse.timeline = timeline_next();
 #endif
-    cfg.blockDim = dim3(256), cfg.stream = m->ctx->stream, cfg.attrs = attr, cfg.numAttrs = (fuse.pdl & 1) ? 1 : 0;
+    cfg.blockDim = dim3(256), cfg.stream = m->ctx->stream;
     // 32-row tiles also where the 16-row grid would no longer be resident at once (three CTAs per SM) while the 32-row
     // grid is: a few CTAs left for a second wave cost a whole tile time (W1,W3 from 145 rows on: 160 rows 1.01 ms per step)
     const long long resident = 3ll * m->ctx->sm_count, col_tiles = (long long)((N + 31) / 32) * nb;
     const bool spills = col_tiles * ((M + 15) / 16) > resident && col_tiles * ((M + 31) / 32) <= resident;
     const bool wide = M >= small_rows_for_wide_tiles() || spills;
-    const bool solo = (fuse.pdl & 1) && col_tiles * ((M + (wide ? 31 : 15)) / (wide ? 32 : 16)) <= m->ctx->sm_count;
+    // Wo / W2 of a step with few rows: pairs of CTAs split the k range (SmallFuse::k_split) while the launch still has at
+    // most one CTA per SM.
+    if (EPI == 1 && m->k_split && !rowsel && (K + kSmallBK - 1) / kSmallBK >= 4 &&
+        2 * col_tiles * ((M + (wide ? 31 : 15)) / (wide ? 32 : 16)) <= m->ctx->sm_count) {
+        fuse.k_split = 2;
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 2, attr[n_attr].val.clusterDim.y = 1, attr[n_attr].val.clusterDim.z = 1;
+        n_attr++;
+    }
+    cfg.attrs = attr, cfg.numAttrs = n_attr;
+    const bool solo = (fuse.pdl & 1) && fuse.k_split * col_tiles * ((M + (wide ? 31 : 15)) / (wide ? 32 : 16)) <= m->ctx->sm_count;
     // The CTA's whole weight slice in shared memory (SmallFuse::w_resident) where the launch is still resident at once
     // with that much shared memory per CTA.  The step's weights do not stay in L2 from one step to the next, so a
     // ring of four k tiles pays a trip to HBM per three tiles (W2, K = 768: 0.43 us per tile); with the slice
     // requested at the top - before the wait for the previous kernel - it is one trip, hidden when the launch moved in early.
     const int bm = wide ? 32 : 16;
-    const long long ctas = col_tiles * ((M + bm - 1) / bm);
+    const long long ctas = fuse.k_split * col_tiles * ((M + bm - 1) / bm);
     const size_t ring = wide ? gemm_small_smem_bytes<4, 2>() : gemm_small_smem_bytes<4, 1>();
-    const size_t slice = sizeof(float) * (4 * (size_t)bm * (kSmallBK + 4) + (size_t)((K + kSmallBK - 1) / kSmallBK) * kSmallBK * (32 + 8));
+    const size_t k_tiles = ((size_t)(K + kSmallBK - 1) / kSmallBK + fuse.k_split - 1) / fuse.k_split;  // of the CTA with the most
+    const size_t slice = sizeof(float) * (4 * (size_t)bm * (kSmallBK + 4) + k_tiles * kSmallBK * (32 + 8));
     const long long by_regs = wide ? 2 : 3;  // 128 / 80 registers per thread
     const long long per_sm = std::min<long long>(by_regs, (long long)(kSmemPerSm / (slice + 1024)));
     if (m->w_resident && slice <= kSmallMaxSmemBytes && per_sm >= 1 && ctas <= per_sm * m->ctx->sm_count) fuse.w_resident = 1;
     cfg.dynamicSmemBytes = fuse.w_resident ? std::max(slice, ring) : ring;
     if (solo) cfg.dynamicSmemBytes = std::max<size_t>(cfg.dynamicSmemBytes, kSoloSmemBytes);
     if (wide) {
-        cfg.gridDim = dim3((N + 31) / 32, (M + 31) / 32, nb);
+        cfg.gridDim = dim3(fuse.k_split * ((N + 31) / 32), (M + 31) / 32, nb);
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 2>, A, B, M, K, N, rowsel, fuse));
     } else {
-        cfg.gridDim = dim3((N + 31) / 32, (M + 15) / 16, nb);
+        cfg.gridDim = dim3(fuse.k_split * ((N + 31) / 32), (M + 15) / 16, nb);
         JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tc_small_kernel<4, NORM, EPI, 1>, A, B, M, K, N, rowsel, fuse));
     }
     JGPT_CUDA_TRY(cudaGetLastError());
@@ -1405,6 +1454,7 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     m->decode_graph_enabled = env_int("JGPT_B200_DECODE_GRAPH", 1);
     m->prefill_fast = env_int("JGPT_B200_PREFILL_EXACT", 0) ? 0 : 1;
     m->w_resident = env_int("JGPT_B200_W_RESIDENT", 1);
+    m->k_split = env_int("JGPT_B200_K_SPLIT", 1);
     m->step_overlap = std::min(3, std::max(-1, env_int("JGPT_B200_STEP_OVERLAP", -1)));  // -1 = the default level
     m->fused_step = env_int("JGPT_B200_FUSED_STEP", 1);
     m->fused_batch = env_int("JGPT_B200_FUSED_BATCH", 0);  // measured slower than the multi-launch step so far: opt-in

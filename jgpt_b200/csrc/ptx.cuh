@@ -73,6 +73,13 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Writes a float to the same shared-memory offset in the CTA of rank `rank` of this cluster (visible there after the
+// next cluster barrier).
+__device__ __forceinline__ void st_cluster_f32(float *local_smem, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 // Reads a float at the same shared-memory offset in the CTA of rank `rank` of this cluster.
 __device__ __forceinline__ float ld_cluster_f32(const float *local_smem, uint32_t rank) {
     uint32_t remote;
