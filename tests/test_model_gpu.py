@@ -509,3 +509,50 @@ def test_overlapped_launches_inside_the_decode_step_change_nothing(ctx, level, m
     for (l0, t0), (l1, t1) in zip(r0, r1):
         assert np.array_equal(l0, l1) and np.array_equal(t0, t1)
     assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
+
+
+def test_resident_weight_slices_and_split_k_pairs(ctx, monkeypatch):
+    """Two launch forms of the decode step's projections.  JGPT_B200_W_RESIDENT: a CTA keeps its whole weight slice in
+    shared memory instead of a ring of four k tiles - the arithmetic is the same, so logits, ids and the cache payload are
+    bit-identical.  JGPT_B200_K_SPLIT: Wo / W2 as pairs of CTAs that each run half of the k tiles - the two halves are
+    added last instead of warp by warp, so logits agree to rounding (1e-4 of the largest logit on the first step), not bit for bit.  d_model 256 / d_ff 512
+    give those products 4 and 8 k tiles (pairs need at least 4)."""
+    om = O.Model(96, 80, 256, 16, 2, 512, eps=1e-5).init_random(seed=9, std=0.05)
+    outs = {}
+    monkeypatch.setenv("JGPT_B200_FUSED_BATCH", "0")
+    for resident, split in ((0, 0), (1, 0), (1, 1), (0, 1)):
+        monkeypatch.setenv("JGPT_B200_W_RESIDENT", str(resident))
+        monkeypatch.setenv("JGPT_B200_K_SPLIT", str(split))
+        gm = GPTModel(ctx, 96, 80, 256, 16, 2, 512, rmsNormEps=1e-5, maxRows=256)
+        gm.setParameters(om.tensors())
+        pool = gm.newPool(n_blocks=6 * 5, max_seqs=6)
+        try:  # six rows: the multi-launch step
+            seqs = [pool.seq_alloc() for _ in range(6)]
+            plens = (33, 5, 16, 40, 1, 27)
+            prompts = [np.array([(i * 7 + s) % 96 for i in range(n)], np.int32) for s, n in enumerate(plens)]
+            _, toks = gm.forwardPrefillBatch(pool, seqs, prompts)
+            lens = np.array(plens, np.int32)
+            rec = []
+            for step in range(5):  # eager, capture, replays
+                logits, nxt = gm.forwardDecodeBatch(pool, seqs, toks, lens, lens)
+                lens = lens + 1
+                rec.append(logits.copy())
+                toks = np.array([(3 * step + s) % 96 for s in range(6)], np.int32)  # fixed ids: the runs stay comparable
+            kd, vd = ctx.alloc((16, 80, 16)), ctx.alloc((16, 80, 16))
+            pool.gather(1, seqs[0], int(lens[0]), 80, kd, vd)
+            outs[(resident, split)] = (rec, kd.to_host(), vd.to_host())
+        finally:
+            pool.close(), gm.close()
+    om.close()
+    for split in (0, 1):
+        (ra, ka, va), (rb, kb, vb) = outs[(0, split)], outs[(1, split)]
+        for la, lb in zip(ra, rb):
+            assert np.array_equal(la, lb)
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+    (r0, k0, v0), (r1, k1, v1) = outs[(1, 0)], outs[(1, 1)]
+    assert any(not np.array_equal(a, b) for a, b in zip(r0, r1)), "the pairs did not run: same bits as one CTA per tile"
+    for step, (a, b) in enumerate(zip(r0, r1)):
+        # step 0 sees the same cache; later a payload value that rounded to the other fp16 neighbour moves logits by more
+        np.testing.assert_allclose(a, b, rtol=0, atol=(1e-4 if step == 0 else 2e-3) * max(1.0, float(np.abs(a).max())))
+    np.testing.assert_allclose(k0, k1, rtol=0, atol=1e-3)  # fp16 payload: a last-bit difference of a value near 1
+    np.testing.assert_allclose(v0, v1, rtol=0, atol=1e-3)
