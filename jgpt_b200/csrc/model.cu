@@ -504,7 +504,16 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         if (m < M) {
             const float *pp = F.ss_in + (size_t)(rowsel ? rowsel[m] : m) * F.parts_in;
             float tot = 0.f;
-            for (int i = 0; i < F.parts_in; i++) tot += pp[i];
+            if (F.parts_in <= 16) {  // all partials requested before the first is added (same order of additions)
+                float pv[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) pv[i] = i < F.parts_in ? pp[i] : 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if (i < F.parts_in) tot += pv[i];
+            } else {
+                for (int i = 0; i < F.parts_in; i++) tot += pp[i];
+            }
             const float rms = sqrtf(tot / (float)K + F.eps);
             inv = (rms > 0.f && isfinite(rms)) ? (1.f / rms) : 0.f;
         }
