@@ -47,6 +47,7 @@ struct Model {
     // Decode-sized steps (rows <= 512): RMSNorm and SwiGLU live inside the projections.
     float *ss_a = nullptr, *ss_b = nullptr;           // [max_rows][ceil(d_model / 32)] partial row sums of squares of x
     std::unordered_map<const float *, float *> w13i;  // interleaved W1/W3 pairs by W1's pointer; dropped when weights change
+    std::unordered_map<const float *, float *> wscaled;  // weights with row k scaled by the preceding norm's gamma[k] (decode-sized steps), by the weights' pointer
     // Decode steps replayed as CUDA graphs (JGPT_B200_DECODE_GRAPH=0 turns it off).  A step's launches depend on
     // the batch size, on the attention's length bucket and on the addresses of every buffer involved; all of that
     // is the key.  A key seen for the second time is captured, from then on replayed.
@@ -99,7 +100,8 @@ static void drop_weight_images(Model *m) {
     for (auto &kv : m->wimg) cudaFree(kv.second);
     for (auto &kv : m->wpair) cudaFree(kv.second);
     for (auto &kv : m->w13i) cudaFree(kv.second);
-    m->wimg.clear(), m->wpair.clear(), m->w13i.clear();
+    for (auto &kv : m->wscaled) cudaFree(kv.second);
+    m->wimg.clear(), m->wpair.clear(), m->w13i.clear(), m->wscaled.clear();
 }
 
 Registry<Model> &model_registry() {
@@ -370,8 +372,12 @@ __host__ __device__ constexpr size_t gemm_small_smem_bytes() { return sizeof(flo
 
 //
 // Fusions of the decode step (template flags):
-//   NORM  A is RMS-normalised on the fly: y = x * inv * gamma with inv from the row's sum of squares, which the
-//         PRODUCER of x has left as `parts_in` partial sums per row (added in ascending order: deterministic).
+//   NORM  the product is that of the RMS-normalised rows, y = (x * inv * gamma) W, computed as inv * (x (gamma W)):
+//         W is the caller's copy of the weights with row k scaled by gamma[k] (scaled_weight), and the row factor inv
+//         -- from the row's sum of squares, which the PRODUCER of x has left as `parts_in` partial sums per row (added in
+//         ascending order: deterministic) -- is applied to the finished sums.  Normalising every A fragment inside the k
+//         loop instead cost 1.3 us per launch (5.4 against 4.1 us for the Q,K,V product at batch 64): the loop could not
+//         start before inv was known and carried two multiplies per fragment.
 //   EPI 1 the epilogue also writes the sum of squares of its 32 output columns of every row (one partial per
 //         column tile) for the next NORM.
 //   EPI 2 W is a W1/W3 pair interleaved in groups of 16 columns; the epilogue writes h1 * g * sigmoid(g)
@@ -412,16 +418,9 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
     const int k_split = (EPI == 1 && F.k_split == 2) ? 2 : 1;
     const int k_part = k_split == 2 ? (int)(blockIdx.x & 1) : 0, col_tile = k_split == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int m0 = blockIdx.y * BM, n0 = col_tile * BN;
-    // norm weights into shared memory up front (weights: no need to wait for the previous kernel): read from global
-    // inside the k loop they put an L2 round trip into every one of its iterations
-    constexpr int kGammaSmem = 1024;
-    __shared__ float s_gamma[NORM ? kGammaSmem : 1];
-    const bool gamma_staged = NORM && K <= kGammaSmem;
 #ifdef JGPT_B200_DECODE_TRACE
     timeline_in(F.timeline);
 #endif
-    if (gamma_staged)
-        for (int k = tid; k < K; k += 256) s_gamma[k] = F.gamma[k];
     // weight tiles do not depend on the previous kernel either: a launch that moved in early requests the first
     // STAGES - 1 of them before it waits (they join the first committed group below)
     const int w_k = tid >> 3, w_c = (tid & 7) * 4;  // second chunk: k + 32
@@ -527,20 +526,10 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         if (kt + STAGES - 1 < nk) load_tiles((kt + STAGES - 1) % STAGES, kbase + (kt + STAGES - 1) * BK);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         uint32_t ah[MT][4], al[MT][4];
-        float g0 = 0.f, g1 = 0.f;
-        if (NORM) {
-            const int k = kbase + kt * BK + ks + t;
-            if (gamma_staged) g0 = k < K ? s_gamma[k] : 0.f, g1 = k + 4 < K ? s_gamma[k + 4] : 0.f;
-            else g0 = k < K ? F.gamma[k] : 0.f, g1 = k + 4 < K ? F.gamma[k + 4] : 0.f;
-        }
 #pragma unroll
         for (int i = 0; i < MT; i++) {
             const int r = 16 * i + g;
             float a0 = As[buf][r][ks + t], a1 = As[buf][r + 8][ks + t], a2 = As[buf][r][ks + t + 4], a3 = As[buf][r + 8][ks + t + 4];
-            if (NORM) {
-                const float ia = s_inv[r], ib = s_inv[r + 8];
-                a0 = a0 * ia * g0, a1 = a1 * ib * g0, a2 = a2 * ia * g1, a3 = a3 * ib * g1;
-            }
             split_tf32(a0, ah[i][0], al[i][0]);
             split_tf32(a1, ah[i][1], al[i][1]);
             split_tf32(a2, ah[i][2], al[i][2]);
@@ -585,6 +574,7 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
             float h = red[0][r][c], gv = red[0][r][16 + c];
 #pragma unroll
             for (int w = 1; w < 8; w++) h += red[w][r][c], gv += red[w][r][16 + c];
+            if (NORM) h *= s_inv[r], gv *= s_inv[r];
             float sg;
             if (gv >= 20.f) sg = 1.f;
             else if (gv <= -20.f) sg = 0.f;
@@ -599,7 +589,7 @@ __global__ void __launch_bounds__(256) gemm_tc_small_kernel(const float *__restr
         float v = red[0][r][c];
 #pragma unroll
         for (int w = 1; w < 8; w++) v += red[w][r][c];
-        vsum[i] = v;
+        vsum[i] = NORM ? v * s_inv[r] : v;
     }
     if (EPI == 1 && k_split == 2) {
         // the second CTA of the pair puts its sums into the first one's shared memory (behind the partial tiles) and is done
@@ -1048,6 +1038,26 @@ static int32_t pair_interleaved(Model *m, const float *W1, const float *W3, int 
     *out = it->second;
     return JGPT_OK;
 }
+// W [K, N] with row k multiplied by gamma[k]: the weights a NORM product reads (built once per weight set).
+__global__ void scale_rows_kernel(const float *__restrict__ W, const float *__restrict__ gamma, long long n, int N, float *__restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = gamma[i / N] * W[i];
+}
+static int32_t scaled_weight(Model *m, const float *W, const float *gamma, int K, int N, const float **out, bool *fresh) {
+    auto it = m->wscaled.find(W);
+    if (it == m->wscaled.end()) {
+        float *buf = nullptr;
+        JGPT_CUDA_TRY(cudaMalloc(&buf, sizeof(float) * (size_t)K * N));
+        it = m->wscaled.emplace(W, buf).first;
+        const long long n = (long long)K * N;
+        scale_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, m->ctx->stream>>>(W, gamma, n, N, buf);
+        JGPT_CUDA_TRY(cudaGetLastError());
+        *fresh = true;  // just written by a kernel on this stream: the launch that reads it must not run ahead of its wait
+    }
+    *out = it->second;
+    return JGPT_OK;
+}
+
 template <bool NORM, int EPI>
 static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int nb, const float *const *W, float *const *C,
                             const float *const *R, const int *rowsel, const SmallFuse &fuse_in) {
@@ -1132,8 +1142,13 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         // (its copy warp fetches tables and K/V slabs meanwhile; that product writes q / k / v only); 2 = the Wo product
         // moves in under the attention's tail as well; 3 = every projection of the layer chain.
         const int ov = step_overlap_level(m, rows);
-        const SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps, (ov >= 1 ? 2 : 0) | ((ov >= 3 && l > 0) ? 1 : 0)};
-        const float *Wqkv[3] = {y.wq, y.wk, y.wv};
+        SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps, (ov >= 1 ? 2 : 0) | ((ov >= 3 && l > 0) ? 1 : 0)};
+        const float *Wqkv[3] = {nullptr, nullptr, nullptr};
+        bool fresh_qkv = false;
+        if ((rc = scaled_weight(m, y.wq, y.norm1, D, D, &Wqkv[0], &fresh_qkv))) return rc;
+        if ((rc = scaled_weight(m, y.wk, y.norm1, D, D, &Wqkv[1], &fresh_qkv))) return rc;
+        if ((rc = scaled_weight(m, y.wv, y.norm1, D, D, &Wqkv[2], &fresh_qkv))) return rc;
+        if (fresh_qkv) n1.pdl &= ~1;
         float *Cqkv[3] = {m->q, m->k, m->v};
         if ((rc = small_launch<true, 0>(m, m->x, rows, D, D, 3, Wqkv, Cqkv, nullptr, nullptr, n1))) return rc;
         if ((rc = attn(l, nullptr, false))) return rc;
@@ -1145,6 +1160,7 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         const float *pair = nullptr;
         bool fresh = false;  // just written by a kernel on this stream: that launch must not read weights ahead of its wait
         if ((rc = pair_interleaved(m, y.w1, y.w3, D, F, &pair, &fresh))) return rc;
+        if ((rc = scaled_weight(m, pair, y.norm2, D, 2 * F, &pair, &fresh))) return rc;
         const float *Wp[1] = {pair};
         float *Ch[1] = {m->h1};
         if ((rc = small_launch<true, 2>(m, m->x, rows, D, 2 * F, 1, Wp, Ch, nullptr, nullptr,
@@ -1204,6 +1220,8 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
     float *C[1] = {m->logits};
     const int *rowsel = n_sel > 0 ? m->d_rowsel : nullptr;
     if (small_mode(m, rows)) {  // the last W2 projection left the row sums of squares in ss_a
+        bool fresh = false;
+        if ((rc = scaled_weight(m, m->lm_head, m->norm_final, D, m->vocab, &W[0], &fresh))) return rc;
         rc = small_launch<true, 0>(m, m->x, out_rows, D, m->vocab, 1, W, C, nullptr, rowsel,
                                    SmallFuse{m->norm_final, m->ss_a, nullptr, (D + 31) / 32, m->eps});
     } else {
