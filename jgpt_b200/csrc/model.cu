@@ -1081,7 +1081,10 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     // grid is: a few CTAs left for a second wave cost a whole tile time (W1,W3 from 145 rows on: 160 rows 1.01 ms per step)
     const long long resident = 3ll * m->ctx->sm_count, col_tiles = (long long)((N + 31) / 32) * nb;
     const bool spills = col_tiles * ((M + 15) / 16) > resident && col_tiles * ((M + 31) / 32) <= resident;
-    const bool wide = M >= small_rows_for_wide_tiles() || spills;
+    // a product of many column tiles (the LM head: 250) runs in several rounds of resident CTAs whatever the tile: with
+    // 32-row tiles it has half as many CTAs, each fetching its weight tile once for twice the rows
+    const bool many_cols = col_tiles > m->ctx->sm_count && M > 16;
+    const bool wide = M >= small_rows_for_wide_tiles() || spills || many_cols;
     // Wo / W2 of a step with few rows: pairs of CTAs split the k range (SmallFuse::k_split) while the launch still has at
     // most one CTA per SM.
     if (EPI == 1 && m->k_split && !rowsel && (K + kSmallBK - 1) / kSmallBK >= 4 &&
