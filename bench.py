@@ -310,13 +310,14 @@ def run_model_decode(ctx, ranks, batch=64, ctx_len=512, steps=40):
         for i in range(0, batch, per_call):
             _, toks[i:i + per_call] = model.forwardPrefillBatch(pool, seqs[i:i + per_call], prompts[i:i + per_call])
         lens = np.full(batch, ctx_len, np.int32)
+        seq_ids = np.asarray(seqs, np.int32)  # converted once, not per step
         dev_next = C.c_void_p()
         B.check(ctx._lib.jgpt_model_next_tokens_device(model.handle, C.byref(dev_next)))
         gathered = 0
 
         def one_step():
             nonlocal toks, gathered
-            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            _, toks = model.forwardDecodeBatch(pool, seq_ids, toks, lens, lens, want_logits=False)
             lens[:] += 1
             gather.submit_device(dev_next.value, batch)
             while gather.ready():

@@ -77,6 +77,7 @@ struct Model {
     uint32_t f_stamp = 0;       // stamps handed out so far; a launch uses f_stamp + 1 ... f_stamp + steps * layers
     int *f_ints = nullptr;      // tokens of a multi-step launch, steps done, abort word
     int *h_fused = nullptr;     // pinned: [kFusedMaxSteps * 4] tokens + steps done
+    int *hd_idx = nullptr, *hd_status = nullptr;  // device-side addresses of h_idx and of the context's status mirror (decode step without copies)
     int *hd_fused = nullptr, *hd_next = nullptr;  // device-side addresses of h_fused and h_next: the kernel writes its results there itself
     // The same for batches (decode_batch.cu; JGPT_B200_FUSED_BATCH=1: on): rows 5 .. fused_batch_rows
     int fused_batch = 0;
@@ -115,13 +116,30 @@ Registry<Model> &model_registry() {
 
 // x[r,:] = tok[id[r],:] + pos[posrow[r],:]   (embedding_token_fwd_kernel + add_position_embedding_broadcast_kernel,
 // src/main/cpp/jgpt_cuda_extra_kernels_launches.inl:937-955, 1020-1032)
+// With idx_host (the decode step): the step's five per-row words (id, position row, sequence, RoPE position, length; stride
+// R) are read from the caller's page-locked host block by the row's own CTA and left in idx_dev for the attention launches:
+// 5 n words instead of a copy of the whole 5 R block ahead of the step.
 __global__ void __launch_bounds__(128) embed_pos_kernel(const float *__restrict__ tok, const float *__restrict__ pos,
                                                         const int *__restrict__ ids, const int *__restrict__ posrow,
-                                                        float *__restrict__ x, int D, float *__restrict__ ss_out) {
+                                                        float *__restrict__ x, int D, float *__restrict__ ss_out,
+                                                        const int *idx_host = nullptr, int *idx_dev = nullptr, int R = 0) {
     __shared__ float red[4];
+    __shared__ int s_word[5];
     const int r = blockIdx.x;
-    const float4 *t = reinterpret_cast<const float4 *>(tok + (size_t)ids[r] * D);
-    const float4 *p = reinterpret_cast<const float4 *>(pos + (size_t)posrow[r] * D);
+    int id, prow;
+    if (idx_host) {
+        if (threadIdx.x < 5) {
+            const int w = idx_host[(size_t)threadIdx.x * R + r];
+            idx_dev[(size_t)threadIdx.x * R + r] = w;
+            s_word[threadIdx.x] = w;
+        }
+        __syncthreads();
+        id = s_word[0], prow = s_word[1];
+    } else {
+        id = ids[r], prow = posrow[r];
+    }
+    const float4 *t = reinterpret_cast<const float4 *>(tok + (size_t)id * D);
+    const float4 *p = reinterpret_cast<const float4 *>(pos + (size_t)prow * D);
     float4 *o = reinterpret_cast<float4 *>(x + (size_t)r * D);
     float ss = 0.f;
     for (int j = threadIdx.x; j < D / 4; j += blockDim.x) {
@@ -643,7 +661,10 @@ __global__ void __launch_bounds__(256) interleave_pair_kernel(const float *__res
 
 // Greedy argmax per row, ties -> lowest index (argmaxLogitsGreedy,
 // src/main/java/com/veles/llm/jgpt/model/GptAutoregressiveGenerator.java:288-299).
-__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ out) {
+// out_host (optional): the ids also go to the caller's page-locked host array, and the context's status word to its
+// host mirror, so that the step needs no copies behind its last kernel.
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ out,
+                                                     int *out_host = nullptr, const int *status_dev = nullptr, int *status_host = nullptr) {
     __shared__ float bv[8];
     __shared__ int bi[8];
     const float *row = logits + (size_t)blockIdx.x * V;
@@ -673,6 +694,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
         for (int w = 1; w < 8; w++)
             if (bv[w] > best || (bv[w] == best && bi[w] < idx)) best = bv[w], idx = bi[w];
         out[blockIdx.x] = idx;
+        if (out_host) out_host[blockIdx.x] = idx;
+        if (status_host && blockIdx.x == 0) *status_host = *status_dev;
     }
 }
 
@@ -1213,7 +1236,7 @@ static int32_t run_layers(Model *m, int rows, const PagedAppendArgs *paged, Attn
 }
 
 // Final norm + LM head over the rows listed in d_rowsel[0..n_sel) (or all rows), then argmax.
-static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = SampleSpec()) {
+static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = SampleSpec(), bool to_host = false) {
     const int D = m->d_model;
     cudaStream_t st = m->ctx->stream;
     const int out_rows = n_sel > 0 ? n_sel : rows;
@@ -1237,7 +1260,8 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
         if (rc) return rc;
         sample_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
     } else {
-        argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
+        if (to_host) argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next, m->hd_next, m->ctx->d_status, m->hd_status);
+        else argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
     }
     JGPT_CUDA_TRY(cudaGetLastError());
     return JGPT_OK;
@@ -1551,6 +1575,9 @@ int32_t jgpt_model_create(jgpt_ctx ctxh, int32_t vocab, int32_t max_seq_len, int
     JGPT_CUDA_TRY(cudaHostAlloc(&m->h_idx, sizeof(int) * 5 * R, cudaHostAllocDefault));
     JGPT_CUDA_TRY(cudaMalloc(&m->d_next, sizeof(int) * R));
     JGPT_CUDA_TRY(cudaHostAlloc(&m->h_next, sizeof(int) * R, cudaHostAllocDefault));
+    JGPT_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&m->hd_idx), m->h_idx, 0));
+    JGPT_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&m->hd_next), m->h_next, 0));
+    JGPT_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&m->hd_status), m->ctx->h_status, 0));
     JGPT_CUDA_TRY(cudaMalloc(&m->d_rowsel, sizeof(int) * R));
     JGPT_CUDA_TRY(cudaHostAlloc(&m->h_u, sizeof(float) * R, cudaHostAllocDefault));
     JGPT_CUDA_TRY(A(&m->d_u, R));
@@ -1880,19 +1907,27 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
         rc = ensure_sample_work(m, n);  // before any capture: it may allocate
         if (rc) return rc;
     }
+    // Greedy decode-sized steps move their few words themselves: the embedding kernel fetches the rows' descriptors from
+    // the page-locked block, the argmax kernel leaves ids and status word in the host mirrors (three copies less per step;
+    // the descriptor copy alone moved 5 R words whatever the batch).  JGPT_B200_STEP_COPIES=1: the copies.
+    static const int step_copies = env_int("JGPT_B200_STEP_COPIES", 0);
+    const bool no_copies = !sampled && !step_copies && small_mode(m, n);
     auto enqueue = [&]() -> int32_t {
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
+        if (!no_copies) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
         if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
-        embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
+        if (no_copies) embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, nullptr, nullptr, m->x, m->d_model, m->ss_a, m->hd_idx, m->d_idx, R);
+        else embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
         int32_t r2 = run_layers(m, n, nullptr, [&](int l, float *, bool) {
             return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att,
                                       (small_mode(m, n) && step_overlap_level(m, n) >= 1) ? 2 : -1);
         });
         if (r2) return r2;
-        r2 = lm_head(m, n, 0, spec);
+        r2 = lm_head(m, n, 0, spec, no_copies);
         if (r2) return r2;
-        JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
-        JGPT_CUDA_TRY(status_enqueue_read(m->ctx));  // part of the replayed graph too
+        if (!no_copies) {
+            JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
+            JGPT_CUDA_TRY(status_enqueue_read(m->ctx));  // part of the replayed graph too
+        }
         return JGPT_OK;
     };
     Model::DecodeGraph *slot = nullptr;

@@ -80,13 +80,14 @@ def run_decode_step(ctx, batch=64, ctx_len=512, steps=50):
         for i in range(0, batch, per_call):
             _, toks[i:i + per_call] = model.forwardPrefillBatch(pool, seqs[i:i + per_call], prompts[i:i + per_call])
         lens = np.full(batch, ctx_len, np.int32)
+        seq_ids = np.asarray(seqs, np.int32)  # converted once: a Python list costs ~5 us per call to turn into an array
         for _ in range(3):
-            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            _, toks = model.forwardDecodeBatch(pool, seq_ids, toks, lens, lens, want_logits=False)
             lens += 1
         ctx.synchronize()
         t0 = time.perf_counter()
         for _ in range(steps):
-            _, toks = model.forwardDecodeBatch(pool, seqs, toks, lens, lens, want_logits=False)
+            _, toks = model.forwardDecodeBatch(pool, seq_ids, toks, lens, lens, want_logits=False)
             lens += 1
         el = (time.perf_counter() - t0) / steps
         return {"workload": f"JGPT-35M batched decode step: batch {batch}, context {ctx_len}+, sampled ids fed back",
