@@ -66,6 +66,7 @@ struct Model {
     std::vector<DecodeGraph> decode_graphs;
     uint64_t decode_graph_clock = 0;
     int decode_graph_enabled = 1;
+    bool first_launch_early = false;  // set while a decode step is enqueued: its embedding kernel lets layer 0's Q,K,V product move in early
     int k_split = 1;  // Wo / W2 of a step with few rows as pairs of CTAs that split the k range (JGPT_B200_K_SPLIT=0: off)
     int w_resident = 1;  // projections of the decode step keep their CTA's weight slice in shared memory when the grid allows (JGPT_B200_W_RESIDENT=0: off)
     int step_overlap = -1;  // programmatic dependent launches inside the decode step (JGPT_B200_STEP_OVERLAP 0..3; -1 = the default, 3)
@@ -126,6 +127,7 @@ __global__ void __launch_bounds__(128) embed_pos_kernel(const float *__restrict_
     __shared__ float red[4];
     __shared__ int s_word[5];
     const int r = blockIdx.x;
+    griddep_launch_dependents();  // a successor launched as a programmatic dependent may move in (it waits for this kernel itself)
     int id, prow;
     if (idx_host) {
         if (threadIdx.x < 5) {
@@ -664,7 +666,9 @@ __global__ void __launch_bounds__(256) interleave_pair_kernel(const float *__res
 // out_host (optional): the ids also go to the caller's page-locked host array, and the context's status word to its
 // host mirror, so that the step needs no copies behind its last kernel.
 __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ out,
-                                                     int *out_host = nullptr, const int *status_dev = nullptr, int *status_host = nullptr) {
+                                                     int *out_host = nullptr, const int *status_dev = nullptr, int *status_host = nullptr,
+                                                     int pdl = 0) {
+    if (pdl) griddep_wait();  // launched as a programmatic dependent of the LM head
     __shared__ float bv[8];
     __shared__ int bi[8];
     const float *row = logits + (size_t)blockIdx.x * V;
@@ -1168,7 +1172,7 @@ static int32_t run_layers_small(Model *m, int rows, AttnFn &&attn) {
         // (its copy warp fetches tables and K/V slabs meanwhile; that product writes q / k / v only); 2 = the Wo product
         // moves in under the attention's tail as well; 3 = every projection of the layer chain.
         const int ov = step_overlap_level(m, rows);
-        SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps, (ov >= 1 ? 2 : 0) | ((ov >= 3 && l > 0) ? 1 : 0)};
+        SmallFuse n1{y.norm1, m->ss_a, nullptr, l == 0 ? 1 : parts, m->eps, (ov >= 1 ? 2 : 0) | ((ov >= 3 && (l > 0 || m->first_launch_early)) ? 1 : 0)};
         const float *Wqkv[3] = {nullptr, nullptr, nullptr};
         bool fresh_qkv = false;
         if ((rc = scaled_weight(m, y.wq, y.norm1, D, D, &Wqkv[0], &fresh_qkv))) return rc;
@@ -1236,7 +1240,7 @@ static int32_t run_layers(Model *m, int rows, const PagedAppendArgs *paged, Attn
 }
 
 // Final norm + LM head over the rows listed in d_rowsel[0..n_sel) (or all rows), then argmax.
-static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = SampleSpec(), bool to_host = false) {
+static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = SampleSpec(), bool to_host = false, bool early = false) {
     const int D = m->d_model;
     cudaStream_t st = m->ctx->stream;
     const int out_rows = n_sel > 0 ? n_sel : rows;
@@ -1249,7 +1253,7 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
         bool fresh = false;
         if ((rc = scaled_weight(m, m->lm_head, m->norm_final, D, m->vocab, &W[0], &fresh))) return rc;
         rc = small_launch<true, 0>(m, m->x, out_rows, D, m->vocab, 1, W, C, nullptr, rowsel,
-                                   SmallFuse{m->norm_final, m->ss_a, nullptr, (D + 31) / 32, m->eps});
+                                   SmallFuse{m->norm_final, m->ss_a, nullptr, (D + 31) / 32, m->eps, (early && !fresh) ? 3 : (early ? 2 : 0)});
     } else {
         rmsnorm_kernel<<<rows, 128, 0, st>>>(m->x, m->norm_final, m->xn, D, m->eps);
         rc = gemm(m, m->xn, out_rows, D, m->vocab, 1, W, C, nullptr, rowsel);
@@ -1260,7 +1264,15 @@ static int32_t lm_head(Model *m, int rows, int n_sel, const SampleSpec &spec = S
         if (rc) return rc;
         sample_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->d_samp, m->vocab, spec.temperature, spec.top_k, m->d_u, m->d_next);
     } else {
-        if (to_host) argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next, m->hd_next, m->ctx->d_status, m->hd_status);
+        if (to_host && early && small_mode(m, rows)) {  // moves in under the LM head's last CTAs
+            cudaLaunchConfig_t cfg = {};
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.gridDim = dim3((unsigned)out_rows), cfg.blockDim = dim3(256), cfg.stream = st, cfg.attrs = attr, cfg.numAttrs = 1;
+            const float *lg = m->logits;
+            JGPT_CUDA_TRY(cudaLaunchKernelEx(&cfg, argmax_kernel, lg, m->vocab, m->d_next, m->hd_next, (const int *)m->ctx->d_status, m->hd_status, 1));
+        } else if (to_host) argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next, m->hd_next, m->ctx->d_status, m->hd_status);
         else argmax_kernel<<<out_rows, 256, 0, st>>>(m->logits, m->vocab, m->d_next);
     }
     JGPT_CUDA_TRY(cudaGetLastError());
@@ -1915,14 +1927,17 @@ static int32_t forward_decode_impl(jgpt_model h, jgpt_kvpool poolh, const int32_
     auto enqueue = [&]() -> int32_t {
         if (!no_copies) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_idx, m->h_idx, sizeof(int) * 5 * (size_t)R, cudaMemcpyHostToDevice, st));
         if (sampled) JGPT_CUDA_TRY(cudaMemcpyAsync(m->d_u, m->h_u, sizeof(float) * (size_t)n, cudaMemcpyHostToDevice, st));
+        const bool chain_early = small_mode(m, n) && step_overlap_level(m, n) >= 3;
+        m->first_launch_early = chain_early;
         if (no_copies) embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, nullptr, nullptr, m->x, m->d_model, m->ss_a, m->hd_idx, m->d_idx, R);
         else embed_pos_kernel<<<n, 128, 0, st>>>(m->tok, m->pos, m->d_idx, m->d_idx + R, m->x, m->d_model, m->ss_a);
         int32_t r2 = run_layers(m, n, nullptr, [&](int l, float *, bool) {
             return launch_attn_decode(p, l, 1, m->q, m->k, m->v, m->d_idx + 2 * R, m->d_idx + 3 * R, m->d_idx + 4 * R, n, len_bucket, m->att,
                                       (small_mode(m, n) && step_overlap_level(m, n) >= 1) ? 2 : -1);
         });
+        m->first_launch_early = false;
         if (r2) return r2;
-        r2 = lm_head(m, n, 0, spec, no_copies);
+        r2 = lm_head(m, n, 0, spec, no_copies, chain_early);
         if (r2) return r2;
         if (!no_copies) {
             JGPT_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(int) * (size_t)n, cudaMemcpyDeviceToHost, st));
