@@ -197,6 +197,39 @@ def test_host_buffer_entry_point_equals_device_entry_point(ctx):
         a.close(), b.close()
 
 
+@pytest.mark.parametrize("way", [0, 1, 2])
+def test_every_way_of_moving_the_host_buffers_gives_the_same_bits(ctx, way, monkeypatch):
+    """JGPT_B200_HOST_ZEROCOPY pins how the host-buffer entry point moves its bytes (0 staged copies pipelined over layer
+    groups, 1 the kernel reads / writes the page-locked buffers itself, 2 inputs copied + result in place): six layers,
+    page-locked buffers, same bits as the device entry point and the same appended token."""
+    lens0 = [31, 32, 100, 7]
+    layers, n, D = 6, 4, 24 * 16
+    a = PagedCase(ctx, lens0, H=24, Dh=16, layers=layers, seed=43, spare_tokens=2)
+    b = PagedCase(ctx, lens0, H=24, Dh=16, layers=layers, seed=43, spare_tokens=2)
+    try:
+        rng = np.random.default_rng(11)
+        q, k, v = (rng.standard_normal((layers, n, D)).astype(np.float32) for _ in range(3))
+        lens1 = np.array(lens0, np.int32) + 1
+        rope = np.array(lens0, np.int32)
+        out_d = ctx.alloc((layers, n, D))
+        b.pool.attn_decode_append(0, layers, ctx.from_host(q), ctx.from_host(k), ctx.from_host(v), b.seq_ids_dev(),
+                                  ctx.from_host(rope), ctx.from_host(lens1), n, int(lens1.max()), out_d)
+        qp, kp, vp, op = (ctx.pinned_array((layers, n, D)) for _ in range(4))
+        qp[:], kp[:], vp[:] = q, k, v
+        monkeypatch.setenv("JGPT_B200_HOST_ZEROCOPY", str(way))
+        for _ in range(2):  # idempotent: the same token goes to the same slot
+            op[:] = np.nan
+            a.pool.attn_decode_append_host(0, layers, qp, kp, vp, a.seqs, rope, lens1, out=op)
+            assert np.array_equal(op, out_d.to_host())
+        q2 = ctx.from_host(rng.standard_normal((layers, n, D)).astype(np.float32))
+        o_a, o_b = ctx.alloc((layers, n, D)), ctx.alloc((layers, n, D))
+        for case, o in ((a, o_a), (b, o_b)):
+            case.pool.attn_decode(0, layers, q2, case.seq_ids_dev(), ctx.from_host(rope), ctx.from_host(lens1), n, int(lens1.max()), o)
+        assert np.array_equal(o_a.to_host(), o_b.to_host())
+    finally:
+        a.close(), b.close()
+
+
 def test_device_self_checks_report_instead_of_faulting(ctx):
     """A block table entry outside the pool is recorded in the status word (read by synchronize), the access
     is redirected inside the pool, nothing faults."""
