@@ -511,19 +511,20 @@ def test_overlapped_launches_inside_the_decode_step_change_nothing(ctx, level, m
     assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
 
 
-def test_resident_weight_slices_and_split_k_pairs(ctx, monkeypatch):
+@pytest.mark.parametrize("dm,heads,dff", [(256, 16, 512), (320, 20, 448)])
+def test_resident_weight_slices_and_split_k_pairs(ctx, monkeypatch, dm, heads, dff):
     """Two launch forms of the decode step's projections.  JGPT_B200_W_RESIDENT: a CTA keeps its whole weight slice in
     shared memory instead of a ring of four k tiles - the arithmetic is the same, so logits, ids and the cache payload are
     bit-identical.  JGPT_B200_K_SPLIT: Wo / W2 as pairs of CTAs that each run half of the k tiles - the two halves are
     added last instead of warp by warp, so logits agree to rounding (1e-4 of the largest logit on the first step), not bit for bit.  d_model 256 / d_ff 512
-    give those products 4 and 8 k tiles (pairs need at least 4)."""
-    om = O.Model(96, 80, 256, 16, 2, 512, eps=1e-5).init_random(seed=9, std=0.05)
+    give those products 4 and 8 k tiles (pairs need at least 4); 320 / 448 give 5 and 7: halves of unequal length."""
+    om = O.Model(96, 80, dm, heads, 2, dff, eps=1e-5).init_random(seed=9, std=0.05)
     outs = {}
     monkeypatch.setenv("JGPT_B200_FUSED_BATCH", "0")
     for resident, split in ((0, 0), (1, 0), (1, 1), (0, 1)):
         monkeypatch.setenv("JGPT_B200_W_RESIDENT", str(resident))
         monkeypatch.setenv("JGPT_B200_K_SPLIT", str(split))
-        gm = GPTModel(ctx, 96, 80, 256, 16, 2, 512, rmsNormEps=1e-5, maxRows=256)
+        gm = GPTModel(ctx, 96, 80, dm, heads, 2, dff, rmsNormEps=1e-5, maxRows=256)
         gm.setParameters(om.tensors())
         pool = gm.newPool(n_blocks=6 * 5, max_seqs=6)
         try:  # six rows: the multi-launch step
@@ -538,7 +539,7 @@ def test_resident_weight_slices_and_split_k_pairs(ctx, monkeypatch):
                 lens = lens + 1
                 rec.append(logits.copy())
                 toks = np.array([(3 * step + s) % 96 for s in range(6)], np.int32)  # fixed ids: the runs stay comparable
-            kd, vd = ctx.alloc((16, 80, 16)), ctx.alloc((16, 80, 16))
+            kd, vd = ctx.alloc((heads, 80, 16)), ctx.alloc((heads, 80, 16))
             pool.gather(1, seqs[0], int(lens[0]), 80, kd, vd)
             outs[(resident, split)] = (rec, kd.to_host(), vd.to_host())
         finally:
