@@ -1042,7 +1042,23 @@ int32_t launch_attn_decode(Pool *p, int layer0, int n_layers, const float *q, co
                 c = t;
                 break;
             }
-        c = std::max(c, (max_blocks + 31) / 32);  // a chunk holds at most 32 blocks
+        const int c_min = (max_blocks + 31) / 32;  // a chunk holds at most 32 blocks
+        if (c == 1 && (c_min > 1 || base > 2ll * p->ctx->sm_count)) {
+            // No split fits one wave: take the one with the least rounds x (chunk length + ~6 blocks' worth of per-CTA
+            // start-up and merge).  160 rows of 40 blocks: 3 chunks in 2 rounds (0.925 ms per step) against 2 chunks in
+            // 2 rounds (0.985); 224 rows: 2 chunks in 2 rounds (1.217) against 3 chunks in 3 (1.264).
+            long long best_cost = -1;
+            for (int t = c_min; t <= std::min(8, (max_blocks + 3) / 4); t++) {
+                const long long cap = t == 1 ? 2ll * p->ctx->sm_count : (long long)cluster_capacity(p, k_new != nullptr, threads, smem, t);
+                if (cap <= 0) continue;
+                // (clusters of three and more: a round counts as full at 15/16 of the capacity, like the one-wave rule above --
+                // 186 rows are two rounds of 93 three-CTA clusters on paper and measured 0.98 ms against 0.92 ms with pairs)
+                const long long full = t >= 3 ? 15 * cap : 16 * cap;
+                const long long rounds = (16 * base + full - 1) / full, cost = rounds * ((max_blocks + t - 1) / t + 6);
+                if (best_cost < 0 || cost < best_cost) best_cost = cost, c = t;
+            }
+        }
+        c = std::max(c, c_min);
         P.chunk_blocks = std::min(32, std::max(4, (max_blocks + c - 1) / c));
     } else {
         P.chunk_blocks = pick_chunk_blocks(p, (long long)n_layers * n * P.n_hg, max_blocks);
