@@ -1111,7 +1111,11 @@ static int32_t small_launch(Model *m, const float *A, int M, int K, int N, int n
     // a product of many column tiles (the LM head: 250) runs in several rounds of resident CTAs whatever the tile: with
     // 32-row tiles it has half as many CTAs, each fetching its weight tile once for twice the rows
     const bool many_cols = col_tiles > m->ctx->sm_count && M > 16;
-    const bool wide = M >= small_rows_for_wide_tiles() || spills || many_cols;
+    // Wo / W2 moving in early: 32-row tiles where only they bring the launch down to one CTA per SM (the early CTAs of a
+    // larger grid are packed three to an SM wherever there is room: 200 rows 1.145 -> 1.088 ms per step)
+    const bool solo_if_wide = EPI == 1 && (fuse.pdl & 1) && col_tiles * ((M + 15) / 16) > m->ctx->sm_count &&
+                              col_tiles * ((M + 31) / 32) <= m->ctx->sm_count;
+    const bool wide = M >= small_rows_for_wide_tiles() || spills || many_cols || solo_if_wide;
     // Wo / W2 of a step with few rows: pairs of CTAs split the k range (SmallFuse::k_split) while the launch still has at
     // most one CTA per SM.
     if (EPI == 1 && m->k_split && !rowsel && (K + kSmallBK - 1) / kSmallBK >= 4 &&
